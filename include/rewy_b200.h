@@ -1,0 +1,141 @@
+/*
+ * rewy_b200 — C ABI of the B200-native chunked delta-rule backward.
+ *
+ * One shared library (librewy_b200.so, sm_100a) exports the whole-family backward functions
+ * that the reference's four autograd backwards call, plus the stage functions they are made of.
+ * Every pointer is a DEVICE pointer to a contiguous token-major tensor; the library never
+ * allocates, frees or synchronises; all work is enqueued on the stream that is passed in.
+ * Fixed envelope (the reference's release envelope, src/fast_delta_rule/runtime.py:75-106):
+ * K = V = 128, chunk = 64, T a positive multiple of 64, equal q/k/v head counts.
+ *
+ * Layouts (element offsets):
+ *   [B,T,H,D]      ((b*T + t)*H + h)*D + d            q,k,v,do,w,u,qg,kg,v_new,dR,b_gate,w_gate and gradients
+ *   [B,T,H,64]     ((b*T + t)*H + h)*64 + j           Aqk, Akk: row t%64, column j of the chunk's 64x64 matrix
+ *   [B,T,H]        (b*T + t)*H + h                    beta, scalar gate, dbeta
+ *   [B,NT,H,K,V]   (((b*NT + n)*H + h)*128 + k)*128+v h, dh (NT = T/64)
+ *   [B,H,K,V]      ((b*H + h)*128 + k)*128 + v        initial_state, dht, dh0
+ * Gates are chunk-local inclusive cumulative sums in LOG2 units (FP32), as the forward saves them.
+ */
+#ifndef REWY_B200_H
+#define REWY_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* rewy_stream_t; /* a cudaStream_t */
+
+enum {
+  REWY_OK = 0,
+  REWY_ERR_NULL = 1,       /* a required pointer is NULL */
+  REWY_ERR_SHAPE = 2,      /* B,T,H outside the envelope */
+  REWY_ERR_ALIGN = 3,      /* a pointer is not 16-byte aligned */
+  REWY_ERR_WORKSPACE = 4,  /* workspace smaller than rewy_bwd_workspace_bytes() */
+  REWY_ERR_LAUNCH = 5,     /* a CUDA launch or API call failed */
+  REWY_ERR_DEVICE = 6,     /* a kernel gave up on a bounded wait (see rewy_read_device_status) */
+  REWY_ERR_UNSUPPORTED = 7 /* family/policy/flag combination not supported */
+};
+
+enum { REWY_DELTA = 0, REWY_GDN = 1, REWY_KDA = 2, REWY_GDN2 = 3 };
+enum { REWY_RECOMPUTE = 0, REWY_SAVED = 1 };
+enum { REWY_OUT_BF16 = 0, REWY_OUT_F32 = 1 };
+
+/* Arguments of one whole-family backward.  Unused pointers are NULL. */
+typedef struct RewyBwdArgs {
+  int32_t family;      /* REWY_DELTA / REWY_GDN / REWY_KDA / REWY_GDN2 */
+  int32_t policy;      /* REWY_RECOMPUTE: w,qg,kg,v_new,h are rebuilt; REWY_SAVED: they are passed in */
+  int32_t B, T, H;
+  int32_t out_dtype;   /* dtype of dq, dk (and db_gate, dw_gate): REWY_OUT_BF16 or REWY_OUT_F32 */
+  int32_t intra_passes;/* 0 = default (3); 1, 2 or 3 BF16 split passes for the matrix-intra products */
+  float scale;
+  /* inputs */
+  const void* q;       /* bf16 [B,T,H,128] */
+  const void* k;       /* bf16 [B,T,H,128] */
+  const void* v;       /* bf16 [B,T,H,128] */
+  const float* g;      /* fp32 log2 cumsum: [B,T,H,128] (KDA, GDN2), [B,T,H] (GDN), NULL (DeltaNet) */
+  const float* beta;   /* fp32 [B,T,H] (DeltaNet, GDN, KDA), NULL (GDN2) */
+  const void* b_gate;  /* bf16 [B,T,H,128] erase gate (GDN2 only) */
+  const void* w_gate;  /* bf16 [B,T,H,128] write gate (GDN2 only) */
+  const void* Aqk;     /* bf16 [B,T,H,64] (KDA, GDN2); NULL for DeltaNet/GDN (rebuilt) */
+  const void* Akk;     /* bf16 [B,T,H,64] */
+  const float* h0;     /* fp32 [B,H,128,128] or NULL */
+  const void* d_o;     /* bf16 [B,T,H,128] gradient of the output */
+  const float* dht;    /* fp32 [B,H,128,128] gradient of the final state, or NULL */
+  /* saved forward tensors (policy REWY_SAVED, KDA/GDN2 only) */
+  const void* w;       /* bf16 [B,T,H,128] = Akk (b*k*gamma) */
+  const void* qg;      /* bf16 [B,T,H,128] = q*gamma */
+  const void* kg;      /* bf16 [B,T,H,128] = k*exp2(g_last - g) */
+  const void* v_new;   /* bf16 [B,T,H,128] */
+  const void* h;       /* bf16 [B,T/64,H,128,128] state entering each chunk */
+  /* outputs */
+  void* dq;            /* out_dtype [B,T,H,128] */
+  void* dk;            /* out_dtype [B,T,H,128] */
+  void* dv;            /* bf16 [B,T,H,128] */
+  float* dg;           /* fp32, shape of g; NULL for DeltaNet */
+  float* dbeta;        /* fp32 [B,T,H]; NULL for GDN2 */
+  void* db_gate;       /* out_dtype [B,T,H,128] (GDN2) */
+  void* dw_gate;       /* out_dtype [B,T,H,128] (GDN2) */
+  float* dh0;          /* fp32 [B,H,128,128] or NULL (must be non-NULL iff h0 is) */
+  /* scratch */
+  void* workspace;
+  size_t workspace_bytes;
+} RewyBwdArgs;
+
+/* Inter-stage tensors; the whole-family functions carve them out of the workspace (or alias the
+ * saved tensors), the stage functions take them explicitly so each stage can be driven alone. */
+typedef struct RewyStageBuffers {
+  void* w;      /* bf16 [B,T,H,128] */
+  void* u;      /* bf16 [B,T,H,128]   (prepare -> forward scan only) */
+  void* qg;     /* bf16 [B,T,H,128] */
+  void* kg;     /* bf16 [B,T,H,128] */
+  void* v_new;  /* bf16 [B,T,H,128] */
+  void* h;      /* bf16 [B,NT,H,128,128] */
+  void* Aqk;    /* bf16 [B,T,H,64] */
+  void* dh;     /* bf16 [B,NT,H,128,128] */
+  void* dR;     /* bf16 [B,T,H,128] */
+} RewyStageBuffers;
+
+/* Whole-family backward.  Replace, one for one, the functions the reference's autograd backwards call:
+ *   rewy_kda_bwd    <- chunk_kda_bwd            as bound at src/fast_delta_rule/_compat/kda.py:169-201
+ *                      (implemented by backends/backward.py:63-73, kda_backward)
+ *   rewy_gdn2_bwd   <- chunk_gdn2_bwd           _compat/gdn2.py:145-171 (backends/backward.py:75-81)
+ *   rewy_gdn_bwd    <- chunk_gated_delta_rule_bwd  _compat/gdn.py:240-260 (backends/backward.py:133-134)
+ *   rewy_delta_bwd  <- chunk_delta_rule_bwd     _compat/delta.py:125-138 (backends/backward.py:136-137)
+ * Return REWY_OK or an error code; rewy_last_error() gives the text. */
+int rewy_kda_bwd(const RewyBwdArgs* args, rewy_stream_t stream);
+int rewy_gdn2_bwd(const RewyBwdArgs* args, rewy_stream_t stream);
+int rewy_gdn_bwd(const RewyBwdArgs* args, rewy_stream_t stream);
+int rewy_delta_bwd(const RewyBwdArgs* args, rewy_stream_t stream);
+
+/* Bytes of workspace a whole-family call needs (the reference's orchestrators allocate the same
+ * intermediates with torch: FLA chunk_kda_bwd stages 1-5, cf. backends/backward.py:15-43,96-131). */
+size_t rewy_bwd_workspace_bytes(int32_t family, int32_t policy, int32_t B, int32_t T, int32_t H);
+
+/* Stage functions.
+ *   rewy_stage_prepare  <- FLA recompute_w_u_fwd (+ Aqk rebuild for the scalar families), called at
+ *                          backends/backward.py:116 and inside FLA chunk_kda_bwd/chunk_gdn2_bwd
+ *   rewy_stage_fwd_scan <- FLA chunk_gated_delta_rule_fwd_h, backends/backward.py:117-118
+ *   rewy_stage_bwd_scan <- chunk_gated_delta_rule_bwd_dhu (FLA; kernels/vector_state_gpu.py:47-67 for GDN2)
+ *                          fused with chunk_kda_bwd_dAv's dv = Aqk^T dO / chunk_bwd_dv_local (backward.py:119-121)
+ *   rewy_stage_chunk_adjoint <- residual WY + matrix intra + reverse gate cumsum:
+ *                          kernels/kda_residual_local_beta.py:8-23, kernels/endpoint_intra.py:306-326,
+ *                          kernels/gdn2_consumer_fp32.py:76-98, kernels/scalar_liveness_gpu.py:87-102,
+ *                          FLA chunk_local_cumsum(reverse=True)
+ */
+int rewy_stage_prepare(const RewyBwdArgs* args, const RewyStageBuffers* buf, rewy_stream_t stream);
+int rewy_stage_fwd_scan(const RewyBwdArgs* args, const RewyStageBuffers* buf, rewy_stream_t stream);
+int rewy_stage_bwd_scan(const RewyBwdArgs* args, const RewyStageBuffers* buf, rewy_stream_t stream);
+int rewy_stage_chunk_adjoint(const RewyBwdArgs* args, const RewyStageBuffers* buf, rewy_stream_t stream);
+
+/* Diagnostics. */
+const char* rewy_last_error(void);       /* thread-local text of the last non-zero status */
+const char* rewy_version(void);
+int rewy_kernel_launch_count(void);      /* kernels launched by this library in this process so far */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* REWY_B200_H */

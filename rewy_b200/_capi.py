@@ -1,0 +1,98 @@
+"""ctypes binding of librewy_b200.so (the C ABI declared in include/rewy_b200.h).
+
+There is no fallback: if the shared library is missing or a call returns a non-zero status a
+RuntimeError is raised.  Tensors are passed as raw device pointers; the launches go to torch's
+current CUDA stream.
+"""
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_int32, c_size_t, c_void_p
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "librewy_b200.so"
+
+DELTA, GDN, KDA, GDN2 = 0, 1, 2, 3
+FAMILY_ID = {"delta": DELTA, "gdn": GDN, "kda": KDA, "gdn2": GDN2}
+RECOMPUTE, SAVED = 0, 1
+OUT_BF16, OUT_F32 = 0, 1
+
+EXPORTS = (
+    "rewy_kda_bwd", "rewy_gdn2_bwd", "rewy_gdn_bwd", "rewy_delta_bwd", "rewy_bwd_workspace_bytes",
+    "rewy_stage_prepare", "rewy_stage_fwd_scan", "rewy_stage_bwd_scan", "rewy_stage_chunk_adjoint",
+    "rewy_last_error", "rewy_version", "rewy_kernel_launch_count",
+)
+
+
+class BwdArgs(ctypes.Structure):
+    _fields_ = [
+        ("family", c_int32), ("policy", c_int32), ("B", c_int32), ("T", c_int32), ("H", c_int32),
+        ("out_dtype", c_int32), ("intra_passes", c_int32), ("scale", c_float),
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("g", c_void_p), ("beta", c_void_p),
+        ("b_gate", c_void_p), ("w_gate", c_void_p), ("Aqk", c_void_p), ("Akk", c_void_p), ("h0", c_void_p),
+        ("d_o", c_void_p), ("dht", c_void_p),
+        ("w", c_void_p), ("qg", c_void_p), ("kg", c_void_p), ("v_new", c_void_p), ("h", c_void_p),
+        ("dq", c_void_p), ("dk", c_void_p), ("dv", c_void_p), ("dg", c_void_p), ("dbeta", c_void_p),
+        ("db_gate", c_void_p), ("dw_gate", c_void_p), ("dh0", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+    ]
+
+
+class StageBuffers(ctypes.Structure):
+    _fields_ = [(n, c_void_p) for n in ("w", "u", "qg", "kg", "v_new", "h", "Aqk", "dh", "dR")]
+
+
+_lib = None
+
+
+def library_path():
+    return LIB_PATH
+
+
+def load():
+    """Load the shared library once; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m rewy_b200.build` (needs nvcc). "
+            "rewy_b200 has no CPU or PyTorch fallback for the backward.")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name in ("rewy_kda_bwd", "rewy_gdn2_bwd", "rewy_gdn_bwd", "rewy_delta_bwd"):
+        fn = getattr(lib, name)
+        fn.argtypes = [ctypes.POINTER(BwdArgs), c_void_p]
+        fn.restype = c_int
+    for name in ("rewy_stage_prepare", "rewy_stage_fwd_scan", "rewy_stage_bwd_scan", "rewy_stage_chunk_adjoint"):
+        fn = getattr(lib, name)
+        fn.argtypes = [ctypes.POINTER(BwdArgs), ctypes.POINTER(StageBuffers), c_void_p]
+        fn.restype = c_int
+    lib.rewy_bwd_workspace_bytes.argtypes = [c_int32, c_int32, c_int32, c_int32, c_int32]
+    lib.rewy_bwd_workspace_bytes.restype = c_size_t
+    lib.rewy_last_error.restype = c_char_p
+    lib.rewy_version.restype = c_char_p
+    lib.rewy_kernel_launch_count.restype = c_int
+    _lib = lib
+    return lib
+
+
+def ptr(t):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def check(status, what):
+    if status != 0:
+        msg = load().rewy_last_error().decode()
+        raise RuntimeError(f"rewy_b200 {what} failed with status {status}: {msg}")
+
+
+def current_stream(device):
+    import torch
+    return c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def workspace_bytes(family, policy, B, T, H):
+    return int(load().rewy_bwd_workspace_bytes(family, policy, B, T, H))
+
+
+def launch_count():
+    return int(load().rewy_kernel_launch_count())

@@ -1,0 +1,211 @@
+// C ABI of the library: argument validation, workspace carving and stage sequencing.
+// No allocation, no synchronisation; every launch goes to the caller's stream.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include "common.cuh"
+
+namespace rewy {
+namespace {
+
+thread_local char g_error[512] = "";
+std::atomic<int> g_launches{0};
+
+int fail(int code, const char* fmt, const char* what = "", long long x = 0) {
+  snprintf(g_error, sizeof(g_error), fmt, what, x);
+  return code;
+}
+
+size_t align_up(size_t x) { return (x + 255) & ~size_t(255); }
+
+struct Plan {
+  bool prepare;       // rebuild w,u,qg,kg (+ forward scan for v_new,h)
+  bool build_aqk;     // scalar families save no Aqk
+  size_t off_dh, off_dR, off_w, off_u, off_qg, off_kg, off_vnew, off_h, off_aqk, total;
+};
+
+Plan make_plan(int family, int policy, long long B, long long T, long long H) {
+  Plan p{};
+  const size_t n = (size_t)B * T * H;  // token-heads
+  p.build_aqk = family == REWY_DELTA || family == REWY_GDN;
+  p.prepare = p.build_aqk || policy == REWY_RECOMPUTE;
+  size_t o = 0;
+  p.off_dh = o; o += align_up(n * 512);
+  p.off_dR = o; o += align_up(n * 256);
+  if (p.prepare) {
+    p.off_w = o; o += align_up(n * 256);
+    p.off_u = o; o += align_up(n * 256);
+    p.off_qg = o; o += align_up(n * 256);
+    p.off_kg = o; o += align_up(n * 256);
+    p.off_vnew = o; o += align_up(n * 256);
+    p.off_h = o; o += align_up(n * 512);
+  }
+  if (p.build_aqk) { p.off_aqk = o; o += align_up(n * 128); }
+  p.total = o;
+  return p;
+}
+
+bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; }
+
+#define REQUIRE_PTR(name)                                                                  \
+  do {                                                                                     \
+    if (a->name == nullptr) return fail(REWY_ERR_NULL, "required pointer '%s' is NULL", #name); \
+    if (misaligned(a->name)) return fail(REWY_ERR_ALIGN, "pointer '%s' is not 16-byte aligned", #name); \
+  } while (0)
+#define OPTIONAL_PTR(name)                                                                 \
+  do {                                                                                     \
+    if (a->name != nullptr && misaligned(a->name))                                         \
+      return fail(REWY_ERR_ALIGN, "pointer '%s' is not 16-byte aligned", #name);           \
+  } while (0)
+
+int validate_common(const RewyBwdArgs* a, int family) {
+  if (a == nullptr) return fail(REWY_ERR_NULL, "args is NULL%s");
+  if (a->family != family) return fail(REWY_ERR_UNSUPPORTED, "args->family does not match the entry point%s");
+  if (a->policy != REWY_RECOMPUTE && a->policy != REWY_SAVED) return fail(REWY_ERR_UNSUPPORTED, "unknown policy%s");
+  if (a->out_dtype != REWY_OUT_BF16 && a->out_dtype != REWY_OUT_F32)
+    return fail(REWY_ERR_UNSUPPORTED, "unknown out_dtype%s");
+  if (a->intra_passes < 0 || a->intra_passes > 3) return fail(REWY_ERR_UNSUPPORTED, "intra_passes must be 0..3%s");
+  if (a->B <= 0 || a->H <= 0) return fail(REWY_ERR_SHAPE, "B and H must be positive%s");
+  if (a->T < C || a->T % C != 0) return fail(REWY_ERR_SHAPE, "T must be a positive multiple of 64 (got %s%lld)", "", a->T);
+  if ((long long)a->B * a->H > 65535) return fail(REWY_ERR_SHAPE, "B*H exceeds the grid limit 65535%s");
+  REQUIRE_PTR(q); REQUIRE_PTR(k); REQUIRE_PTR(v); REQUIRE_PTR(Akk); REQUIRE_PTR(d_o);
+  REQUIRE_PTR(dq); REQUIRE_PTR(dk); REQUIRE_PTR(dv);
+  OPTIONAL_PTR(h0); OPTIONAL_PTR(dht); OPTIONAL_PTR(dh0);
+  if (family == REWY_DELTA) {
+    if (a->g != nullptr || a->dg != nullptr) return fail(REWY_ERR_UNSUPPORTED, "DeltaNet takes no gate%s");
+  } else {
+    REQUIRE_PTR(g); REQUIRE_PTR(dg);
+  }
+  if (family == REWY_GDN2) {
+    REQUIRE_PTR(b_gate); REQUIRE_PTR(w_gate); REQUIRE_PTR(db_gate); REQUIRE_PTR(dw_gate);
+  } else {
+    REQUIRE_PTR(beta); REQUIRE_PTR(dbeta);
+  }
+  if (family == REWY_KDA || family == REWY_GDN2) {
+    REQUIRE_PTR(Aqk);
+    if (a->policy == REWY_SAVED) { REQUIRE_PTR(w); REQUIRE_PTR(qg); REQUIRE_PTR(kg); REQUIRE_PTR(v_new); REQUIRE_PTR(h); }
+  } else if (a->policy == REWY_SAVED) {
+    return fail(REWY_ERR_UNSUPPORTED, "the scalar-gate families always recompute (no saved WY tensors)%s");
+  }
+  return REWY_OK;
+}
+
+int check_cuda(cudaError_t e, const char* stage) {
+  if (e == cudaSuccess) return REWY_OK;
+  snprintf(g_error, sizeof(g_error), "%s: %s", stage, cudaGetErrorString(e));
+  return REWY_ERR_LAUNCH;
+}
+
+int run_family(const RewyBwdArgs* a, int family, cudaStream_t st) {
+  int rc = validate_common(a, family);
+  if (rc != REWY_OK) return rc;
+  const Plan p = make_plan(family, a->policy, a->B, a->T, a->H);
+  if (a->workspace == nullptr) return fail(REWY_ERR_NULL, "required pointer '%s' is NULL", "workspace");
+  if (misaligned(a->workspace)) return fail(REWY_ERR_ALIGN, "pointer '%s' is not 16-byte aligned", "workspace");
+  if (a->workspace_bytes < p.total)
+    return fail(REWY_ERR_WORKSPACE, "workspace too small: need %s%lld bytes", "", (long long)p.total);
+  char* ws = static_cast<char*>(a->workspace);
+  RewyStageBuffers s{};
+  s.dh = ws + p.off_dh;
+  s.dR = ws + p.off_dR;
+  if (p.prepare) {
+    s.w = ws + p.off_w; s.u = ws + p.off_u; s.qg = ws + p.off_qg; s.kg = ws + p.off_kg;
+    s.v_new = ws + p.off_vnew; s.h = ws + p.off_h;
+  } else {
+    s.w = const_cast<void*>(a->w); s.qg = const_cast<void*>(a->qg); s.kg = const_cast<void*>(a->kg);
+    s.v_new = const_cast<void*>(a->v_new); s.h = const_cast<void*>(a->h);
+  }
+  s.Aqk = p.build_aqk ? static_cast<void*>(ws + p.off_aqk) : const_cast<void*>(a->Aqk);
+  if (p.prepare) {
+    if ((rc = check_cuda(launch_prepare(*a, s, st), "prepare")) != REWY_OK) return rc;
+    if ((rc = check_cuda(launch_fwd_scan(*a, s, st), "forward state scan")) != REWY_OK) return rc;
+  }
+  if ((rc = check_cuda(launch_bwd_scan(*a, s, st), "reverse state scan")) != REWY_OK) return rc;
+  if ((rc = check_cuda(launch_chunk_adjoint(*a, s, st), "chunk adjoint")) != REWY_OK) return rc;
+  return REWY_OK;
+}
+
+int validate_stage(const RewyBwdArgs* a, const RewyStageBuffers* s) {
+  if (a == nullptr || s == nullptr) return fail(REWY_ERR_NULL, "args or buffers is NULL%s");
+  if (a->family < REWY_DELTA || a->family > REWY_GDN2) return fail(REWY_ERR_UNSUPPORTED, "unknown family%s");
+  if (a->B <= 0 || a->H <= 0 || a->T < C || a->T % C != 0) return fail(REWY_ERR_SHAPE, "bad B/T/H%s");
+  if ((long long)a->B * a->H > 65535) return fail(REWY_ERR_SHAPE, "B*H exceeds the grid limit 65535%s");
+  return REWY_OK;
+}
+
+#define STAGE_PTR(expr, name)                                                               \
+  do {                                                                                      \
+    if ((expr) == nullptr) return fail(REWY_ERR_NULL, "required pointer '%s' is NULL", name); \
+    if (misaligned(expr)) return fail(REWY_ERR_ALIGN, "pointer '%s' is not 16-byte aligned", name); \
+  } while (0)
+
+}  // namespace
+
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+}  // namespace rewy
+
+using namespace rewy;
+
+extern "C" {
+
+int rewy_kda_bwd(const RewyBwdArgs* a, rewy_stream_t st) { return run_family(a, REWY_KDA, (cudaStream_t)st); }
+int rewy_gdn2_bwd(const RewyBwdArgs* a, rewy_stream_t st) { return run_family(a, REWY_GDN2, (cudaStream_t)st); }
+int rewy_gdn_bwd(const RewyBwdArgs* a, rewy_stream_t st) { return run_family(a, REWY_GDN, (cudaStream_t)st); }
+int rewy_delta_bwd(const RewyBwdArgs* a, rewy_stream_t st) { return run_family(a, REWY_DELTA, (cudaStream_t)st); }
+
+size_t rewy_bwd_workspace_bytes(int32_t family, int32_t policy, int32_t B, int32_t T, int32_t H) {
+  if (B <= 0 || T <= 0 || H <= 0) return 0;
+  return make_plan(family, policy, B, T, H).total;
+}
+
+int rewy_stage_prepare(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_stream_t st) {
+  int rc = validate_stage(a, s);
+  if (rc != REWY_OK) return rc;
+  STAGE_PTR(a->q, "q"); STAGE_PTR(a->k, "k"); STAGE_PTR(a->v, "v"); STAGE_PTR(a->Akk, "Akk");
+  STAGE_PTR(s->w, "w"); STAGE_PTR(s->u, "u"); STAGE_PTR(s->qg, "qg"); STAGE_PTR(s->kg, "kg");
+  if (a->family != REWY_DELTA) STAGE_PTR(a->g, "g");
+  if (a->family == REWY_GDN2) { STAGE_PTR(a->b_gate, "b_gate"); STAGE_PTR(a->w_gate, "w_gate"); }
+  else STAGE_PTR(a->beta, "beta");
+  if (a->family == REWY_DELTA || a->family == REWY_GDN) STAGE_PTR(s->Aqk, "Aqk");
+  return check_cuda(launch_prepare(*a, *s, (cudaStream_t)st), "prepare");
+}
+
+int rewy_stage_fwd_scan(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_stream_t st) {
+  int rc = validate_stage(a, s);
+  if (rc != REWY_OK) return rc;
+  STAGE_PTR(s->kg, "kg"); STAGE_PTR(s->w, "w"); STAGE_PTR(s->u, "u"); STAGE_PTR(s->h, "h"); STAGE_PTR(s->v_new, "v_new");
+  if (a->family != REWY_DELTA) STAGE_PTR(a->g, "g");
+  return check_cuda(launch_fwd_scan(*a, *s, (cudaStream_t)st), "forward state scan");
+}
+
+int rewy_stage_bwd_scan(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_stream_t st) {
+  int rc = validate_stage(a, s);
+  if (rc != REWY_OK) return rc;
+  STAGE_PTR(s->qg, "qg"); STAGE_PTR(s->kg, "kg"); STAGE_PTR(s->w, "w"); STAGE_PTR(s->Aqk, "Aqk");
+  STAGE_PTR(a->d_o, "d_o"); STAGE_PTR(s->dh, "dh"); STAGE_PTR(s->dR, "dR");
+  if (a->family != REWY_DELTA) STAGE_PTR(a->g, "g");
+  return check_cuda(launch_bwd_scan(*a, *s, (cudaStream_t)st), "reverse state scan");
+}
+
+int rewy_stage_chunk_adjoint(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_stream_t st) {
+  int rc = validate_stage(a, s);
+  if (rc != REWY_OK) return rc;
+  STAGE_PTR(a->q, "q"); STAGE_PTR(a->k, "k"); STAGE_PTR(a->v, "v"); STAGE_PTR(a->Akk, "Akk"); STAGE_PTR(a->d_o, "d_o");
+  STAGE_PTR(s->v_new, "v_new"); STAGE_PTR(s->h, "h"); STAGE_PTR(s->dh, "dh"); STAGE_PTR(s->dR, "dR");
+  STAGE_PTR(a->dq, "dq"); STAGE_PTR(a->dk, "dk"); STAGE_PTR(a->dv, "dv");
+  if (a->family != REWY_DELTA) { STAGE_PTR(a->g, "g"); STAGE_PTR(a->dg, "dg"); }
+  if (a->family == REWY_GDN2) {
+    STAGE_PTR(a->b_gate, "b_gate"); STAGE_PTR(a->w_gate, "w_gate"); STAGE_PTR(a->db_gate, "db_gate");
+    STAGE_PTR(a->dw_gate, "dw_gate");
+  } else {
+    STAGE_PTR(a->beta, "beta"); STAGE_PTR(a->dbeta, "dbeta");
+  }
+  return check_cuda(launch_chunk_adjoint(*a, *s, (cudaStream_t)st), "chunk adjoint");
+}
+
+const char* rewy_last_error(void) { return g_error; }
+const char* rewy_version(void) { return "rewy_b200 0.1.0 (sm_100a)"; }
+int rewy_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

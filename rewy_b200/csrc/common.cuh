@@ -1,0 +1,67 @@
+// Shared definitions of the delta-rule backward kernels (sm_100a).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../../include/rewy_b200.h"
+
+namespace rewy {
+
+constexpr int C = 64;    // chunk rows
+constexpr int DK = 128;  // key head dim
+constexpr int DV = 128;  // value head dim
+
+enum GateMode { GATE_NONE = 0, GATE_SCALAR = 1, GATE_VECTOR = 2 };
+
+using bf16 = __nv_bfloat16;
+
+struct Dims {
+  int B, T, H, NT;
+};
+
+// Host-side launchers (one per stage); each returns a cudaError_t from the launch.
+cudaError_t launch_prepare(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);
+cudaError_t launch_fwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);
+cudaError_t launch_bwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);
+cudaError_t launch_chunk_adjoint(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);
+void count_launch(int n = 1);
+
+__host__ __device__ inline int gate_mode_of(int family) {
+  return family == REWY_DELTA ? GATE_NONE : (family == REWY_GDN ? GATE_SCALAR : GATE_VECTOR);
+}
+
+// ---- small device helpers -------------------------------------------------------------------
+__device__ __forceinline__ float bf2f(bf16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ bf16 f2bf(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&p);
+}
+__device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
+  __nv_bfloat162 p = *reinterpret_cast<__nv_bfloat162*>(&u);
+  return __bfloat1622float2(p);
+}
+
+// Copy a [rows x cols] BF16 tile (cols multiple of 8) from global (row pitch g_ld elements) to
+// shared (row pitch s_ld elements) with 16-byte accesses by the whole CTA.
+template <int ROWS, int COLS>
+__device__ __forceinline__ void load_tile_bf16(bf16* __restrict__ s, int s_ld, const bf16* __restrict__ g,
+                                               size_t g_ld) {
+  constexpr int V8 = COLS / 8;
+  for (int i = threadIdx.x; i < ROWS * V8; i += blockDim.x) {
+    int r = i / V8, c = (i % V8) * 8;
+    *reinterpret_cast<uint4*>(s + r * s_ld + c) = *reinterpret_cast<const uint4*>(g + (size_t)r * g_ld + c);
+  }
+}
+template <int ROWS, int COLS>
+__device__ __forceinline__ void store_tile_bf16(bf16* __restrict__ g, size_t g_ld, const bf16* __restrict__ s,
+                                                int s_ld) {
+  constexpr int V8 = COLS / 8;
+  for (int i = threadIdx.x; i < ROWS * V8; i += blockDim.x) {
+    int r = i / V8, c = (i % V8) * 8;
+    *reinterpret_cast<uint4*>(g + (size_t)r * g_ld + c) = *reinterpret_cast<const uint4*>(s + r * s_ld + c);
+  }
+}
+
+}  // namespace rewy

@@ -1,0 +1,219 @@
+"""Autograd functions and public operators of the four families.
+
+Same contracts as the reference's private autograd copies (src/fast_delta_rule/_compat/kda.py:23-210,
+gdn.py:128-267, gdn2.py:43-201, delta.py:19-141): the forward saves FLA's tensor set (policy
+``disable_recompute`` decides whether w,u,qg,kg,v_new,h are kept), the backward hands them to the
+whole-family backward of ``rewy_b200.backward`` and casts to the input dtypes.  The backward stays bound
+to this implementation after a ``use_backend`` context exits, like the reference's.
+"""
+import torch
+
+from . import backward as _bwd
+from .forward import chunk_forward
+
+
+def _l2norm_fwd(x, eps=1e-6):
+    xf = x.float()
+    rstd = torch.rsqrt(xf.pow(2).sum(-1, keepdim=True) + eps)
+    return (xf * rstd).to(x.dtype), rstd
+
+
+def _l2norm_bwd(y, rstd, dy):
+    yf, dyf = y.float(), dy.float()
+    return (dyf * rstd - (dyf * yf).sum(-1, keepdim=True) * yf * rstd)
+
+
+def _sigmoid_bwd(x, dy, scale):
+    s = torch.sigmoid(x.float())
+    return dy.float() * scale * s * (1 - s)
+
+
+class ChunkKDAFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
+                use_beta_sigmoid_in_kernel, allow_neg_eigval, disable_recompute):
+        q_rstd = k_rstd = None
+        if use_qk_l2norm_in_kernel:
+            q, q_rstd = _l2norm_fwd(q)
+            k, k_rstd = _l2norm_fwd(k)
+        beta_raw = beta
+        if use_beta_sigmoid_in_kernel:
+            beta = (torch.sigmoid(beta_raw.float()) * (2.0 if allow_neg_eigval else 1.0)).to(beta_raw.dtype)
+        f = chunk_forward("kda", q, k, v, g=g, beta=beta, scale=scale, initial_state=initial_state,
+                          output_final_state=output_final_state)
+        keep = (lambda x: x) if disable_recompute else (lambda x: None)
+        ctx.save_for_backward(q, q_rstd, k, k_rstd, v, f["g_cumsum"], g, beta_raw, beta, f["Aqk"], f["Akk"],
+                              keep(f["w"]), keep(f["u"]), keep(f["qg"]), keep(f["kg"]), keep(f["v_new"]),
+                              keep(f["h"]), initial_state)
+        ctx.scale, ctx.disable_recompute = scale, disable_recompute
+        ctx.use_qk_l2norm_in_kernel, ctx.use_beta_sigmoid_in_kernel = use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel
+        ctx.allow_neg_eigval = allow_neg_eigval
+        return f["o"].type_as(q), f["final_state"]
+
+    @staticmethod
+    def backward(ctx, do, dht):
+        (q, q_rstd, k, k_rstd, v, g_cumsum, g_input, beta_raw, beta, Aqk, Akk, w, u, qg, kg, v_new, h,
+         initial_state) = ctx.saved_tensors
+        fuse_cast = not ctx.use_qk_l2norm_in_kernel
+        dq, dk, dv, db, dg, dh0, _, _ = _bwd.kda_backward(
+            q=q, k=k, v=v, beta=beta, Aqk=Aqk, Akk=Akk, scale=ctx.scale, initial_state=initial_state, do=do, dht=dht,
+            g=g_cumsum, disable_recompute=ctx.disable_recompute, w=w, u=u, qg=qg, kg=kg, v_new=v_new, h=h,
+            out_dtype=torch.bfloat16 if fuse_cast else torch.float32)
+        if ctx.use_qk_l2norm_in_kernel:
+            dq = _l2norm_bwd(q, q_rstd, dq)
+            dk = _l2norm_bwd(k, k_rstd, dk)
+        if ctx.use_beta_sigmoid_in_kernel:
+            db = _sigmoid_bwd(beta_raw, db, 2.0 if ctx.allow_neg_eigval else 1.0)
+        return (dq.to(q), dk.to(k), dv.to(v), dg.to(g_input), db.to(beta_raw), None, dh0, None, None, None, None, None)
+
+
+class ChunkGDN2Function(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, g, b, w, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
+                disable_recompute):
+        q_rstd = k_rstd = None
+        if use_qk_l2norm_in_kernel:
+            q, q_rstd = _l2norm_fwd(q)
+            k, k_rstd = _l2norm_fwd(k)
+        f = chunk_forward("gdn2", q, k, v, g=g, b=b, w=w, scale=scale, initial_state=initial_state,
+                          output_final_state=output_final_state)
+        keep = (lambda x: x) if disable_recompute else (lambda x: None)
+        ctx.save_for_backward(q, q_rstd, k, k_rstd, v, f["g_cumsum"], g, b, w, f["Aqk"], f["Akk"], keep(f["w"]),
+                              keep(f["u"]), keep(f["qg"]), keep(f["kg"]), keep(f["v_new"]), keep(f["h"]), initial_state)
+        ctx.scale, ctx.disable_recompute, ctx.use_qk_l2norm_in_kernel = scale, disable_recompute, use_qk_l2norm_in_kernel
+        return f["o"].type_as(q), f["final_state"]
+
+    @staticmethod
+    def backward(ctx, do, dht):
+        (q, q_rstd, k, k_rstd, v, g_cumsum, g_input, b, w, Aqk, Akk, w_wy, u_wy, qg, kg, v_new, h,
+         initial_state) = ctx.saved_tensors
+        fuse_cast = not ctx.use_qk_l2norm_in_kernel
+        dq, dk, dv, db, dw, dg, dh0, _, _ = _bwd.gdn2_backward(
+            q=q, k=k, v=v, b=b, w_gate=w, Aqk=Aqk, Akk=Akk, scale=ctx.scale, initial_state=initial_state, do=do,
+            dht=dht, g=g_cumsum, w_wy=w_wy, u_wy=u_wy, qg=qg, kg=kg, v_new=v_new, h=h,
+            disable_recompute=ctx.disable_recompute, out_dtype=torch.bfloat16 if fuse_cast else torch.float32)
+        if ctx.use_qk_l2norm_in_kernel:
+            dq = _l2norm_bwd(q, q_rstd, dq)
+            dk = _l2norm_bwd(k, k_rstd, dk)
+        return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg.to(g_input.dtype), db.to(b.dtype), dw.to(w.dtype),
+                None, dh0, None, None, None)
+
+
+class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
+                use_beta_sigmoid_in_kernel, allow_neg_eigval):
+        q_rstd = k_rstd = None
+        if use_qk_l2norm_in_kernel:
+            q, q_rstd = _l2norm_fwd(q)
+            k, k_rstd = _l2norm_fwd(k)
+        beta_raw = beta
+        if use_beta_sigmoid_in_kernel:
+            beta = (torch.sigmoid(beta_raw.float()) * (2.0 if allow_neg_eigval else 1.0)).to(beta_raw.dtype)
+        f = chunk_forward("gdn", q, k, v, g=g, beta=beta, scale=scale, initial_state=initial_state,
+                          output_final_state=output_final_state)
+        ctx.save_for_backward(q, q_rstd, k, k_rstd, v, f["g_cumsum"], g, beta_raw, beta, f["Akk"], initial_state)
+        ctx.scale, ctx.use_qk_l2norm_in_kernel = scale, use_qk_l2norm_in_kernel
+        ctx.use_beta_sigmoid_in_kernel, ctx.allow_neg_eigval = use_beta_sigmoid_in_kernel, allow_neg_eigval
+        return f["o"].to(q.dtype), f["final_state"]
+
+    @staticmethod
+    def backward(ctx, do, dht):
+        q, q_rstd, k, k_rstd, v, g, g_input, beta_raw, beta, A, initial_state = ctx.saved_tensors
+        fuse_cast = not ctx.use_qk_l2norm_in_kernel
+        dq, dk, dv, db, dg, dh0, _, _ = _bwd.gdn_backward(
+            q=q, k=k, v=v, g=g, beta=beta, A=A, scale=ctx.scale, initial_state=initial_state, do=do, dht=dht,
+            out_dtype=torch.bfloat16 if fuse_cast else torch.float32)
+        if ctx.use_qk_l2norm_in_kernel:
+            dq = _l2norm_bwd(q, q_rstd, dq)
+            dk = _l2norm_bwd(k, k_rstd, dk)
+        if ctx.use_beta_sigmoid_in_kernel:
+            db = _sigmoid_bwd(beta_raw, db, 2.0 if ctx.allow_neg_eigval else 1.0)
+        return (dq.to(q), dk.to(k), dv.to(v), dg.to(g_input), db.to(beta_raw), None, dh0, None, None, None, None)
+
+
+class ChunkDeltaRuleFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, beta, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel):
+        q_rstd = k_rstd = None
+        if use_qk_l2norm_in_kernel:
+            q, q_rstd = _l2norm_fwd(q)
+            k, k_rstd = _l2norm_fwd(k)
+        f = chunk_forward("delta", q, k, v, beta=beta, scale=scale, initial_state=initial_state,
+                          output_final_state=output_final_state)
+        ctx.save_for_backward(q, q_rstd, k, k_rstd, v, beta, f["Akk"], initial_state)
+        ctx.scale, ctx.use_qk_l2norm_in_kernel = scale, use_qk_l2norm_in_kernel
+        return f["o"].to(q.dtype), f["final_state"]
+
+    @staticmethod
+    def backward(ctx, do, dht):
+        q, q_rstd, k, k_rstd, v, beta, A, initial_state = ctx.saved_tensors
+        fuse_cast = not ctx.use_qk_l2norm_in_kernel
+        dq, dk, dv, db, dh0 = _bwd.delta_backward(
+            q=q, k=k, v=v, beta=beta, A=A, scale=ctx.scale, initial_state=initial_state, do=do, dht=dht,
+            out_dtype=torch.bfloat16 if fuse_cast else torch.float32)
+        if ctx.use_qk_l2norm_in_kernel:
+            dq = _l2norm_bwd(q, q_rstd, dq)
+            dk = _l2norm_bwd(k, k_rstd, dk)
+        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), db.to(beta.dtype), None, dh0, None, None
+
+
+def _common_checks(q, k, v, initial_state):
+    if q.shape != k.shape:
+        raise ValueError(f"q and k must have the same shape, got q={tuple(q.shape)} vs k={tuple(k.shape)}")
+    if initial_state is not None and initial_state.dtype != torch.float32:
+        raise ValueError("initial_state must be in float32.")
+
+
+@torch.compiler.disable
+def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
+              use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False, use_beta_sigmoid_in_kernel=False,
+              allow_neg_eigval=False, safe_gate=False, lower_bound=None, disable_recompute=False,
+              return_intermediate_states=False, state_v_first=False, cu_seqlens=None, cu_seqlens_cpu=None,
+              cp_context=None, use_graph=False, max_num_seqs=None, **kwargs):
+    """KDA (per-channel gated delta rule).  q,k [B,T,H,128] BF16, v [B,T,H,128], g [B,T,H,128] per-step
+    natural-log decay, beta [B,T,H].  Returns (o, final_state)."""
+    _common_checks(q, k, v, initial_state)
+    if allow_neg_eigval and not use_beta_sigmoid_in_kernel:
+        raise ValueError("`allow_neg_eigval=True` requires `use_beta_sigmoid_in_kernel=True`.")
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
+    return ChunkKDAFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
+                                  use_beta_sigmoid_in_kernel, allow_neg_eigval, disable_recompute)
+
+
+@torch.compiler.disable
+def chunk_gdn2(q, k, v, g, b, w, scale=None, initial_state=None, output_final_state=False,
+               use_qk_l2norm_in_kernel=False, use_gate_in_kernel=False, cu_seqlens=None, cu_seqlens_cpu=None,
+               safe_gate=False, lower_bound=None, disable_recompute=False, return_intermediate_states=False,
+               state_v_first=False, cp_context=None, **kwargs):
+    """GDN2 (vector erase gate b [B,T,H,128], vector write gate w [B,T,H,128]).  Returns (o, final_state)."""
+    _common_checks(q, k, v, initial_state)
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
+    return ChunkGDN2Function.apply(q, k, v, g, b, w, scale, initial_state, output_final_state,
+                                   use_qk_l2norm_in_kernel, disable_recompute)
+
+
+@torch.compiler.disable
+def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
+                           use_qk_l2norm_in_kernel=False, use_beta_sigmoid_in_kernel=False, allow_neg_eigval=False,
+                           state_v_first=False, cu_seqlens=None, cu_seqlens_cpu=None, chunk_indices=None,
+                           cp_context=None, **kwargs):
+    """Gated DeltaNet (scalar per-head gate g [B,T,H]).  Returns (o, final_state)."""
+    _common_checks(q, k, v, initial_state)
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
+    return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state,
+                                             use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel, allow_neg_eigval)
+
+
+@torch.compiler.disable
+def chunk_delta_rule(q, k, v, beta, scale=None, initial_state=None, output_final_state=False,
+                     use_qk_l2norm_in_kernel=False, cu_seqlens=None, cu_seqlens_cpu=None, **kwargs):
+    """DeltaNet (ungated delta rule).  Returns (o, final_state)."""
+    _common_checks(q, k, v, initial_state)
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
+    return ChunkDeltaRuleFunction.apply(q, k, v, beta, scale, initial_state, output_final_state,
+                                        use_qk_l2norm_in_kernel)

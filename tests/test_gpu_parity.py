@@ -1,0 +1,338 @@
+"""GPU parity tests: every CUDA stage and the whole-family backward, called through the C ABI, against
+the FP64 CPU oracle on the same seeded inputs.
+
+Tolerances (normalised RMSE = ||got-ref||/||ref||):
+  2e-3  for every gradient of the whole-family backward against the FP64 closed-form backward fed with the
+        same (BF16) saved tensors — the bound the operator is specified to;
+  8e-3 / 2e-2 (gate, beta and vector-gate gradients) for the public autograd path against the FP64 token
+        recurrence on the raw inputs — the reference's own acceptance limits
+        (src/fast_delta_rule/validation.py:68-71).
+"""
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import (base_args, call_stage, forward_saved, nrmse, oracle_backward, stage_buffers)
+from rewy_b200 import _capi
+from rewy_b200.synthetic import make_inputs, operator_inputs
+
+pytestmark = pytest.mark.gpu
+
+OPS = ("kda", "gdn2", "gdn", "delta")
+DEV = "cuda:0"
+TOL = 2e-3
+
+
+def _inputs(op, B=1, T=256, H=2, seed=42, **kw):
+    kw.setdefault("gate_scale", 0.1 if op != "gdn" else 1.0)
+    kw.setdefault("gate", "softplus" if op != "gdn" else "head_exp")
+    return make_inputs(op, B, T, H, seed=seed, device=DEV, **kw)
+
+
+def _report(errs, tol):
+    bad = {n: e for n, e in errs.items() if not (e <= (tol[n] if isinstance(tol, dict) else tol))}
+    assert not bad, f"NRMSE above tolerance: {bad}; all: {errs}"
+
+
+@pytest.mark.parametrize("op", OPS)
+def test_stage_prepare(op):
+    xs = _inputs(op)
+    saved = forward_saved(op, xs)
+    a, keep = base_args(op, xs, saved)
+    B, T, H, _ = xs["k"].shape
+    mk = lambda d: torch.full((B, T, H, d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    w, u, qg, kg, aqk = mk(128), mk(128), mk(128), mk(128), mk(64)
+    call_stage("rewy_stage_prepare", a, stage_buffers(w=w, u=u, qg=qg, kg=kg, Aqk=aqk), DEV)
+    errs = dict(w=nrmse(saved["w"], w), u=nrmse(saved["u"], u), qg=nrmse(saved["qg"], qg), kg=nrmse(saved["kg"], kg))
+    if op in ("gdn", "delta"):
+        errs["Aqk"] = nrmse(saved["Aqk"], aqk)
+    _report(errs, 4e-3)   # both sides round to BF16; identical up to accumulation order
+
+
+@pytest.mark.parametrize("op", OPS)
+def test_stage_forward_scan(op):
+    xs = _inputs(op)
+    saved = forward_saved(op, xs)
+    a, keep = base_args(op, xs, saved)
+    h = torch.full_like(saved["h"], float("nan"))
+    v_new = torch.full_like(saved["v_new"], float("nan"))
+    call_stage("rewy_stage_fwd_scan", a, stage_buffers(w=saved["w"], u=saved["u"], kg=saved["kg"], h=h, v_new=v_new), DEV)
+    _report(dict(h=nrmse(saved["h"], h), v_new=nrmse(saved["v_new"], v_new)), 4e-3)
+
+
+@pytest.mark.parametrize("op", OPS)
+def test_stage_reverse_scan(op):
+    xs = _inputs(op)
+    saved = forward_saved(op, xs)
+    ref = oracle_backward(op, xs, saved)
+    a, keep = base_args(op, xs, saved)
+    dh = torch.full_like(saved["h"], float("nan"))
+    dR = torch.full_like(saved["v_new"], float("nan"))
+    dh0 = torch.full((xs["k"].shape[0], xs["k"].shape[2], 128, 128), float("nan"), device=DEV)
+    a.dh0 = _capi.ptr(dh0)
+    call_stage("rewy_stage_bwd_scan", a,
+               stage_buffers(qg=saved["qg"], kg=saved["kg"], w=saved["w"], Aqk=saved["Aqk"], dh=dh, dR=dR), DEV)
+    _report(dict(dh=nrmse(ref["dh"], dh), dR=nrmse(ref["dR"], dR), dh0=nrmse(ref["dh0"], dh0)), TOL)
+
+
+def _run_chunk_adjoint(op, xs, saved, dh, dR, out_f32=True, passes=0):
+    a, keep = base_args(op, xs, saved, _capi.OUT_F32 if out_f32 else _capi.OUT_BF16, passes)
+    B, T, H, _ = xs["k"].shape
+    odt = torch.float32 if out_f32 else torch.bfloat16
+    nan = lambda shape, dt: torch.full(shape, float("nan"), dtype=dt, device=DEV)
+    out = dict(dq=nan((B, T, H, 128), odt), dk=nan((B, T, H, 128), odt), dv=nan((B, T, H, 128), torch.bfloat16))
+    if op != "delta":
+        out["dg"] = nan(tuple(saved["g_cumsum"].shape), torch.float32)
+    if op == "gdn2":
+        out["db_gate"], out["dw_gate"] = nan((B, T, H, 128), odt), nan((B, T, H, 128), odt)
+    else:
+        out["dbeta"] = nan((B, T, H), torch.float32)
+    for n, t in out.items():
+        setattr(a, n, _capi.ptr(t))
+    call_stage("rewy_stage_chunk_adjoint", a, stage_buffers(v_new=saved["v_new"], h=saved["h"], dh=dh, dR=dR), DEV)
+    return out
+
+
+def _grad_errs(op, ref, out):
+    errs = dict(dq=nrmse(ref["dq"], out["dq"]), dk=nrmse(ref["dk"], out["dk"]), dv=nrmse(ref["dv"], out["dv"]))
+    if op != "delta":
+        errs["dg"] = nrmse(ref["dg"], out["dg"])
+    if op == "gdn2":
+        errs["db"], errs["dw"] = nrmse(ref["db"], out["db_gate"]), nrmse(ref["dw"], out["dw_gate"])
+    else:
+        errs["dbeta"] = nrmse(ref["dbeta"], out["dbeta"])
+    return errs
+
+
+@pytest.mark.parametrize("op", OPS)
+def test_stage_chunk_adjoint(op):
+    xs = _inputs(op)
+    saved = forward_saved(op, xs)
+    ref = oracle_backward(op, xs, saved)
+    dh = ref["dh"].to(torch.bfloat16).to(DEV)
+    dR = ref["dR"].to(torch.bfloat16).to(DEV)
+    out = _run_chunk_adjoint(op, xs, saved, dh, dR)
+    _report(_grad_errs(op, ref, out), TOL)
+
+
+def _family_call(op, xs, saved, policy_saved, out_dtype=torch.float32, passes=None):
+    from rewy_b200 import backward as bw
+    common = dict(q=xs["q"], k=xs["k"], v=xs["v"], scale=128 ** -0.5, initial_state=xs.get("initial_state"),
+                  do=xs["do"], dht=xs.get("dht"), out_dtype=out_dtype, intra_passes=passes)
+    if op == "kda":
+        r = bw.kda_backward(beta=xs["beta"], Aqk=saved["Aqk"], Akk=saved["Akk"], g=saved["g_cumsum"],
+                            disable_recompute=policy_saved, w=saved["w"], u=saved["u"], qg=saved["qg"], kg=saved["kg"],
+                            v_new=saved["v_new"], h=saved["h"], **common)
+        return dict(dq=r[0], dk=r[1], dv=r[2], dbeta=r[3], dg=r[4], dh0=r[5])
+    if op == "gdn2":
+        r = bw.gdn2_backward(b=xs["b"], w_gate=xs["w"], Aqk=saved["Aqk"], Akk=saved["Akk"], g=saved["g_cumsum"],
+                             disable_recompute=policy_saved, w_wy=saved["w"], u_wy=saved["u"], qg=saved["qg"],
+                             kg=saved["kg"], v_new=saved["v_new"], h=saved["h"], **common)
+        return dict(dq=r[0], dk=r[1], dv=r[2], db_gate=r[3], dw_gate=r[4], dg=r[5], dh0=r[6])
+    if op == "gdn":
+        r = bw.gdn_backward(g=saved["g_cumsum"], beta=xs["beta"], A=saved["Akk"], **common)
+        return dict(dq=r[0], dk=r[1], dv=r[2], dbeta=r[3], dg=r[4], dh0=r[5])
+    r = bw.delta_backward(beta=xs["beta"], A=saved["Akk"], **common)
+    return dict(dq=r[0], dk=r[1], dv=r[2], dbeta=r[3], dh0=r[4])
+
+
+@pytest.mark.parametrize("op,policy_saved", [("kda", True), ("kda", False), ("gdn2", True), ("gdn2", False),
+                                             ("gdn", False), ("delta", False)])
+def test_family_backward_matches_oracle(op, policy_saved):
+    xs = _inputs(op, B=2, T=256, H=2, seed=7)
+    saved = forward_saved(op, xs)
+    ref = oracle_backward(op, xs, saved)
+    out = _family_call(op, xs, saved, policy_saved)
+    torch.cuda.synchronize()
+    errs = _grad_errs(op, ref, out)
+    errs["dh0"] = nrmse(ref["dh0"], out["dh0"])
+    _report(errs, TOL)
+
+
+@pytest.mark.parametrize("op", OPS)
+def test_family_backward_bf16_outputs_and_no_states(op):
+    """dq/dk written directly in BF16; no initial state, no final-state gradient."""
+    xs = _inputs(op, T=128, H=1, seed=11, state=False)
+    saved = forward_saved(op, xs)
+    ref = oracle_backward(op, xs, saved)
+    out = _family_call(op, xs, saved, op in ("kda", "gdn2"), out_dtype=torch.bfloat16)
+    assert out["dh0"] is None and out["dq"].dtype == torch.bfloat16
+    _report(_grad_errs(op, ref, out), 4e-3)   # includes the final BF16 rounding of dq, dk
+
+
+@pytest.mark.parametrize("case", ["zero_beta", "tiny_beta", "beta_over_one", "strong_gate", "weak_gate", "zero_gate",
+                                  "mixed_tiles", "nonmonotonic_gate", "positive_gate", "dht_only", "h0_only"])
+def test_kda_edge_cases(case):
+    """The reference's named KDA acceptance grid (research/operators/gpu_matrix_20261024/run.py:52-78)."""
+    state, grad_state = True, True
+    if case == "dht_only":
+        state = False
+    if case == "h0_only":
+        grad_state = False
+    xs = _inputs("kda", T=192, H=2, seed=123, state=state, grad_state=grad_state)
+    if case == "zero_beta":
+        xs["beta"][:, ::3] = 0
+    elif case == "tiny_beta":
+        xs["beta"] = (xs["beta"].float() * 1e-8).to(torch.bfloat16)
+    elif case == "beta_over_one":
+        xs["beta"] = (xs["beta"].float() * 2).to(torch.bfloat16)
+    elif case == "strong_gate":
+        xs["g"] = xs["g"] * 20          # ~ -1.5 nat per step: spans far above 80 log2 units per chunk
+    elif case == "weak_gate":
+        xs["g"] = xs["g"] / 100
+    elif case == "zero_gate":
+        xs["g"] = torch.zeros_like(xs["g"])
+    elif case == "mixed_tiles":
+        xs["g"][:, 64:128, 0, :32] *= 30  # one chunk/head takes the pairwise path next to centred ones
+    elif case == "nonmonotonic_gate":
+        xs["g"] = xs["g"] * torch.where(torch.rand_like(xs["g"]) < 0.3, -1.0, 1.0)
+    elif case == "positive_gate":
+        xs["g"] = -xs["g"] * 0.2
+    saved = forward_saved("kda", xs)
+    ref = oracle_backward("kda", xs, saved)
+    out = _family_call("kda", xs, saved, True)
+    errs = _grad_errs("kda", ref, out)
+    if state:
+        errs["dh0"] = nrmse(ref["dh0"], out["dh0"])
+    for n, t in out.items():
+        if t is not None:
+            assert torch.isfinite(t.float()).all(), f"{n} not finite"
+    _report(errs, 4e-3 if case in ("strong_gate", "mixed_tiles") else TOL)
+
+
+@pytest.mark.parametrize("op", ("gdn2", "gdn"))
+def test_strong_gate_pairwise_path(op):
+    xs = _inputs(op, T=128, H=2, seed=5)
+    xs["g"] = xs["g"] * (25 if op == "gdn2" else 3)
+    saved = forward_saved(op, xs)
+    ref = oracle_backward(op, xs, saved)
+    out = _family_call(op, xs, saved, op == "gdn2")
+    errs = _grad_errs(op, ref, out)
+    _report(errs, 4e-3)
+
+
+def test_single_pass_intra_is_selectable_and_close():
+    xs = _inputs("kda", T=128, H=2, seed=3)
+    saved = forward_saved("kda", xs)
+    ref = oracle_backward("kda", xs, saved)
+    out1 = _family_call("kda", xs, saved, True, passes=1)
+    out3 = _family_call("kda", xs, saved, True, passes=3)
+    e1, e3 = _grad_errs("kda", ref, out1), _grad_errs("kda", ref, out3)
+    _report(e3, TOL)
+    _report(e1, 6e-3)
+
+
+@pytest.mark.parametrize("family", ("kda", "gdn2"))
+@pytest.mark.parametrize("scale", (1.0, 3.0))
+def test_matrix_intra_on_reference_captured_inputs(golden_dir, family, scale):
+    """The reference's captured matrix-intra inputs (validation/npu950_intra) pushed through the chunk
+    kernel: Akk = I, dR = -dAkk (as P), v_new = unit rows and dO = dAqk/scale make the kernel's internal
+    dAqk/dAkk equal the captured ones (up to BF16 rounding of those operands); h = dh = 0 removes every
+    other term.  Limits are the reference's 0.008 / 0.02 (scripts/npu950_intra_regression.py:59-72)."""
+    with np.load(golden_dir / f"intra_{family}_inputs.npz") as z:
+        x = {n: torch.from_numpy(z[n].copy()) for n in z.files}
+    with np.load(golden_dir / f"intra_{family}_expected.npz") as z:
+        exp = {n: torch.from_numpy(z[f"scale{scale:g}_{n}"]) for n in ("dq", "dk", "db", "dg")}
+    B, C, H, K = x["q"].shape
+    sc = 128 ** -0.5
+    L = torch.tril(x["dAqk"].permute(0, 2, 1, 3)).permute(0, 2, 1, 3)          # [B,C,H,C] rows i, cols j
+    D = torch.tril(x["dAkk"].permute(0, 2, 1, 3), -1).permute(0, 2, 1, 3)
+    z128 = lambda: torch.zeros(B, C, H, 128)
+    dO, P, R = z128(), z128(), z128()
+    dO[..., :C] = L / sc
+    P[..., :C] = -D
+    R[..., :C] = torch.eye(C)[None, :, None, :]
+    eye = torch.eye(C)[None, :, None, :].expand(B, C, H, C)
+    bf = lambda t: t.to(torch.bfloat16).to(DEV).contiguous()
+    xs = dict(q=bf(x["q"]), k=bf(x["k"]), v=bf(z128()), do=bf(dO))
+    if family == "kda":
+        xs["beta"] = x["beta"].to(DEV)
+    else:
+        xs["b"], xs["w"] = bf(x["b"]), bf(z128())
+    saved = dict(g_cumsum=(x["g"] * scale).to(DEV).contiguous(), Akk=bf(eye), v_new=bf(R),
+                 h=torch.zeros(B, 1, H, 128, 128, dtype=torch.bfloat16, device=DEV))
+    out = _run_chunk_adjoint(family, xs, saved, torch.zeros_like(saved["h"]), bf(P))
+    # expected intra contribution = reference oracle output minus the partials it started from, with the
+    # L/D operands as the kernel sees them (BF16-rounded) accounted for by the tolerance
+    want = {n: exp[n].double() - x[n].double() for n in exp}
+    want["dg"] = want["dg"].flip(1).cumsum(1).flip(1)   # the kernel also applies the reverse chunk cumsum
+    got = dict(dq=out["dq"], dk=out["dk"], dg=out["dg"], db=out["dbeta"] if family == "kda" else out["db_gate"])
+    errs = {n: nrmse(want[n], got[n]) for n in want}
+    _report(errs, dict(dq=0.008, dk=0.008, db=0.02, dg=0.02))
+
+
+@pytest.mark.parametrize("op", OPS)
+def test_public_autograd_path_against_recurrence(op):
+    """Public API end to end, like the reference's ``verify`` (validation.py:47-76): forward under
+    use_backend('optimized'), backward after leaving the context, FP64 token recurrence as the oracle."""
+    import rewy_b200 as fdr
+    from oracle import recurrence_grads
+    xs = _inputs(op, T=128, H=2, seed=42, gate_scale=0.05, gate="softplus")
+    ins = {n: (x.detach().clone().requires_grad_() if x is not None else None) for n, x in operator_inputs(op, xs).items()}
+    fdr.stats(reset=True)
+    policies = (False, True) if op in ("kda", "gdn2") else (False,)
+    ref, o_ref, fin_ref = recurrence_grads(op, {n: (x.detach().cpu() if x is not None else None) for n, x in ins.items()},
+                                           xs["do"].cpu(), xs["dht"].cpu())
+    for saved_policy in policies:
+        kw = dict(ins, output_final_state=True)
+        if op in ("kda", "gdn2"):
+            kw["disable_recompute"] = saved_policy
+        with fdr.use_backend("optimized", ops=(op,)):
+            o, fin = getattr(fdr, {"kda": "chunk_kda", "gdn2": "chunk_gdn2", "gdn": "chunk_gated_delta_rule",
+                                   "delta": "chunk_delta_rule"}[op])(**kw)
+        leaves = [x for x in ins.values() if x is not None]
+        grads = torch.autograd.grad((o, fin), leaves, (xs["do"], xs["dht"]))
+        names = [n for n, x in ins.items() if x is not None]
+        errs = {n: nrmse(ref[n], g) for n, g in zip(names, grads)}
+        errs["o"] = nrmse(o_ref, o)
+        errs["final_state"] = nrmse(fin_ref, fin)
+        tol = {n: (0.02 if n in ("g", "beta", "b", "w") else 0.008) for n in errs}
+        _report(errs, tol)
+    fdr.assert_used((op,))
+    assert fdr.stats()[f"{op}.optimized_backward"] == len(policies)
+
+
+def test_rejections_and_error_codes():
+    import rewy_b200 as fdr
+    xs = _inputs("kda", T=128, H=1)
+    with fdr.use_backend("optimized"):
+        with pytest.raises(RuntimeError, match="multiple of 64"):
+            fdr.chunk_kda(xs["q"][:, :65], xs["k"][:, :65], xs["v"][:, :65], xs["g"][:, :65], xs["beta"][:, :65])
+    saved = forward_saved("kda", xs)
+    a, keep = base_args("kda", xs, saved)
+    lib = _capi.load()
+    assert lib.rewy_kda_bwd(a, None) == 1 and b"NULL" in lib.rewy_last_error()     # outputs missing
+    a.T = 100
+    assert lib.rewy_kda_bwd(a, None) == 2                                           # bad shape
+
+
+def test_full_size_headline_properties():
+    """BASELINE headline shape (KDA B=8,T=8192,H=32) through size-independent properties:
+    linearity of the backward in (dO, dht) and equality of one (batch, head) slice with the FP64 oracle run
+    on that slice alone (the path is independent across batch and head)."""
+    from rewy_b200.forward import chunk_forward
+    B, T, H = 8, 8192, 32
+    dev = torch.device(DEV)
+    g = torch.Generator(device=dev); g.manual_seed(1)
+    rn = lambda *s: torch.randn(*s, generator=g, device=dev)
+    q = torch.nn.functional.normalize(rn(B, T, H, 128), dim=-1).to(torch.bfloat16)
+    k = torch.nn.functional.normalize(rn(B, T, H, 128), dim=-1).to(torch.bfloat16)
+    v = rn(B, T, H, 128).to(torch.bfloat16)
+    gate = -torch.nn.functional.softplus(rn(B, T, H, 128)) * 0.1
+    beta = torch.sigmoid(rn(B, T, H)).to(torch.bfloat16)
+    do = rn(B, T, H, 128).to(torch.bfloat16)
+    xs = dict(q=q, k=k, v=v, g=gate, beta=beta, do=do, initial_state=None, dht=None)
+    saved = chunk_forward("kda", q, k, v, g=gate, beta=beta)
+    out = _family_call("kda", xs, saved, True)
+    xs2 = dict(xs, do=(do.float() * 2).to(torch.bfloat16))
+    out2 = _family_call("kda", xs2, saved, True)
+    for n in ("dq", "dk", "dv", "dg", "dbeta"):
+        assert nrmse(out[n].float() * 2, out2[n]) < 5e-3, n
+    b0, h0 = 5, 17
+    sl = lambda t: None if t is None else t[b0:b0 + 1, :, h0:h0 + 1].contiguous()
+    xs_s = {n: sl(t) for n, t in xs.items()}
+    saved_s = {n: (sl(t) if n != "h" else t[b0:b0 + 1, :, h0:h0 + 1].contiguous()) for n, t in saved.items()
+               if t is not None and n not in ("o", "final_state")}
+    ref = oracle_backward("kda", xs_s, saved_s)
+    got = {n: sl(t) for n, t in out.items() if t is not None}
+    _report(_grad_errs("kda", ref, got), TOL)

@@ -1,0 +1,154 @@
+"""CPU tests of the host layer: selection, dispatch report, rejection envelope, C-ABI exports.
+Mirrors the reference's control-plane tests (tests/test_runtime.py:6-33)."""
+import ctypes
+import re
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_import_has_no_side_effects():
+    code = ("import sys; import rewy_b200; "
+            "assert 'torch' not in sys.modules and 'fla' not in sys.modules and 'ctypes' not in sys.modules; print('ok')")
+    r = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
+def test_nested_use_backend_restores_on_exception():
+    from rewy_b200 import runtime, use_backend
+    assert runtime.selection().backend == "original"
+    with use_backend("optimized", ops=("kda",)):
+        assert runtime.selection().ops == ("kda",)
+        with pytest.raises(ZeroDivisionError):
+            with use_backend("original"):
+                assert runtime.selection().backend == "original"
+                1 / 0
+        assert runtime.selection().backend == "optimized"
+    assert runtime.selection().backend == "original"
+
+
+def test_unknown_backend_and_operator_rejected():
+    from rewy_b200 import runtime
+    with pytest.raises(ValueError):
+        runtime.configure("fastest")
+    with pytest.raises(ValueError):
+        runtime.configure("optimized", ops=("kda", "mamba"))
+    with pytest.raises(ValueError):
+        runtime.operator("mamba")
+
+
+def test_assert_used_reports_missing_backward():
+    import rewy_b200 as fdr
+    fdr.stats(reset=True)
+    with pytest.raises(RuntimeError, match="No optimized_backward calls"):
+        fdr.assert_used(("kda",))
+    fdr.runtime.record("kda", "optimized_backward")
+    fdr.assert_used(("kda",))
+    assert fdr.stats(reset=True) == {"kda.optimized_backward": 1}
+    rep = fdr.dispatch_report()
+    assert set(rep) == {"backend", "counts", "count_boundary"}
+
+
+@pytest.mark.parametrize("mutate,reason", [
+    (lambda a: a.update(q=a["q"].float()), "BF16"),
+    (lambda a: a.update(q=a["q"][:, :65], k=a["k"][:, :65], v=a["v"][:, :65]), "multiple of 64"),
+    (lambda a: a.update(chunk_size=32), "chunk_size=64"),
+    (lambda a: a.update(cu_seqlens=torch.tensor([0, 128])), "packed/variable"),
+    (lambda a: a.update(scale=0.5), "custom scale"),
+    (lambda a: a.update(safe_gate=True), "safe_gate"),
+    (lambda a: a.update(use_gate_in_kernel=True), "fused gate"),
+    (lambda a: a.update(v=a["v"][..., :64]), "K=V=128"),
+])
+def test_rejection_envelope(mutate, reason):
+    from rewy_b200.runtime import rejection_reason
+    t = torch.zeros(1, 128, 2, 128, dtype=torch.bfloat16)
+    args = dict(q=t, k=t, v=t)
+    assert rejection_reason("kda", args, device_types=("cpu",)) is None
+    mutate(args)
+    got = rejection_reason("kda", args, device_types=("cpu",))
+    assert got is not None and reason in got, got
+
+
+def test_rejection_on_cpu_tensors_is_device():
+    from rewy_b200.runtime import rejection_reason
+    t = torch.zeros(1, 128, 2, 128, dtype=torch.bfloat16)
+    assert rejection_reason("kda", dict(q=t, k=t, v=t)) == "CUDA required"
+    assert rejection_reason("kda", dict(q=t[0], k=t, v=t)) == "expected rank-4 q/k/v"
+
+
+def test_strict_rejection_raises_and_counts():
+    import rewy_b200 as fdr
+    fdr.stats(reset=True)
+    t = torch.zeros(1, 128, 2, 128, dtype=torch.bfloat16)
+    with fdr.use_backend("optimized"):
+        with pytest.raises(RuntimeError, match="rewy_b200 kda: CUDA required"):
+            fdr.chunk_kda(t, t, t, torch.zeros(1, 128, 2, 128), torch.zeros(1, 128, 2))
+    assert fdr.stats(reset=True) == {"kda.rejected:CUDA required": 1}
+
+
+def test_backward_functions_refuse_cpu_tensors():
+    from rewy_b200 import backward
+    t = torch.zeros(1, 128, 2, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        backward.delta_backward(t, t, t, torch.zeros(1, 128, 2), torch.zeros(1, 128, 2, 64), 1.0, None, t, None)
+
+
+def test_shared_library_exports_every_declared_symbol():
+    """Every function declared in include/rewy_b200.h is exported by the built library."""
+    from rewy_b200 import _capi
+    header = (ROOT / "include" / "rewy_b200.h").read_text()
+    declared = set(re.findall(r"^\s*(?:const\s+char\*|int|size_t)\s+(rewy_\w+)\s*\(", header, re.M))
+    assert declared == set(_capi.EXPORTS), declared ^ set(_capi.EXPORTS)
+    lib = ctypes.CDLL(str(_capi.library_path()))
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert b"sm_100a" in _capi.load().rewy_version()
+
+
+def test_struct_layout_matches_header_field_order():
+    from rewy_b200 import _capi
+    header = (ROOT / "include" / "rewy_b200.h").read_text()
+    body = header[header.index("typedef struct RewyBwdArgs {"):header.index("} RewyBwdArgs;")]
+    fields = re.findall(r"^\s*(?:const\s+)?(?:void|float|int32_t|size_t)\s*\*?\s*([\w, ]+);", body, re.M)
+    names = [n.strip() for f in fields for n in f.split(",")]
+    assert names == [n for n, _ in _capi.BwdArgs._fields_]
+    body = header[header.index("typedef struct RewyStageBuffers {"):header.index("} RewyStageBuffers;")]
+    names = re.findall(r"^\s*void\*\s+(\w+);", body, re.M)
+    assert names == [n for n, _ in _capi.StageBuffers._fields_]
+
+
+def test_argument_validation_without_a_gpu():
+    """Status codes for bad arguments are produced before any CUDA call."""
+    from rewy_b200 import _capi
+    lib = _capi.load()
+    a = _capi.BwdArgs()
+    a.family, a.B, a.T, a.H = _capi.KDA, 1, 100, 1
+    assert lib.rewy_kda_bwd(a, None) == 2 and b"multiple of 64" in lib.rewy_last_error()
+    a.T = 128
+    assert lib.rewy_kda_bwd(a, None) == 1 and b"'q'" in lib.rewy_last_error()
+    assert lib.rewy_gdn_bwd(a, None) == 7
+    assert lib.rewy_bwd_workspace_bytes(_capi.KDA, _capi.SAVED, 1, 128, 1) == 128 * (512 + 256)
+    assert lib.rewy_bwd_workspace_bytes(_capi.GDN, _capi.RECOMPUTE, 1, 128, 1) == 128 * (512 + 256 + 5 * 256 + 512 + 128)
+
+
+def test_forward_producer_matches_oracle_forward_on_cpu():
+    """The product's torch forward (BF16 operands) against the FP64 chunked forward of the oracle."""
+    from oracle import chunk_forward as oracle_forward
+    from rewy_b200.forward import chunk_forward
+    from rewy_b200.synthetic import make_inputs, operator_inputs
+    for op in ("kda", "gdn", "gdn2", "delta"):
+        xs = make_inputs(op, 1, 128, 2, seed=8)
+        ins = operator_inputs(op, xs)
+        kw = {n: ins[n] for n in ins if n not in ("initial_state",)}
+        got = chunk_forward(op, initial_state=ins["initial_state"], **kw)
+        ref = oracle_forward(op, ins)
+        for n in ("o", "final_state", "Aqk", "Akk", "w", "u", "qg", "kg", "v_new", "h"):
+            err = ((got[n].double() - ref[n]).norm() / ref[n].norm()).item()
+            assert err < 6e-3, (op, n, err)
+        if op != "delta":
+            assert torch.allclose(got["g_cumsum"].double(), ref["g_cumsum"], atol=1e-5)
