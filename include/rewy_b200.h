@@ -95,7 +95,8 @@ typedef struct RewyStageBuffers {
   void* h;      /* bf16 [B,NT,H,128,128] */
   void* Aqk;    /* bf16 [B,T,H,64] */
   void* dh;     /* bf16 [B,NT,H,128,128] */
-  void* dR;     /* bf16 [B,T,H,128] */
+  void* dR;     /* bf16 [B,T,H,128]  high part of dR = kg dh + Aqk^T dO */
+  void* dR_lo;  /* bf16 [B,T,H,128]  low part: bf16(dR - dR_hi); P = Akk^T (dR + dR_lo) keeps dv, dbeta inside 2e-3 */
 } RewyStageBuffers;
 
 /* Whole-family backward.  Replace, one for one, the functions the reference's autograd backwards call:
@@ -129,6 +130,14 @@ int rewy_stage_prepare(const RewyBwdArgs* args, const RewyStageBuffers* buf, rew
 int rewy_stage_fwd_scan(const RewyBwdArgs* args, const RewyStageBuffers* buf, rewy_stream_t stream);
 int rewy_stage_bwd_scan(const RewyBwdArgs* args, const RewyStageBuffers* buf, rewy_stream_t stream);
 int rewy_stage_chunk_adjoint(const RewyBwdArgs* args, const RewyStageBuffers* buf, rewy_stream_t stream);
+
+/* Optional per-stage device timing of the whole-family calls (no counterpart in the reference, which
+ * times stages by re-capturing them: research/operators/a800_ablation/audit.py:38-47).  While enabled, each
+ * whole-family call records CUDA events on its stream around its stage launches (up to 256 calls).
+ * rewy_stage_timing_read sums the elapsed milliseconds per stage {prepare, forward scan, reverse scan,
+ * chunk adjoint} over the recorded calls; the stream must have been synchronised by the caller. */
+int rewy_stage_timing_enable(int enable);
+int rewy_stage_timing_read(float* ms_sum4, int* calls);
 
 /* Diagnostics. */
 const char* rewy_last_error(void);       /* thread-local text of the last non-zero status */

@@ -19,6 +19,7 @@ OUT_BF16, OUT_F32 = 0, 1
 EXPORTS = (
     "rewy_kda_bwd", "rewy_gdn2_bwd", "rewy_gdn_bwd", "rewy_delta_bwd", "rewy_bwd_workspace_bytes",
     "rewy_stage_prepare", "rewy_stage_fwd_scan", "rewy_stage_bwd_scan", "rewy_stage_chunk_adjoint",
+    "rewy_stage_timing_enable", "rewy_stage_timing_read",
     "rewy_last_error", "rewy_version", "rewy_kernel_launch_count",
 )
 
@@ -38,7 +39,7 @@ class BwdArgs(ctypes.Structure):
 
 
 class StageBuffers(ctypes.Structure):
-    _fields_ = [(n, c_void_p) for n in ("w", "u", "qg", "kg", "v_new", "h", "Aqk", "dh", "dR")]
+    _fields_ = [(n, c_void_p) for n in ("w", "u", "qg", "kg", "v_new", "h", "Aqk", "dh", "dR", "dR_lo")]
 
 
 _lib = None
@@ -68,6 +69,10 @@ def load():
         fn.restype = c_int
     lib.rewy_bwd_workspace_bytes.argtypes = [c_int32, c_int32, c_int32, c_int32, c_int32]
     lib.rewy_bwd_workspace_bytes.restype = c_size_t
+    lib.rewy_stage_timing_enable.argtypes = [c_int]
+    lib.rewy_stage_timing_enable.restype = c_int
+    lib.rewy_stage_timing_read.argtypes = [ctypes.POINTER(c_float), ctypes.POINTER(c_int)]
+    lib.rewy_stage_timing_read.restype = c_int
     lib.rewy_last_error.restype = c_char_p
     lib.rewy_version.restype = c_char_p
     lib.rewy_kernel_launch_count.restype = c_int
@@ -92,6 +97,21 @@ def current_stream(device):
 
 def workspace_bytes(family, policy, B, T, H):
     return int(load().rewy_bwd_workspace_bytes(family, policy, B, T, H))
+
+
+STAGE_NAMES = ("prepare", "fwd_scan", "bwd_scan", "chunk_adjoint")
+
+
+def stage_timing_enable(on=True):
+    check(load().rewy_stage_timing_enable(1 if on else 0), "rewy_stage_timing_enable")
+
+
+def stage_timing_read():
+    """Returns ({stage: total ms}, calls) for the whole-family calls recorded since enabling."""
+    ms = (c_float * 4)()
+    calls = c_int(0)
+    check(load().rewy_stage_timing_read(ms, ctypes.byref(calls)), "rewy_stage_timing_read")
+    return {n: float(ms[i]) for i, n in enumerate(STAGE_NAMES)}, int(calls.value)
 
 
 def launch_count():

@@ -21,7 +21,7 @@ size_t align_up(size_t x) { return (x + 255) & ~size_t(255); }
 struct Plan {
   bool prepare;       // rebuild w,u,qg,kg (+ forward scan for v_new,h)
   bool build_aqk;     // scalar families save no Aqk
-  size_t off_dh, off_dR, off_w, off_u, off_qg, off_kg, off_vnew, off_h, off_aqk, total;
+  size_t off_dh, off_dR, off_dRlo, off_w, off_u, off_qg, off_kg, off_vnew, off_h, off_aqk, total;
 };
 
 Plan make_plan(int family, int policy, long long B, long long T, long long H) {
@@ -32,6 +32,7 @@ Plan make_plan(int family, int policy, long long B, long long T, long long H) {
   size_t o = 0;
   p.off_dh = o; o += align_up(n * 512);
   p.off_dR = o; o += align_up(n * 256);
+  p.off_dRlo = o; o += align_up(n * 256);
   if (p.prepare) {
     p.off_w = o; o += align_up(n * 256);
     p.off_u = o; o += align_up(n * 256);
@@ -90,6 +91,24 @@ int validate_common(const RewyBwdArgs* a, int family) {
   return REWY_OK;
 }
 
+// Optional per-stage device timing of the whole-family calls (off by default): a ring of CUDA-event sets,
+// one set per call, recorded on the caller's stream between the stage launches.
+constexpr int TIMING_SETS = 256;
+constexpr int TIMING_STAGES = 4;  // prepare, forward scan, reverse scan, chunk adjoint
+struct Timing {
+  bool enabled = false;
+  int used = 0;
+  cudaEvent_t ev[TIMING_SETS][TIMING_STAGES + 1];
+  bool have[TIMING_SETS][TIMING_STAGES + 1];
+  bool created = false;
+} g_timing;
+
+void timing_mark(int set, int idx, cudaStream_t st) {
+  if (set < 0) return;
+  cudaEventRecord(g_timing.ev[set][idx], st);
+  g_timing.have[set][idx] = true;
+}
+
 int check_cuda(cudaError_t e, const char* stage) {
   if (e == cudaSuccess) return REWY_OK;
   snprintf(g_error, sizeof(g_error), "%s: %s", stage, cudaGetErrorString(e));
@@ -108,6 +127,7 @@ int run_family(const RewyBwdArgs* a, int family, cudaStream_t st) {
   RewyStageBuffers s{};
   s.dh = ws + p.off_dh;
   s.dR = ws + p.off_dR;
+  s.dR_lo = ws + p.off_dRlo;
   if (p.prepare) {
     s.w = ws + p.off_w; s.u = ws + p.off_u; s.qg = ws + p.off_qg; s.kg = ws + p.off_kg;
     s.v_new = ws + p.off_vnew; s.h = ws + p.off_h;
@@ -116,12 +136,22 @@ int run_family(const RewyBwdArgs* a, int family, cudaStream_t st) {
     s.v_new = const_cast<void*>(a->v_new); s.h = const_cast<void*>(a->h);
   }
   s.Aqk = p.build_aqk ? static_cast<void*>(ws + p.off_aqk) : const_cast<void*>(a->Aqk);
+  int set = -1;
+  if (g_timing.enabled && g_timing.used < TIMING_SETS) {
+    set = g_timing.used++;
+    for (int i = 0; i <= TIMING_STAGES; i++) g_timing.have[set][i] = false;
+  }
+  timing_mark(set, 0, st);
   if (p.prepare) {
     if ((rc = check_cuda(launch_prepare(*a, s, st), "prepare")) != REWY_OK) return rc;
+    timing_mark(set, 1, st);
     if ((rc = check_cuda(launch_fwd_scan(*a, s, st), "forward state scan")) != REWY_OK) return rc;
   }
+  timing_mark(set, 2, st);
   if ((rc = check_cuda(launch_bwd_scan(*a, s, st), "reverse state scan")) != REWY_OK) return rc;
+  timing_mark(set, 3, st);
   if ((rc = check_cuda(launch_chunk_adjoint(*a, s, st), "chunk adjoint")) != REWY_OK) return rc;
+  timing_mark(set, 4, st);
   return REWY_OK;
 }
 
@@ -183,7 +213,7 @@ int rewy_stage_bwd_scan(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_st
   int rc = validate_stage(a, s);
   if (rc != REWY_OK) return rc;
   STAGE_PTR(s->qg, "qg"); STAGE_PTR(s->kg, "kg"); STAGE_PTR(s->w, "w"); STAGE_PTR(s->Aqk, "Aqk");
-  STAGE_PTR(a->d_o, "d_o"); STAGE_PTR(s->dh, "dh"); STAGE_PTR(s->dR, "dR");
+  STAGE_PTR(a->d_o, "d_o"); STAGE_PTR(s->dh, "dh"); STAGE_PTR(s->dR, "dR"); STAGE_PTR(s->dR_lo, "dR_lo");
   if (a->family != REWY_DELTA) STAGE_PTR(a->g, "g");
   return check_cuda(launch_bwd_scan(*a, *s, (cudaStream_t)st), "reverse state scan");
 }
@@ -193,6 +223,7 @@ int rewy_stage_chunk_adjoint(const RewyBwdArgs* a, const RewyStageBuffers* s, re
   if (rc != REWY_OK) return rc;
   STAGE_PTR(a->q, "q"); STAGE_PTR(a->k, "k"); STAGE_PTR(a->v, "v"); STAGE_PTR(a->Akk, "Akk"); STAGE_PTR(a->d_o, "d_o");
   STAGE_PTR(s->v_new, "v_new"); STAGE_PTR(s->h, "h"); STAGE_PTR(s->dh, "dh"); STAGE_PTR(s->dR, "dR");
+  STAGE_PTR(s->dR_lo, "dR_lo");
   STAGE_PTR(a->dq, "dq"); STAGE_PTR(a->dk, "dk"); STAGE_PTR(a->dv, "dv");
   if (a->family != REWY_DELTA) { STAGE_PTR(a->g, "g"); STAGE_PTR(a->dg, "dg"); }
   if (a->family == REWY_GDN2) {
@@ -202,6 +233,37 @@ int rewy_stage_chunk_adjoint(const RewyBwdArgs* a, const RewyStageBuffers* s, re
     STAGE_PTR(a->beta, "beta"); STAGE_PTR(a->dbeta, "dbeta");
   }
   return check_cuda(launch_chunk_adjoint(*a, *s, (cudaStream_t)st), "chunk adjoint");
+}
+
+int rewy_stage_timing_enable(int enable) {
+  if (enable && !g_timing.created) {
+    for (int i = 0; i < TIMING_SETS; i++)
+      for (int j = 0; j <= TIMING_STAGES; j++)
+        if (cudaEventCreate(&g_timing.ev[i][j]) != cudaSuccess) return fail(REWY_ERR_LAUNCH, "cudaEventCreate failed%s");
+    g_timing.created = true;
+  }
+  g_timing.enabled = enable != 0;
+  g_timing.used = 0;
+  return REWY_OK;
+}
+
+int rewy_stage_timing_read(float* ms_sum, int* calls) {
+  if (ms_sum == nullptr || calls == nullptr) return fail(REWY_ERR_NULL, "ms_sum or calls is NULL%s");
+  for (int j = 0; j < TIMING_STAGES; j++) ms_sum[j] = 0.f;
+  *calls = g_timing.used;
+  for (int i = 0; i < g_timing.used; i++) {
+    // stage j runs between mark j and the next recorded mark
+    int prev = 0;
+    for (int j = 1; j <= TIMING_STAGES; j++) {
+      if (!g_timing.have[i][j]) continue;
+      float ms = 0.f;
+      cudaError_t e = cudaEventElapsedTime(&ms, g_timing.ev[i][prev], g_timing.ev[i][j]);
+      if (e != cudaSuccess) return check_cuda(e, "stage timing (synchronise the stream first)");
+      ms_sum[j - 1] += ms;
+      prev = j;
+    }
+  }
+  return REWY_OK;
 }
 
 const char* rewy_last_error(void) { return g_error; }

@@ -1,5 +1,5 @@
 // Stage "chunk adjoint": everything of the backward that is local to one 64-token chunk of one head.
-//   P = Akk^T dR;  dv = w*P (dw_gate = v*P);  dAqk = scale*tril(dO R^T);  dAkk = -tril(P R^T, -1)
+//   P = Akk^T (dR + dR_lo);  dv = w*P (dw_gate = v*P);  dAqk = scale*tril(dO R^T);  dAkk = -tril(P R^T, -1)
 //   dq = gamma*scale*(dO h^T) + alpha*(dAqk Yc)
 //   gamma*eb = gamma*(-P h^T) + alpha*(dAkk Yc)
 //   yb/gamma = zeta*(dAqk^T Qc + dAkk^T Ec) + exp2(g_last-g)*(R dh^T)
@@ -25,7 +25,7 @@ constexpr int LDG = 132;  // pitch of the FP32 dg tile
 constexpr float SPAN_LIMIT = 80.f;
 
 struct ChunkParams {
-  const bf16 *q, *k, *v, *bg, *wg, *Akk, *dO, *R, *h, *dh, *dR;
+  const bf16 *q, *k, *v, *bg, *wg, *Akk, *dO, *R, *h, *dh, *dR, *dRlo;
   const float *g, *beta;
   void *dq, *dk, *dbg, *dwg;
   bf16* dv;
@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(256, 1) chunk_adjoint_kernel(const ChunkParams
   float* sG32 = reinterpret_cast<float*>(sDO);             // [64][132] alias of sDO+sR for the cumsum
   bf16* sAkk = sXh;                                        // phase A aliases
   bf16* sDRt = sXl;
+  bf16* sDRlo = sEh;
 
   const int n = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
   const int T = p.T, H = p.H, NT = T / C;
@@ -87,6 +88,7 @@ __global__ void __launch_bounds__(256, 1) chunk_adjoint_kernel(const ChunkParams
   // ---- phase 0: tiles for P, centres, flags ------------------------------------------------
   load_tile_bf16<C, 64>(sAkk, LD64, p.Akk + base64, (size_t)H * 64);
   load_tile_bf16<C, 128>(sDRt, LD128, p.dR + base128, ldt);
+  load_tile_bf16<C, 128>(sDRlo, LD128, p.dRlo + base128, ldt);
   load_tile_bf16<C, 128>(sDO, LD128, p.dO + base128, ldt);
   load_tile_bf16<C, 128>(sR, LD128, p.R + base128, ldt);
   if (tid < C) sRow[tid] = 0.f;
@@ -140,6 +142,7 @@ __global__ void __launch_bounds__(256, 1) chunk_adjoint_kernel(const ChunkParams
     Tile<64, 128, 2, 4> acc;
     acc.zero();
     acc.mma<64>(Operand<true>{sAkk, LD64}, Operand<true>{sDRt, LD128});
+    acc.mma<64>(Operand<true>{sAkk, LD64}, Operand<true>{sDRlo, LD128});
     float part[acc.TM][2];
 #pragma unroll
     for (int i = 0; i < acc.TM; i++) part[i][0] = part[i][1] = 0.f;
@@ -486,7 +489,7 @@ cudaError_t launch_chunk_adjoint(const RewyBwdArgs& a, const RewyStageBuffers& s
   p.q = (const bf16*)a.q; p.k = (const bf16*)a.k; p.v = (const bf16*)a.v;
   p.bg = (const bf16*)a.b_gate; p.wg = (const bf16*)a.w_gate; p.Akk = (const bf16*)a.Akk;
   p.dO = (const bf16*)a.d_o; p.R = (const bf16*)s.v_new; p.h = (const bf16*)s.h; p.dh = (const bf16*)s.dh;
-  p.dR = (const bf16*)s.dR; p.g = a.g; p.beta = a.beta;
+  p.dR = (const bf16*)s.dR; p.dRlo = (const bf16*)s.dR_lo; p.g = a.g; p.beta = a.beta;
   p.dq = a.dq; p.dk = a.dk; p.dbg = a.db_gate; p.dwg = a.dw_gate; p.dv = (bf16*)a.dv; p.dg = a.dg; p.dbeta = a.dbeta;
   p.T = a.T; p.H = a.H; p.out_f32 = a.out_dtype == REWY_OUT_F32; p.passes = a.intra_passes == 1 ? 1 : 3;
   p.scale = a.scale;

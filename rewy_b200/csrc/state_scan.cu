@@ -30,7 +30,7 @@ template <int GATE>
 __global__ void __launch_bounds__(256) bwd_scan_kernel(
     const bf16* __restrict__ qg, const bf16* __restrict__ kg, const bf16* __restrict__ w, const bf16* __restrict__ Aqk,
     const bf16* __restrict__ dO, const float* __restrict__ g, const float* __restrict__ dht, bf16* __restrict__ dh,
-    bf16* __restrict__ dR, float* __restrict__ dh0, int T, int H, float scale) {
+    bf16* __restrict__ dR, bf16* __restrict__ dRlo, float* __restrict__ dh0, int T, int H, float scale) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sQg = reinterpret_cast<bf16*>(smem_raw);
   bf16* sKg = sQg + C * LD128;
@@ -39,7 +39,8 @@ __global__ void __launch_bounds__(256) bwd_scan_kernel(
   bf16* sAqk = sDO + C * LD64;   // [64][72]
   bf16* sDh = sAqk + C * LD64;   // [128][72]
   bf16* sDR = sDh + DK * LD64;   // [64][72]
-  float* sLam = reinterpret_cast<float*>(sDR + C * LD64);
+  bf16* sDRlo = sDR + C * LD64;  // [64][72]
+  float* sLam = reinterpret_cast<float*>(sDRlo + C * LD64);
 
   const int v0 = blockIdx.x * BV, bh = blockIdx.y, b = bh / H, h = bh % H;
   const int NT = T / C;
@@ -77,11 +78,15 @@ __global__ void __launch_bounds__(256) bwd_scan_kernel(
       acc.mma<128>(Operand<false>{sKg, LD128}, Operand<true>{sDh, LD64});
       acc.mma<64>(Operand<true>{sAqk, LD64}, Operand<true>{sDO, LD64});
       acc.for_each_pair([&](int r, int c, float& x0, float& x1) {
-        *reinterpret_cast<uint32_t*>(sDR + r * LD64 + c) = pack_bf16(x0, x1);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(x0, x1);
+        float2 hf = __bfloat1622float2(hi);
+        *reinterpret_cast<__nv_bfloat162*>(sDR + r * LD64 + c) = hi;
+        *reinterpret_cast<uint32_t*>(sDRlo + r * LD64 + c) = pack_bf16(x0 - hf.x, x1 - hf.y);
       });
     }
     __syncthreads();
     store_tile_bf16<C, BV>(dR + base128 + v0, ldt, sDR, LD64);
+    store_tile_bf16<C, BV>(dRlo + base128 + v0, ldt, sDRlo, LD64);
     {
       Tile<128, 64, 4, 2> tmp;
       tmp.zero();
@@ -163,7 +168,7 @@ __global__ void __launch_bounds__(256) fwd_scan_kernel(
   }
 }
 
-constexpr size_t BWD_SMEM = (size_t)(3 * C * LD128 + 3 * C * LD64 + DK * LD64) * sizeof(bf16) + DK * sizeof(float);
+constexpr size_t BWD_SMEM = (size_t)(3 * C * LD128 + 4 * C * LD64 + DK * LD64) * sizeof(bf16) + DK * sizeof(float);
 constexpr size_t FWD_SMEM = (size_t)(2 * C * LD128 + 2 * C * LD64 + DK * LD64) * sizeof(bf16) + DK * sizeof(float);
 
 template <int GATE>
@@ -173,7 +178,8 @@ cudaError_t run_bwd(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_
   if (e != cudaSuccess) return e;
   dim3 grid(DV / BV, a.B * a.H);
   kern<<<grid, 256, BWD_SMEM, st>>>((const bf16*)s.qg, (const bf16*)s.kg, (const bf16*)s.w, (const bf16*)s.Aqk,
-                                    (const bf16*)a.d_o, a.g, a.dht, (bf16*)s.dh, (bf16*)s.dR, a.dh0, a.T, a.H, a.scale);
+                                    (const bf16*)a.d_o, a.g, a.dht, (bf16*)s.dh, (bf16*)s.dR, (bf16*)s.dR_lo, a.dh0, a.T, a.H,
+                                    a.scale);
   count_launch();
   return cudaGetLastError();
 }

@@ -68,14 +68,24 @@ def test_stage_reverse_scan(op):
     a, keep = base_args(op, xs, saved)
     dh = torch.full_like(saved["h"], float("nan"))
     dR = torch.full_like(saved["v_new"], float("nan"))
+    dR_lo = torch.full_like(saved["v_new"], float("nan"))
     dh0 = torch.full((xs["k"].shape[0], xs["k"].shape[2], 128, 128), float("nan"), device=DEV)
     a.dh0 = _capi.ptr(dh0)
-    call_stage("rewy_stage_bwd_scan", a,
-               stage_buffers(qg=saved["qg"], kg=saved["kg"], w=saved["w"], Aqk=saved["Aqk"], dh=dh, dR=dR), DEV)
-    _report(dict(dh=nrmse(ref["dh"], dh), dR=nrmse(ref["dR"], dR), dh0=nrmse(ref["dh0"], dh0)), TOL)
+    call_stage("rewy_stage_bwd_scan", a, stage_buffers(qg=saved["qg"], kg=saved["kg"], w=saved["w"], Aqk=saved["Aqk"],
+                                                       dh=dh, dR=dR, dR_lo=dR_lo), DEV)
+    # dh is stored in BF16 (inter-stage contract), dR as a BF16 hi/lo pair
+    _report(dict(dh=nrmse(ref["dh"], dh), dR=nrmse(ref["dR"], dR.float() + dR_lo.float()),
+                 dh0=nrmse(ref["dh0"], dh0)), 3e-3)
 
 
-def _run_chunk_adjoint(op, xs, saved, dh, dR, out_f32=True, passes=0):
+def _split(x):
+    hi = x.to(torch.bfloat16)
+    return hi.to(DEV).contiguous(), (x - hi.to(x.dtype)).to(torch.bfloat16).to(DEV).contiguous()
+
+
+def _run_chunk_adjoint(op, xs, saved, dh, dR, out_f32=True, passes=0, dR_lo=None):
+    if dR_lo is None:
+        dR_lo = torch.zeros_like(dR)
     a, keep = base_args(op, xs, saved, _capi.OUT_F32 if out_f32 else _capi.OUT_BF16, passes)
     B, T, H, _ = xs["k"].shape
     odt = torch.float32 if out_f32 else torch.bfloat16
@@ -89,18 +99,23 @@ def _run_chunk_adjoint(op, xs, saved, dh, dR, out_f32=True, passes=0):
         out["dbeta"] = nan((B, T, H), torch.float32)
     for n, t in out.items():
         setattr(a, n, _capi.ptr(t))
-    call_stage("rewy_stage_chunk_adjoint", a, stage_buffers(v_new=saved["v_new"], h=saved["h"], dh=dh, dR=dR), DEV)
+    call_stage("rewy_stage_chunk_adjoint", a, stage_buffers(v_new=saved["v_new"], h=saved["h"], dh=dh, dR=dR, dR_lo=dR_lo), DEV)
     return out
 
 
 def _grad_errs(op, ref, out):
-    errs = dict(dq=nrmse(ref["dq"], out["dq"]), dk=nrmse(ref["dk"], out["dk"]), dv=nrmse(ref["dv"], out["dv"]))
+    """Errors in the public dtype of each output: the FP64 reference is rounded to that dtype first, as the
+    reference's own regression does (scripts/npu950_intra_regression.py:66)."""
+    def err(name_ref, name_out):
+        got = out[name_out]
+        return nrmse(ref[name_ref].to(got.dtype), got)
+    errs = dict(dq=err("dq", "dq"), dk=err("dk", "dk"), dv=err("dv", "dv"))
     if op != "delta":
-        errs["dg"] = nrmse(ref["dg"], out["dg"])
+        errs["dg"] = err("dg", "dg")
     if op == "gdn2":
-        errs["db"], errs["dw"] = nrmse(ref["db"], out["db_gate"]), nrmse(ref["dw"], out["dw_gate"])
+        errs["db"], errs["dw"] = err("db", "db_gate"), err("dw", "dw_gate")
     else:
-        errs["dbeta"] = nrmse(ref["dbeta"], out["dbeta"])
+        errs["dbeta"] = err("dbeta", "dbeta")
     return errs
 
 
@@ -110,8 +125,8 @@ def test_stage_chunk_adjoint(op):
     saved = forward_saved(op, xs)
     ref = oracle_backward(op, xs, saved)
     dh = ref["dh"].to(torch.bfloat16).to(DEV)
-    dR = ref["dR"].to(torch.bfloat16).to(DEV)
-    out = _run_chunk_adjoint(op, xs, saved, dh, dR)
+    dR, dR_lo = _split(ref["dR"])
+    out = _run_chunk_adjoint(op, xs, saved, dh, dR, dR_lo=dR_lo)
     _report(_grad_errs(op, ref, out), TOL)
 
 
@@ -157,7 +172,7 @@ def test_family_backward_bf16_outputs_and_no_states(op):
     ref = oracle_backward(op, xs, saved)
     out = _family_call(op, xs, saved, op in ("kda", "gdn2"), out_dtype=torch.bfloat16)
     assert out["dh0"] is None and out["dq"].dtype == torch.bfloat16
-    _report(_grad_errs(op, ref, out), 4e-3)   # includes the final BF16 rounding of dq, dk
+    _report(_grad_errs(op, ref, out), TOL)
 
 
 @pytest.mark.parametrize("case", ["zero_beta", "tiny_beta", "beta_over_one", "strong_gate", "weak_gate", "zero_gate",
