@@ -97,6 +97,8 @@ typedef struct RewyStageBuffers {
   void* dh;     /* bf16 [B,NT,H,128,128] */
   void* dR;     /* bf16 [B,T,H,128]  high part of dR = kg dh + Aqk^T dO */
   void* dR_lo;  /* bf16 [B,T,H,128]  low part: bf16(dR - dR_hi); P = Akk^T (dR + dR_lo) keeps dv, dbeta inside 2e-3 */
+  void* ctrl;   /* int32 [2 + B*H*T/64] control block of the chunk stage: [0] device status word, [1] number of
+                   chunks whose gate span was too wide for the centred products, [2..] their indices */
 } RewyStageBuffers;
 
 /* Whole-family backward.  Replace, one for one, the functions the reference's autograd backwards call:
@@ -138,6 +140,26 @@ int rewy_stage_chunk_adjoint(const RewyBwdArgs* args, const RewyStageBuffers* bu
  * chunk adjoint} over the recorded calls; the stream must have been synchronised by the caller. */
 int rewy_stage_timing_enable(int enable);
 int rewy_stage_timing_read(float* ms_sum4, int* calls);
+
+/* Control block.  A whole-family call keeps it at offset 0 of its workspace; the stage function takes it in
+ * RewyStageBuffers.ctrl.  rewy_device_status copies the status word to the host (this call SYNCHRONISES the
+ * stream) and returns REWY_ERR_DEVICE if a kernel gave up on a bounded wait; rewy_wide_chunk_count returns how
+ * many chunks took the exact pairwise path (the analogue of the reference's per-tile fallback flags,
+ * kernels/endpoint_intra.py:301-304), or -1 on error.  No counterpart in the reference for the status word. */
+int rewy_device_status(const void* ctrl, rewy_stream_t stream);
+int rewy_wide_chunk_count(const void* ctrl, rewy_stream_t stream);
+
+/* Kernel variant of the chunk stage: 0 (default) tensor-core kernel, 1 warp-MMA kernel on every chunk
+ * (cross-check).  Process-wide; no counterpart in the reference. */
+int rewy_set_chunk_variant(int variant);
+
+/* Self-test of the tensor-core plumbing (no counterpart in the reference): one CTA pushes every shared-memory
+ * operand form the stages use through tcgen05.mma.  Inputs row-major on the device: A [128x128] bf16,
+ * B [64x128] bf16, Akk [64x64] bf16, dR [64x128] bf16, Y [128x64] f32, H [64x64] f32.  out [128x384] f32:
+ * columns 0-63 A B^T, 64-127 -(A B^T), 128-255 (rows 0-63) Akk^T dR, 256-319 Y H^T, 320-383 Y H (TF32).
+ * err: device int, non-zero if a bounded wait inside the kernel gave up. */
+int rewy_selftest_tensor_core(const void* A, const void* B, const void* Akk, const void* dR, const float* Y,
+                              const float* H, float* out, int* err, rewy_stream_t stream);
 
 /* Diagnostics. */
 const char* rewy_last_error(void);       /* thread-local text of the last non-zero status */

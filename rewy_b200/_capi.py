@@ -19,7 +19,8 @@ OUT_BF16, OUT_F32 = 0, 1
 EXPORTS = (
     "rewy_kda_bwd", "rewy_gdn2_bwd", "rewy_gdn_bwd", "rewy_delta_bwd", "rewy_bwd_workspace_bytes",
     "rewy_stage_prepare", "rewy_stage_fwd_scan", "rewy_stage_bwd_scan", "rewy_stage_chunk_adjoint",
-    "rewy_stage_timing_enable", "rewy_stage_timing_read",
+    "rewy_stage_timing_enable", "rewy_stage_timing_read", "rewy_selftest_tensor_core",
+    "rewy_device_status", "rewy_wide_chunk_count", "rewy_set_chunk_variant",
     "rewy_last_error", "rewy_version", "rewy_kernel_launch_count",
 )
 
@@ -39,7 +40,7 @@ class BwdArgs(ctypes.Structure):
 
 
 class StageBuffers(ctypes.Structure):
-    _fields_ = [(n, c_void_p) for n in ("w", "u", "qg", "kg", "v_new", "h", "Aqk", "dh", "dR", "dR_lo")]
+    _fields_ = [(n, c_void_p) for n in ("w", "u", "qg", "kg", "v_new", "h", "Aqk", "dh", "dR", "dR_lo", "ctrl")]
 
 
 _lib = None
@@ -73,6 +74,14 @@ def load():
     lib.rewy_stage_timing_enable.restype = c_int
     lib.rewy_stage_timing_read.argtypes = [ctypes.POINTER(c_float), ctypes.POINTER(c_int)]
     lib.rewy_stage_timing_read.restype = c_int
+    lib.rewy_selftest_tensor_core.argtypes = [c_void_p] * 9
+    lib.rewy_selftest_tensor_core.restype = c_int
+    lib.rewy_device_status.argtypes = [c_void_p, c_void_p]
+    lib.rewy_device_status.restype = c_int
+    lib.rewy_wide_chunk_count.argtypes = [c_void_p, c_void_p]
+    lib.rewy_wide_chunk_count.restype = c_int
+    lib.rewy_set_chunk_variant.argtypes = [c_int]
+    lib.rewy_set_chunk_variant.restype = c_int
     lib.rewy_last_error.restype = c_char_p
     lib.rewy_version.restype = c_char_p
     lib.rewy_kernel_launch_count.restype = c_int

@@ -47,7 +47,8 @@ def _c(t, dtype=None):
     return t.contiguous()
 
 
-def _run(family, policy, B, T, H, scale, tensors, out_dtype, intra_passes, workspace, want_dg, want_dbeta, vector_gates):
+def _run(family, policy, B, T, H, scale, tensors, out_dtype, intra_passes, workspace, want_dg, want_dbeta, vector_gates,
+         check_status=False):
     """tensors: dict name -> tensor or None for every input pointer of RewyBwdArgs."""
     lib = _capi.load()
     q = tensors["q"]
@@ -85,6 +86,9 @@ def _run(family, policy, B, T, H, scale, tensors, out_dtype, intra_passes, works
           _capi.DELTA: lib.rewy_delta_bwd}[family]
     with torch.cuda.device(dev):
         _capi.check(fn(a, _capi.current_stream(dev)), fn.__name__)
+        if check_status:  # synchronises: reads the device status word at the start of the workspace
+            _capi.check(lib.rewy_device_status(_capi.ptr(workspace), _capi.current_stream(dev)), "device status")
+            out["wide_chunks"] = int(lib.rewy_wide_chunk_count(_capi.ptr(workspace), _capi.current_stream(dev)))
     # Inputs, outputs and workspace were allocated on (or are already in use by) the current stream, the
     # same stream the launches went to, so the caching allocator's stream-ordered reuse keeps them valid.
     return out
@@ -94,7 +98,7 @@ def kda_backward(q, k, v, beta, Aqk, Akk, scale, initial_state, do, dht, g=None,
                  cu_seqlens=None, chunk_indices=None, chunk_size=64, safe_gate=False, lower_bound=None,
                  use_gate_in_kernel=False, A_log=None, dt_bias=None, disable_recompute=False, cp_context=None,
                  w=None, u=None, qg=None, kg=None, v_new=None, h=None, use_graph=False, chunk_offsets=None,
-                 *, out_dtype=None, intra_passes=None, workspace=None):
+                 *, out_dtype=None, intra_passes=None, workspace=None, check_status=False):
     """KDA backward.  Returns (dq, dk, dv, db, dg, dh0, dA, dbias) like FLA's ``chunk_kda_bwd``;
     ``g`` is the chunk-local cumulative gate in log2 units that the forward saved."""
     B, T, H = _check_common(q, k, v, do, chunk_size, cu_seqlens, cp_context, state_v_first, use_gate_in_kernel)
@@ -111,7 +115,7 @@ def kda_backward(q, k, v, beta, Aqk, Akk, scale, initial_state, do, dht, g=None,
         kg=_c(kg, torch.bfloat16) if saved else None, v_new=_c(v_new, torch.bfloat16) if saved else None,
         h=_c(h, torch.bfloat16) if saved else None)
     out = _run(_capi.KDA, _capi.SAVED if saved else _capi.RECOMPUTE, B, T, H, scale, tensors, out_dtype,
-               intra_passes, workspace, True, True, False)
+               intra_passes, workspace, True, True, False, check_status)
     record("kda", "optimized_backward")
     return out["dq"], out["dk"], out["dv"], out["dbeta"], out["dg"], out["dh0"], None, None
 
@@ -120,7 +124,7 @@ def gdn2_backward(q, k, v, b, w_gate, Aqk, Akk, scale, initial_state, do, dht, g
                   chunk_indices=None, chunk_size=64, safe_gate=False, lower_bound=None, use_gate_in_kernel=False,
                   A_log=None, dt_bias=None, state_v_first=False, w_wy=None, u_wy=None, qg=None, kg=None, v_new=None,
                   h=None, disable_recompute=False, cp_context=None,
-                  *, out_dtype=None, intra_passes=None, workspace=None):
+                  *, out_dtype=None, intra_passes=None, workspace=None, check_status=False):
     """GDN2 backward.  Returns (dq, dk, dv, db, dw, dg, dh0, dA_log, ddt_bias) like ``chunk_gdn2_bwd``."""
     B, T, H = _check_common(q, k, v, do, chunk_size, cu_seqlens, cp_context, state_v_first, use_gate_in_kernel)
     _unsupported("safe_gate", safe_gate)
@@ -135,14 +139,14 @@ def gdn2_backward(q, k, v, b, w_gate, Aqk, Akk, scale, initial_state, do, dht, g
         kg=_c(kg, torch.bfloat16) if saved else None, v_new=_c(v_new, torch.bfloat16) if saved else None,
         h=_c(h, torch.bfloat16) if saved else None)
     out = _run(_capi.GDN2, _capi.SAVED if saved else _capi.RECOMPUTE, B, T, H, scale, tensors, out_dtype,
-               intra_passes, workspace, True, False, True)
+               intra_passes, workspace, True, False, True, check_status)
     record("gdn2", "optimized_backward")
     return out["dq"], out["dk"], out["dv"], out["db_gate"], out["dw_gate"], out["dg"], out["dh0"], None, None
 
 
 def gdn_backward(q, k, v, g, beta, A, scale, initial_state, do, dht, cu_seqlens=None, cp_context=None,
                  chunk_indices=None, state_v_first=False, use_gate_in_kernel=False, g_input=None, A_log=None,
-                 dt_bias=None, chunk_size=64, *, out_dtype=None, intra_passes=None, workspace=None):
+                 dt_bias=None, chunk_size=64, *, out_dtype=None, intra_passes=None, workspace=None, check_status=False):
     """Gated DeltaNet backward.  Returns (dq, dk, dv, db, dg, dh0, dA_log, ddt_bias) — ``db`` before ``dg``
     as at src/fast_delta_rule/backends/backward.py:130."""
     B, T, H = _check_common(q, k, v, do, chunk_size, cu_seqlens, cp_context, state_v_first, use_gate_in_kernel)
@@ -151,13 +155,13 @@ def gdn_backward(q, k, v, g, beta, A, scale, initial_state, do, dht, cu_seqlens=
         Aqk=None, Akk=_c(A, torch.bfloat16), h0=_c(initial_state, torch.float32), d_o=_c(do, torch.bfloat16),
         dht=_c(dht, torch.float32), w=None, qg=None, kg=None, v_new=None, h=None)
     out = _run(_capi.GDN, _capi.RECOMPUTE, B, T, H, scale, tensors, out_dtype, intra_passes, workspace,
-               True, True, False)
+               True, True, False, check_status)
     record("gdn", "optimized_backward")
     return out["dq"], out["dk"], out["dv"], out["dbeta"], out["dg"], out["dh0"], None, None
 
 
 def delta_backward(q, k, v, beta, A, scale, initial_state, do, dht, cu_seqlens=None, chunk_indices=None,
-                   chunk_size=64, *, out_dtype=None, intra_passes=None, workspace=None):
+                   chunk_size=64, *, out_dtype=None, intra_passes=None, workspace=None, check_status=False):
     """DeltaNet backward.  Returns (dq, dk, dv, db, dh0) like ``chunk_delta_rule_bwd``."""
     B, T, H = _check_common(q, k, v, do, chunk_size, cu_seqlens, None, False, False)
     tensors = dict(
@@ -165,6 +169,6 @@ def delta_backward(q, k, v, beta, A, scale, initial_state, do, dht, cu_seqlens=N
         Aqk=None, Akk=_c(A, torch.bfloat16), h0=_c(initial_state, torch.float32), d_o=_c(do, torch.bfloat16),
         dht=_c(dht, torch.float32), w=None, qg=None, kg=None, v_new=None, h=None)
     out = _run(_capi.DELTA, _capi.RECOMPUTE, B, T, H, scale, tensors, out_dtype, intra_passes, workspace,
-               False, True, False)
+               False, True, False, check_status)
     record("delta", "optimized_backward")
     return out["dq"], out["dk"], out["dv"], out["dbeta"], out["dh0"]

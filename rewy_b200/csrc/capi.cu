@@ -21,7 +21,7 @@ size_t align_up(size_t x) { return (x + 255) & ~size_t(255); }
 struct Plan {
   bool prepare;       // rebuild w,u,qg,kg (+ forward scan for v_new,h)
   bool build_aqk;     // scalar families save no Aqk
-  size_t off_dh, off_dR, off_dRlo, off_w, off_u, off_qg, off_kg, off_vnew, off_h, off_aqk, total;
+  size_t off_ctrl, off_dh, off_dR, off_dRlo, off_w, off_u, off_qg, off_kg, off_vnew, off_h, off_aqk, total;
 };
 
 Plan make_plan(int family, int policy, long long B, long long T, long long H) {
@@ -30,6 +30,7 @@ Plan make_plan(int family, int policy, long long B, long long T, long long H) {
   p.build_aqk = family == REWY_DELTA || family == REWY_GDN;
   p.prepare = p.build_aqk || policy == REWY_RECOMPUTE;
   size_t o = 0;
+  p.off_ctrl = o; o += align_up(sizeof(int) * (size_t)(2 + B * H * (T / C)));
   p.off_dh = o; o += align_up(n * 512);
   p.off_dR = o; o += align_up(n * 256);
   p.off_dRlo = o; o += align_up(n * 256);
@@ -109,6 +110,13 @@ void timing_mark(int set, int idx, cudaStream_t st) {
   g_timing.have[set][idx] = true;
 }
 
+std::atomic<int> g_chunk_variant{0};  // 0 = tensor-core kernel (+ pairwise list), 1 = warp-MMA kernel everywhere
+
+cudaError_t run_chunk_adjoint(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
+  if (g_chunk_variant.load(std::memory_order_relaxed) == 1) return launch_chunk_adjoint_warp(a, s, nullptr, st);
+  return launch_chunk_adjoint_tc(a, s, static_cast<int*>(s.ctrl), st);
+}
+
 int check_cuda(cudaError_t e, const char* stage) {
   if (e == cudaSuccess) return REWY_OK;
   snprintf(g_error, sizeof(g_error), "%s: %s", stage, cudaGetErrorString(e));
@@ -125,6 +133,7 @@ int run_family(const RewyBwdArgs* a, int family, cudaStream_t st) {
     return fail(REWY_ERR_WORKSPACE, "workspace too small: need %s%lld bytes", "", (long long)p.total);
   char* ws = static_cast<char*>(a->workspace);
   RewyStageBuffers s{};
+  s.ctrl = ws + p.off_ctrl;
   s.dh = ws + p.off_dh;
   s.dR = ws + p.off_dR;
   s.dR_lo = ws + p.off_dRlo;
@@ -150,7 +159,7 @@ int run_family(const RewyBwdArgs* a, int family, cudaStream_t st) {
   timing_mark(set, 2, st);
   if ((rc = check_cuda(launch_bwd_scan(*a, s, st), "reverse state scan")) != REWY_OK) return rc;
   timing_mark(set, 3, st);
-  if ((rc = check_cuda(launch_chunk_adjoint(*a, s, st), "chunk adjoint")) != REWY_OK) return rc;
+  if ((rc = check_cuda(run_chunk_adjoint(*a, s, st), "chunk adjoint")) != REWY_OK) return rc;
   timing_mark(set, 4, st);
   return REWY_OK;
 }
@@ -224,6 +233,7 @@ int rewy_stage_chunk_adjoint(const RewyBwdArgs* a, const RewyStageBuffers* s, re
   STAGE_PTR(a->q, "q"); STAGE_PTR(a->k, "k"); STAGE_PTR(a->v, "v"); STAGE_PTR(a->Akk, "Akk"); STAGE_PTR(a->d_o, "d_o");
   STAGE_PTR(s->v_new, "v_new"); STAGE_PTR(s->h, "h"); STAGE_PTR(s->dh, "dh"); STAGE_PTR(s->dR, "dR");
   STAGE_PTR(s->dR_lo, "dR_lo");
+  if (g_chunk_variant.load(std::memory_order_relaxed) != 1) STAGE_PTR(s->ctrl, "ctrl");
   STAGE_PTR(a->dq, "dq"); STAGE_PTR(a->dk, "dk"); STAGE_PTR(a->dv, "dv");
   if (a->family != REWY_DELTA) { STAGE_PTR(a->g, "g"); STAGE_PTR(a->dg, "dg"); }
   if (a->family == REWY_GDN2) {
@@ -232,7 +242,7 @@ int rewy_stage_chunk_adjoint(const RewyBwdArgs* a, const RewyStageBuffers* s, re
   } else {
     STAGE_PTR(a->beta, "beta"); STAGE_PTR(a->dbeta, "dbeta");
   }
-  return check_cuda(launch_chunk_adjoint(*a, *s, (cudaStream_t)st), "chunk adjoint");
+  return check_cuda(run_chunk_adjoint(*a, *s, (cudaStream_t)st), "chunk adjoint");
 }
 
 int rewy_stage_timing_enable(int enable) {
@@ -264,6 +274,30 @@ int rewy_stage_timing_read(float* ms_sum, int* calls) {
     }
   }
   return REWY_OK;
+}
+
+int rewy_set_chunk_variant(int variant) {
+  if (variant != 0 && variant != 1) return fail(REWY_ERR_UNSUPPORTED, "chunk variant must be 0 or 1%s");
+  g_chunk_variant.store(variant, std::memory_order_relaxed);
+  return REWY_OK;
+}
+
+int rewy_device_status(const void* ctrl, rewy_stream_t st) {
+  if (ctrl == nullptr) return fail(REWY_ERR_NULL, "required pointer '%s' is NULL", "ctrl");
+  int word[2] = {0, 0};
+  cudaError_t e = cudaMemcpyAsync(word, ctrl, sizeof(word), cudaMemcpyDeviceToHost, (cudaStream_t)st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)st);
+  if (e != cudaSuccess) return check_cuda(e, "device status read");
+  if (word[0] != 0) return fail(REWY_ERR_DEVICE, "a kernel gave up on a bounded wait at site %s%lld", "", word[0]);
+  return REWY_OK;
+}
+
+int rewy_wide_chunk_count(const void* ctrl, rewy_stream_t st) {
+  if (ctrl == nullptr) return -1;
+  int word[2] = {0, 0};
+  cudaError_t e = cudaMemcpyAsync(word, ctrl, sizeof(word), cudaMemcpyDeviceToHost, (cudaStream_t)st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)st);
+  return e == cudaSuccess ? word[1] : -1;
 }
 
 const char* rewy_last_error(void) { return g_error; }

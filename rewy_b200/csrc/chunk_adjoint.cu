@@ -32,6 +32,7 @@ struct ChunkParams {
   float *dg, *dbeta;
   int T, H, out_f32, passes;
   float scale;
+  const int* list;  // nullptr, or [count, chunk indices...] (flattened (batch*head)*NT + chunk)
 };
 
 __device__ __forceinline__ void store_out2(void* base, size_t off, float x0, float x1, int out_f32) {
@@ -49,8 +50,7 @@ __device__ __forceinline__ void split_store(bf16* hi, bf16* lo, int idx, float x
 }
 
 template <int GATE, bool VB>
-__global__ void __launch_bounds__(256, 1) chunk_adjoint_kernel(const ChunkParams p) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+__device__ __forceinline__ void chunk_body(const ChunkParams& p, const int n, const int bh, unsigned char* smem_raw) {
   bf16* sDO = reinterpret_cast<bf16*>(smem_raw);  // [64][136]
   bf16* sR = sDO + C * LD128;                     // [64][136]
   bf16* sP = sR + C * LD128;                      // [64][136]
@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(256, 1) chunk_adjoint_kernel(const ChunkParams
   bf16* sDRt = sXl;
   bf16* sDRlo = sEh;
 
-  const int n = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  const int b = bh / p.H, h = bh % p.H;
   const int T = p.T, H = p.H, NT = T / C;
   const size_t row0 = (size_t)b * T + (size_t)n * C;
   const size_t ldt = (size_t)H * 128;
@@ -467,6 +467,23 @@ __global__ void __launch_bounds__(256, 1) chunk_adjoint_kernel(const ChunkParams
   }
 }
 
+// Grid mode: blockIdx = (chunk, batch*head).  List mode (p.list != nullptr): the CTAs walk over the chunk
+// indices list[1 .. list[0]] that the tensor-core kernel left to the exact pairwise path.
+template <int GATE, bool VB>
+__global__ void __launch_bounds__(256, 1) chunk_adjoint_kernel(const ChunkParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  if (p.list == nullptr) {
+    chunk_body<GATE, VB>(p, blockIdx.x, blockIdx.y, smem_raw);
+    return;
+  }
+  const int count = p.list[0], NT = p.T / C;
+  for (int i = blockIdx.x; i < count; i += gridDim.x) {
+    const int chunk = p.list[1 + i];
+    chunk_body<GATE, VB>(p, chunk % NT, chunk / NT, smem_raw);
+    __syncthreads();
+  }
+}
+
 constexpr size_t CHUNK_SMEM = (size_t)(3 * C * LD128 + DK * LD128 + 4 * C * LD128 + 4 * C * LD64) * sizeof(bf16) +
                               (size_t)(C + DK + DK + C) * sizeof(float) + 16;
 static_assert((size_t)C * LDG * sizeof(float) <= (size_t)2 * C * LD128 * sizeof(bf16), "dg tile must fit its alias");
@@ -477,6 +494,7 @@ cudaError_t run(const ChunkParams& p, int B, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CHUNK_SMEM);
   if (e != cudaSuccess) return e;
   dim3 grid(p.T / C, B * p.H);
+  if (p.list != nullptr) grid = dim3(min(p.T / C * B * p.H, 296), 1);
   kern<<<grid, 256, CHUNK_SMEM, st>>>(p);
   count_launch();
   return cudaGetLastError();
@@ -484,8 +502,9 @@ cudaError_t run(const ChunkParams& p, int B, cudaStream_t st) {
 
 }  // namespace
 
-cudaError_t launch_chunk_adjoint(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
+cudaError_t launch_chunk_adjoint_warp(const RewyBwdArgs& a, const RewyStageBuffers& s, const int* list, cudaStream_t st) {
   ChunkParams p;
+  p.list = list;
   p.q = (const bf16*)a.q; p.k = (const bf16*)a.k; p.v = (const bf16*)a.v;
   p.bg = (const bf16*)a.b_gate; p.wg = (const bf16*)a.w_gate; p.Akk = (const bf16*)a.Akk;
   p.dO = (const bf16*)a.d_o; p.R = (const bf16*)s.v_new; p.h = (const bf16*)s.h; p.dh = (const bf16*)s.dh;

@@ -1,0 +1,632 @@
+// Stage "chunk adjoint" on the Blackwell tensor cores (tcgen05 + TMEM accumulators, TMA tile loads).
+//
+// Same mathematics as chunk_adjoint.cu (the reference functions it replaces are listed there); this file is
+// the production path.  One persistent CTA per SM walks over chunks; per chunk:
+//   P      = Akk^T (dR_hi + dR_lo)                 M=128 (64 valid rows) N=128 K=64   both operands MN-major
+//   [H;-D] = [dO;P] R^T                            M=128 N=64 K=128                  one stacked product
+//   X1 = h dO^T, X3 = -(h P^T), X5 = dh R^T        M=128 (key channel) N=64 (token) K=128
+//   X2 = Yc^T H^T, X4 = Yc^T D^T, X6 = Qc^T H + Ec^T D   K=64, BF16 hi/lo split operands (3 passes each)
+// The accumulators of the last six products are [key channel x token]: epilogue thread k owns channel k and
+// all 64 tokens, so gate factors are per-thread scalars per token and the reverse gate cumsum is a running sum
+// inside the thread.  Chunks whose cumulative gate spans 80 or more log2 units are not processed here: their
+// indices are appended to a list that the warp-MMA kernel (exact pairwise path) works off afterwards.
+#include "tc05.cuh"
+
+namespace rewy {
+namespace {
+using namespace tc;
+
+constexpr float SPAN_LIMIT = 80.f;
+
+struct TcParams {
+  const bf16 *q, *k, *v, *bg, *wg, *dh;
+  const float *g, *beta;
+  void *dq, *dk, *dbg, *dwg;
+  bf16* dv;
+  float *dg, *dbeta;
+  int* wide_list;   // [0] = count, [1..] = flattened chunk indices with a wide gate span
+  int* err;         // device status word: non-zero if a bounded wait gave up
+  int T, H, NT, total_chunks, out_f32;
+  float scale;
+};
+
+// Shared-memory plan (byte offsets from a 1024-byte aligned base).  "t0" tiles are dead once P is computed and
+// are then overwritten by the Qc tiles; dh is loaded into the h buffer after the products that read h are done.
+struct Smem {
+  static constexpr uint32_t AKK = 0;                   // [64 j][64 i] BF16                      8 KB
+  static constexpr uint32_t DRHI = AKK + 8192;         // 2 panels [64 j][64 v]                  16 KB   (later Qc hi)
+  static constexpr uint32_t DRLO = DRHI + 16384;       //                                        16 KB   (later Qc lo)
+  static constexpr uint32_t DOP = DRLO + 16384;        // per v-panel: dO [64][64] then P [64][64] 32 KB
+  static constexpr uint32_t R = DOP + 32768;           // 2 panels [64 j][64 v]                  16 KB
+  static constexpr uint32_t HS = R + 16384;            // 2 panels [128 k][64 v]  h, later dh    32 KB
+  static constexpr uint32_t HHI = HS + 32768;          // dAqk hi [64 i][64 j]                   8 KB
+  static constexpr uint32_t HLO = HHI + 8192;
+  static constexpr uint32_t DHI = HLO + 8192;          // dAkk hi
+  static constexpr uint32_t DLO = DHI + 8192;
+  static constexpr uint32_t YHI = DLO + 8192;          // Yc^T hi [128 k][64 t]                  16 KB
+  static constexpr uint32_t YLO = YHI + 16384;
+  static constexpr uint32_t EHI = YLO + 16384;         // Ec^T hi
+  static constexpr uint32_t ELO = EHI + 16384;
+  static constexpr uint32_t QHI = DRHI;                // Qc^T hi/lo alias the dR tiles
+  static constexpr uint32_t QLO = DRLO;
+  static constexpr uint32_t TILES_END = ELO + 16384;   // 204800
+  static constexpr uint32_t BETA = TILES_END;          // float[64]
+  static constexpr uint32_t DBETA = BETA + 256;        // float[64]
+  static constexpr uint32_t GS = DBETA + 256;          // float[64] scalar gate rows
+  static constexpr uint32_t DGS = GS + 256;            // float[64] per-token gate sums (scalar gate)
+  static constexpr uint32_t BARS = DGS + 256;          // 8 mbarriers
+  static constexpr uint32_t TMEM = BARS + 64;          // uint32 tmem base (+ flags)
+  static constexpr uint32_t TOTAL = TMEM + 64;
+};
+static_assert(Smem::TOTAL + 1024 <= 232448, "shared memory plan exceeds the 227 KB per-CTA limit");
+
+enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C12, BAR_C3 };
+
+// TMEM column plan (512 columns allocated).
+constexpr uint32_t TM_P = 0, TM_HD = 128, TM_X1 = 192, TM_X2 = 256, TM_X3 = 320, TM_X4 = 384, TM_X5 = 0, TM_X6 = 64;
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&r)[16]) {
+  uint32_t u[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+        "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 16; i++) r[i] = __uint_as_float(u[i]);
+}
+
+__device__ __forceinline__ void store_out1(void* base, size_t off, float x, int out_f32) {
+  if (out_f32)
+    reinterpret_cast<float*>(base)[off] = x;
+  else
+    reinterpret_cast<bf16*>(base)[off] = f2bf(x);
+}
+
+// Pack 8 FP32 values into 8 BF16 "hi" and 8 BF16 "lo" (residual) values.
+__device__ __forceinline__ void split8(const float (&x)[8], uint4& hi, uint4& lo) {
+  uint32_t h[4], l[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    __nv_bfloat162 hh = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+    float2 hf = __bfloat1622float2(hh);
+    h[i] = *reinterpret_cast<uint32_t*>(&hh);
+    l[i] = pack_bf16(x[2 * i] - hf.x, x[2 * i + 1] - hf.y);
+  }
+  hi = make_uint4(h[0], h[1], h[2], h[3]);
+  lo = make_uint4(l[0], l[1], l[2], l[3]);
+}
+
+// K-major BF16 product over `ksteps` K=16 steps; tiles made of 64-element (128-byte) panels `panel_*` bytes apart.
+__device__ __forceinline__ void mma_kmajor(uint32_t d, uint32_t a, uint32_t a_panel, uint32_t b, uint32_t b_panel,
+                                           int ksteps, uint32_t idesc, bool accumulate) {
+  for (int ks = 0; ks < ksteps; ks++) {
+    uint64_t ad = smem_desc(a + (ks >> 2) * a_panel + (ks & 3) * 32, 16, 1024);
+    uint64_t bd = smem_desc(b + (ks >> 2) * b_panel + (ks & 3) * 32, 16, 1024);
+    mma_f16(d, ad, bd, idesc, accumulate || ks > 0);
+  }
+}
+
+// Sum over the warp of x[lane & 15] for each of the 16 per-thread values (16 shuffles); every lane returns the
+// total of value index (lane & 15).
+__device__ __forceinline__ float warp_sum16(float (&x)[16], int lane) {
+#pragma unroll
+  for (int m = 8, n = 16; m >= 1; m >>= 1, n >>= 1) {
+    const bool up = (lane & m) != 0;
+#pragma unroll
+    for (int i = 0; i < n / 2; i++) {
+      float send = up ? x[i] : x[i + n / 2];
+      float keep = up ? x[i + n / 2] : x[i];
+      x[i] = keep + __shfl_xor_sync(0xffffffffu, send, m);
+    }
+  }
+  return x[0] + __shfl_xor_sync(0xffffffffu, x[0], 16);
+}
+
+template <int GATE, bool VB>
+__global__ void __launch_bounds__(128, 1)
+chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_constant__ CUtensorMap tmDRhi,
+                        const __grid_constant__ CUtensorMap tmDRlo, const __grid_constant__ CUtensorMap tmDO,
+                        const __grid_constant__ CUtensorMap tmR, const __grid_constant__ CUtensorMap tmH,
+                        const __grid_constant__ CUtensorMap tmDH, const TcParams p) {
+  extern __shared__ __align__(1024) unsigned char raw[];
+  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  float* sBeta = reinterpret_cast<float*>(sm + Smem::BETA);
+  float* sDb = reinterpret_cast<float*>(sm + Smem::DBETA);
+  float* sGs = reinterpret_cast<float*>(sm + Smem::GS);
+  float* sDgs = reinterpret_cast<float*>(sm + Smem::DGS);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + Smem::BARS);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + Smem::TMEM);
+  const uint32_t sb = smem_u32(sm);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int T = p.T, H = p.H, NT = p.NT;
+  const size_t ldt = (size_t)H * 128;
+  const float scale = p.scale;
+
+  if (tid == 0) {
+    for (int i = 0; i < 8; i++) mbar_init(&bars[i], 1);
+    fence_barrier_init();
+    prefetch_tmap(&tmAkk); prefetch_tmap(&tmDRhi); prefetch_tmap(&tmDRlo); prefetch_tmap(&tmDO);
+    prefetch_tmap(&tmR); prefetch_tmap(&tmH); prefetch_tmap(&tmDH);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tb = *tmem_slot;
+  const uint32_t tlane = tb + ((uint32_t)(warp * 32) << 16);  // this warp's TMEM lanes
+  uint32_t ph = 0;                                            // phase bit per barrier
+  bool alive = true;                                          // false once a bounded wait gave up
+
+  constexpr uint32_t ID_P = instr_desc(FMT_BF16, 128, 128, true, true);
+  constexpr uint32_t ID_KK = instr_desc(FMT_BF16, 128, 64, false, false);
+  constexpr uint32_t ID_KK_NEG = instr_desc(FMT_BF16, 128, 64, false, false, true, false);
+  constexpr uint32_t ID_KMN = instr_desc(FMT_BF16, 128, 64, false, true);
+
+  auto wait = [&](int b, int code) {
+    if (alive) alive = mbar_wait(&bars[b], (ph >> b) & 1u, p.err, code);
+  };
+
+  for (int chunk = blockIdx.x; chunk < p.total_chunks && alive; chunk += gridDim.x) {
+    const int bh = chunk / NT, n = chunk % NT, b = bh / H, h = bh % H;
+    const int row0 = b * T + n * C;                       // first token row in [B*T]
+    const size_t base128 = ((size_t)row0 * H + h) * 128;
+    const size_t base1 = (size_t)row0 * H + h;
+    const int hrow0 = ((b * NT + n) * H + h) * 128;        // first row of this chunk's state in [B*NT*H*128]
+    uint32_t used = 0;
+
+    if (tid == 0) {
+      mbar_expect_tx(&bars[BAR_A], 8192 + 2 * 16384);
+      tma_load_2d(sm + Smem::AKK, &tmAkk, h * 64, row0, &bars[BAR_A]);
+      for (int pn = 0; pn < 2; pn++) {
+        tma_load_2d(sm + Smem::DRHI + pn * 8192, &tmDRhi, h * 128 + 64 * pn, row0, &bars[BAR_A]);
+        tma_load_2d(sm + Smem::DRLO + pn * 8192, &tmDRlo, h * 128 + 64 * pn, row0, &bars[BAR_A]);
+      }
+      mbar_expect_tx(&bars[BAR_B], 2 * 16384);
+      mbar_expect_tx(&bars[BAR_C], 32768);
+      for (int pn = 0; pn < 2; pn++) {
+        tma_load_2d(sm + Smem::DOP + pn * 16384, &tmDO, h * 128 + 64 * pn, row0, &bars[BAR_B]);
+        tma_load_2d(sm + Smem::R + pn * 8192, &tmR, h * 128 + 64 * pn, row0, &bars[BAR_B]);
+        tma_load_2d(sm + Smem::HS + pn * 16384, &tmH, 64 * pn, hrow0, &bars[BAR_C]);
+      }
+    }
+    used |= (1u << BAR_A) | (1u << BAR_B) | (1u << BAR_C);
+    if (tid < C) {
+      sBeta[tid] = VB ? 0.f : p.beta[base1 + (size_t)tid * H];
+      sDb[tid] = 0.f;
+      sDgs[tid] = 0.f;
+      if (GATE == GATE_SCALAR) sGs[tid] = p.g[base1 + (size_t)tid * H];
+    }
+    __syncthreads();
+
+    // ---- gate rows of this thread's key channel, centre, span -----------------------------------
+    float g[C];
+    float cen = 0.f;
+    bool wide = false;
+    if (GATE != GATE_NONE) {
+      float lo = INFINITY, hi = -INFINITY;
+#pragma unroll
+      for (int t = 0; t < C; t++) {
+        g[t] = GATE == GATE_VECTOR ? p.g[base128 + (size_t)t * ldt + tid] : sGs[t];
+        lo = fminf(lo, g[t]);
+        hi = fmaxf(hi, g[t]);
+      }
+      cen = 0.5f * (lo + hi);
+      wide = !(hi - lo < SPAN_LIMIT);
+    } else {
+#pragma unroll
+      for (int t = 0; t < C; t++) g[t] = 0.f;
+    }
+    if (__syncthreads_or(wide ? 1 : 0)) {
+      // wide gate span: leave the chunk to the exact pairwise kernel; drain the loads already in flight
+      if (tid == 0) {
+        wait(BAR_A, 101); wait(BAR_B, 102); wait(BAR_C, 103);
+        int idx = atomicAdd(&p.wide_list[0], 1);
+        p.wide_list[1 + idx] = chunk;
+      }
+      ph ^= used;
+      alive = __syncthreads_and(alive ? 1 : 0) != 0;
+      continue;
+    }
+
+    // ---- P = Akk^T (dR_hi + dR_lo) ----------------------------------------------------------------
+    if (tid == 0) {
+      wait(BAR_A, 1);
+      if (alive) {
+        tc_fence_after_sync();
+        for (int ks = 0; ks < 4; ks++)
+          mma_f16(tb + TM_P, smem_desc(sb + Smem::AKK + ks * 2048, 8192, 1024),
+                  smem_desc(sb + Smem::DRHI + ks * 2048, 8192, 1024), ID_P, ks > 0);
+        for (int ks = 0; ks < 4; ks++)
+          mma_f16(tb + TM_P, smem_desc(sb + Smem::AKK + ks * 2048, 8192, 1024),
+                  smem_desc(sb + Smem::DRLO + ks * 2048, 8192, 1024), ID_P, true);
+        mma_commit(&bars[BAR_P]);
+      }
+    }
+    used |= 1u << BAR_P;
+
+    // ---- operand tiles of the matrix-intra products: Yc^T and Ec^T (row = this thread's channel) ----
+    const float ec = GATE == GATE_NONE ? 1.f : exp2f(cen);
+#pragma unroll
+    for (int t8 = 0; t8 < 8; t8++) {
+      float y[8], e[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int t = t8 * 8 + j;
+        const size_t go = base128 + (size_t)t * ldt + tid;
+        const float kk = bf2f(p.k[go]);
+        const float a = GATE == GATE_NONE ? 1.f : exp2f(g[t] - cen), z = GATE == GATE_NONE ? 1.f : exp2f(cen - g[t]);
+        const float bb = VB ? bf2f(p.bg[go]) : sBeta[t];
+        y[j] = kk * z;
+        e[j] = bb * kk * a;
+      }
+      uint4 hi, lo;
+      split8(y, hi, lo);
+      *reinterpret_cast<uint4*>(sm + Smem::YHI + swz(tid, t8)) = hi;
+      *reinterpret_cast<uint4*>(sm + Smem::YLO + swz(tid, t8)) = lo;
+      split8(e, hi, lo);
+      *reinterpret_cast<uint4*>(sm + Smem::EHI + swz(tid, t8)) = hi;
+      *reinterpret_cast<uint4*>(sm + Smem::ELO + swz(tid, t8)) = lo;
+    }
+
+    // ---- after P: Qc^T tiles over the dead dR tiles, P epilogue on the 64 row threads ------------------
+    wait(BAR_P, 2);
+    tc_fence_after_sync();
+#pragma unroll
+    for (int t8 = 0; t8 < 8; t8++) {
+      float x[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int t = t8 * 8 + j;
+        const float a = GATE == GATE_NONE ? 1.f : exp2f(g[t] - cen);
+        x[j] = bf2f(p.q[base128 + (size_t)t * ldt + tid]) * a;
+      }
+      uint4 hi, lo;
+      split8(x, hi, lo);
+      *reinterpret_cast<uint4*>(sm + Smem::QHI + swz(tid, t8)) = hi;
+      *reinterpret_cast<uint4*>(sm + Smem::QLO + swz(tid, t8)) = lo;
+    }
+    if (tid < C && alive) {
+      const int i = tid;
+      const size_t go = base128 + (size_t)i * ldt;
+      const float beta_i = sBeta[i];
+      float dbv = 0.f;
+#pragma unroll 1
+      for (int c4 = 0; c4 < 8; c4++) {
+        float x[16];
+        tmem_ld16(tlane + TM_P + 16 * c4, x);
+        tmem_ld_wait();
+        const int v0 = 16 * c4;
+        uint4 vraw[2] = {*reinterpret_cast<const uint4*>(p.v + go + v0), *reinterpret_cast<const uint4*>(p.v + go + v0 + 8)};
+        const uint32_t* vu = reinterpret_cast<const uint32_t*>(vraw);
+        uint32_t dvp[8], pp[8];
+        float dwv[16];
+        uint4 wraw[2];
+        if (VB) {
+          wraw[0] = *reinterpret_cast<const uint4*>(p.wg + go + v0);
+          wraw[1] = *reinterpret_cast<const uint4*>(p.wg + go + v0 + 8);
+        }
+        const uint32_t* wu = reinterpret_cast<const uint32_t*>(wraw);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          float2 vv = unpack_bf16(vu[j]);
+          float w0 = beta_i, w1 = beta_i;
+          if (VB) {
+            float2 ww = unpack_bf16(wu[j]);
+            w0 = ww.x; w1 = ww.y;
+            dwv[2 * j] = vv.x * x[2 * j];
+            dwv[2 * j + 1] = vv.y * x[2 * j + 1];
+          } else {
+            dbv += vv.x * x[2 * j] + vv.y * x[2 * j + 1];
+          }
+          dvp[j] = pack_bf16(w0 * x[2 * j], w1 * x[2 * j + 1]);
+          pp[j] = pack_bf16(x[2 * j], x[2 * j + 1]);
+        }
+        *reinterpret_cast<uint4*>(p.dv + go + v0) = make_uint4(dvp[0], dvp[1], dvp[2], dvp[3]);
+        *reinterpret_cast<uint4*>(p.dv + go + v0 + 8) = make_uint4(dvp[4], dvp[5], dvp[6], dvp[7]);
+        if (VB) {
+          if (p.out_f32) {
+            float* o = reinterpret_cast<float*>(p.dwg) + go + v0;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+              *reinterpret_cast<float4*>(o + 4 * j) = make_float4(dwv[4 * j], dwv[4 * j + 1], dwv[4 * j + 2], dwv[4 * j + 3]);
+          } else {
+            uint32_t dwp[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) dwp[j] = pack_bf16(dwv[2 * j], dwv[2 * j + 1]);
+            bf16* o = reinterpret_cast<bf16*>(p.dwg) + go + v0;
+            *reinterpret_cast<uint4*>(o) = make_uint4(dwp[0], dwp[1], dwp[2], dwp[3]);
+            *reinterpret_cast<uint4*>(o + 8) = make_uint4(dwp[4], dwp[5], dwp[6], dwp[7]);
+          }
+        }
+        const uint32_t ptile = Smem::DOP + (v0 >> 6) * 16384 + 8192;
+        const int ch = (v0 & 63) >> 3;
+        *reinterpret_cast<uint4*>(sm + ptile + swz(i, ch)) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
+        *reinterpret_cast<uint4*>(sm + ptile + swz(i, ch + 1)) = make_uint4(pp[4], pp[5], pp[6], pp[7]);
+      }
+      sDb[i] = dbv;
+    }
+    fence_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+
+    // ---- [dAqk/scale ; -dAkk] = [dO ; P] R^T ---------------------------------------------------------
+    if (tid == 0) {
+      wait(BAR_B, 3);
+      if (alive) {
+        tc_fence_after_sync();
+        mma_kmajor(tb + TM_HD, sb + Smem::DOP, 16384, sb + Smem::R, 8192, 8, ID_KK, false);
+        mma_commit(&bars[BAR_HD]);
+      }
+    }
+    used |= 1u << BAR_HD;
+    wait(BAR_HD, 4);
+    tc_fence_after_sync();
+    if (alive) {
+      const int i = tid & 63;
+      const bool lower_incl = tid < C;  // rows 0..63: dAqk (diagonal kept); rows 64..127: dAkk (strictly lower)
+      const float mul = lower_incl ? scale : -1.f;
+      const uint32_t thi = lower_incl ? Smem::HHI : Smem::DHI, tlo = lower_incl ? Smem::HLO : Smem::DLO;
+#pragma unroll 1
+      for (int c4 = 0; c4 < 4; c4++) {
+        float x[16];
+        tmem_ld16(tlane + TM_HD + 16 * c4, x);
+        tmem_ld_wait();
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+          float y[8];
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const int col = 16 * c4 + 8 * half + j;
+            const bool keep = lower_incl ? (col <= i) : (col < i);
+            y[j] = keep ? mul * x[8 * half + j] : 0.f;
+          }
+          uint4 hi, lo;
+          split8(y, hi, lo);
+          *reinterpret_cast<uint4*>(sm + thi + swz(i, 2 * c4 + half)) = hi;
+          *reinterpret_cast<uint4*>(sm + tlo + swz(i, 2 * c4 + half)) = lo;
+        }
+      }
+    }
+    fence_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+
+    // ---- products that read h: X1 = h dO^T, X2 = Yc^T dAqk^T, X3 = -(h P^T), X4 = Yc^T dAkk^T ---------------
+    if (tid == 0) {
+      wait(BAR_C, 5);
+      if (alive) {
+        tc_fence_after_sync();
+        mma_kmajor(tb + TM_X1, sb + Smem::HS, 16384, sb + Smem::DOP, 16384, 8, ID_KK, false);
+        mma_kmajor(tb + TM_X2, sb + Smem::YHI, 0, sb + Smem::HHI, 0, 4, ID_KK, false);
+        mma_kmajor(tb + TM_X2, sb + Smem::YLO, 0, sb + Smem::HHI, 0, 4, ID_KK, true);
+        mma_kmajor(tb + TM_X2, sb + Smem::YHI, 0, sb + Smem::HLO, 0, 4, ID_KK, true);
+        mma_kmajor(tb + TM_X3, sb + Smem::HS, 16384, sb + Smem::DOP + 8192, 16384, 8, ID_KK_NEG, false);
+        mma_kmajor(tb + TM_X4, sb + Smem::YHI, 0, sb + Smem::DHI, 0, 4, ID_KK, false);
+        mma_kmajor(tb + TM_X4, sb + Smem::YLO, 0, sb + Smem::DHI, 0, 4, ID_KK, true);
+        mma_kmajor(tb + TM_X4, sb + Smem::YHI, 0, sb + Smem::DLO, 0, 4, ID_KK, true);
+        mma_commit(&bars[BAR_C12]);
+      }
+    }
+    used |= 1u << BAR_C12;
+    // chunk-end gate term, part 1: sum_v h[k,v] dh[k,v] for this thread's channel (h row from the tile, dh row
+    // from global memory)
+    float hd = 0.f;
+    if (GATE != GATE_NONE) {
+      if (tid != 0) wait(BAR_C, 6);
+      if (alive) {
+        const bf16* dhrow = p.dh + (size_t)hrow0 * 128 + (size_t)tid * 128;
+#pragma unroll 4
+        for (int ch = 0; ch < 16; ch++) {
+          uint4 a = *reinterpret_cast<const uint4*>(sm + Smem::HS + (ch >> 3) * 16384 + swz(tid, ch & 7));
+          uint4 d = *reinterpret_cast<const uint4*>(dhrow + ch * 8);
+          const uint32_t* au = reinterpret_cast<const uint32_t*>(&a);
+          const uint32_t* du = reinterpret_cast<const uint32_t*>(&d);
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            float2 x = unpack_bf16(au[j]), y = unpack_bf16(du[j]);
+            hd += x.x * y.x + x.y * y.y;
+          }
+        }
+      }
+    }
+    __syncthreads();  // every generic read of the h tile is done before dh overwrites it
+
+    // ---- dh into the h buffer, then X5 = dh R^T and X6 = Qc^T dAqk + Ec^T dAkk ----------------------------
+    if (tid == 0) {
+      wait(BAR_C12, 7);
+      if (alive) {
+        mbar_expect_tx(&bars[BAR_D], 32768);
+        for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::HS + pn * 16384, &tmDH, 64 * pn, hrow0, &bars[BAR_D]);
+      }
+      wait(BAR_D, 8);
+      if (alive) {
+        tc_fence_after_sync();
+        mma_kmajor(tb + TM_X5, sb + Smem::HS, 16384, sb + Smem::R, 8192, 8, ID_KK, false);
+        // B operand stored [reduction row i][n = j contiguous]: MN-major, a K=16 step spans two 8-row atoms
+        const uint32_t amat[6] = {Smem::QHI, Smem::QLO, Smem::QHI, Smem::EHI, Smem::ELO, Smem::EHI};
+        const uint32_t bmat[6] = {Smem::HHI, Smem::HHI, Smem::HLO, Smem::DHI, Smem::DHI, Smem::DLO};
+        for (int m = 0; m < 6; m++)
+          for (int ks = 0; ks < 4; ks++)
+            mma_f16(tb + TM_X6, smem_desc(sb + amat[m] + ks * 32, 16, 1024),
+                    smem_desc(sb + bmat[m] + ks * 2048, 8192, 1024), ID_KMN, m > 0 || ks > 0);
+        mma_commit(&bars[BAR_C3]);
+      }
+    }
+    used |= (1u << BAR_D) | (1u << BAR_C3);
+    wait(BAR_C3, 10);
+    tc_fence_after_sync();
+
+    // ---- epilogue: thread = key channel, tokens in reverse order (running reverse cumsum of the gate row) ----
+    if (alive) {
+      const int kch = tid;
+      const float gl = GATE == GATE_VECTOR ? p.g[base128 + (size_t)(C - 1) * ldt + kch] : (GATE == GATE_SCALAR ? sGs[C - 1] : 0.f);
+      const float en = GATE == GATE_NONE ? 1.f : exp2f(gl - cen);  // exp2(g_last - g) = zeta * en
+      float run = 0.f;  // reverse cumulative gate gradient of this channel
+      if (GATE != GATE_NONE) {
+        // chunk-end term: lam*sum_v h dh + sum_t k * exp2(g_last-g) * (R dh^T)
+        float colsum = 0.f;
+#pragma unroll 1
+        for (int tc4 = 0; tc4 < 4; tc4++) {
+          float x5[16];
+          tmem_ld16(tlane + TM_X5 + 16 * tc4, x5);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; j++) {
+            const int t = 16 * tc4 + j;
+            const float gt = GATE == GATE_VECTOR ? p.g[base128 + (size_t)t * ldt + kch] : sGs[t];
+            colsum += bf2f(p.k[base128 + (size_t)t * ldt + kch]) * exp2f(gl - gt) * x5[j];
+          }
+        }
+        run = exp2f(gl) * hd + colsum;
+        if (GATE == GATE_SCALAR) {
+          // scalar gate: the chunk-end term of every channel lands on the last token's sum
+          float s = run;
+#pragma unroll
+          for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+          if (lane == 0) atomicAdd(&sDgs[C - 1], s);
+          run = 0.f;
+        }
+      }
+#pragma unroll 1
+      for (int tc4 = 3; tc4 >= 0; tc4--) {
+        float x1[16], x2[16], x3[16], x4[16], x5[16], x6[16];
+        tmem_ld16(tlane + TM_X1 + 16 * tc4, x1);
+        tmem_ld16(tlane + TM_X2 + 16 * tc4, x2);
+        tmem_ld16(tlane + TM_X3 + 16 * tc4, x3);
+        tmem_ld16(tlane + TM_X4 + 16 * tc4, x4);
+        tmem_ld16(tlane + TM_X5 + 16 * tc4, x5);
+        tmem_ld16(tlane + TM_X6 + 16 * tc4, x6);
+        tmem_ld_wait();
+        float dbp[16], dgp[16];
+#pragma unroll
+        for (int j = 15; j >= 0; j--) {
+          const int t = 16 * tc4 + j;
+          const size_t go = base128 + (size_t)t * ldt + kch;
+          float al = 1.f, ze = 1.f, ga = 1.f, f = 1.f;
+          if (GATE != GATE_NONE) {
+            const float gt = GATE == GATE_VECTOR ? p.g[go] : sGs[t];
+            al = exp2f(gt - cen);
+            ze = exp2f(cen - gt);
+            ga = al * ec;
+            f = ze * en;
+          }
+          const float kk = bf2f(p.k[go]), qq = bf2f(p.q[go]);
+          const float bb = VB ? bf2f(p.bg[go]) : sBeta[t];
+          const float dq = ga * scale * x1[j] + al * x2[j];
+          const float e = ga * x3[j] + al * x4[j];   // gamma * eb
+          const float y = ze * x6[j] + f * x5[j];    // yb / gamma
+          const float dk = bb * e + y;
+          store_out1(p.dq, go, dq, p.out_f32);
+          store_out1(p.dk, go, dk, p.out_f32);
+          if (VB)
+            store_out1(p.dbg, go, kk * e, p.out_f32);
+          else
+            dbp[j] = kk * e;
+          if (GATE != GATE_NONE) {
+            const float row = qq * dq + kk * (bb * e - y);
+            if (GATE == GATE_VECTOR) {
+              run += row;
+              p.dg[go] = run;
+            } else {
+              dgp[j] = row;
+            }
+          }
+        }
+        if (!VB) {
+          float s = warp_sum16(dbp, lane);
+          if (lane < 16) atomicAdd(&sDb[16 * tc4 + lane], s);
+        }
+        if (GATE == GATE_SCALAR) {
+          float s = warp_sum16(dgp, lane);
+          if (lane < 16) atomicAdd(&sDgs[16 * tc4 + lane], s);
+        }
+      }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (alive) {
+      if (!VB && tid < C) p.dbeta[base1 + (size_t)tid * H] = sDb[tid];
+      if (GATE == GATE_SCALAR && tid == 0) {
+        float run = 0.f;
+        for (int t = C - 1; t >= 0; --t) {
+          run += sDgs[t];
+          p.dg[base1 + (size_t)t * H] = run;
+        }
+      }
+    }
+    ph ^= used;
+    alive = __syncthreads_and(alive ? 1 : 0) != 0;
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tb, 512);
+}
+
+constexpr size_t TC_SMEM = Smem::TOTAL + 1024;
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      n = 148;
+  }
+  return n;
+}
+
+template <int GATE, bool VB>
+cudaError_t run(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
+  auto kern = chunk_adjoint_tc_kernel<GATE, VB>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+  if (e != cudaSuccess) return e;
+  const int grid = p.total_chunks < sm_count() ? p.total_chunks : sm_count();
+  kern<<<grid, 128, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], p);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+// ctrl: device int[2 + total_chunks]: [0] status word, [1] number of wide-span chunks, [2..] their indices.
+cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* ctrl, cudaStream_t st) {
+  const int B = a.B, T = a.T, H = a.H, NT = T / C;
+  const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
+  CUtensorMap tm[7];
+  bool ok = encode_tmap_2d(&tm[0], a.Akk, 2, (uint64_t)H * 64, rows, (uint64_t)H * 128, 64, 64) &&
+            encode_tmap_2d(&tm[1], s.dR, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+            encode_tmap_2d(&tm[2], s.dR_lo, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+            encode_tmap_2d(&tm[3], a.d_o, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+            encode_tmap_2d(&tm[4], s.v_new, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+            encode_tmap_2d(&tm[5], s.h, 2, 128, srows, 256, 64, 128) &&
+            encode_tmap_2d(&tm[6], s.dh, 2, 128, srows, 256, 64, 128);
+  if (!ok) return cudaErrorInvalidValue;
+  cudaError_t e = cudaMemsetAsync(ctrl, 0, 2 * sizeof(int), st);
+  if (e != cudaSuccess) return e;
+  TcParams p;
+  p.q = (const bf16*)a.q; p.k = (const bf16*)a.k; p.v = (const bf16*)a.v; p.bg = (const bf16*)a.b_gate;
+  p.wg = (const bf16*)a.w_gate; p.dh = (const bf16*)s.dh; p.g = a.g; p.beta = a.beta;
+  p.dq = a.dq; p.dk = a.dk; p.dbg = a.db_gate; p.dwg = a.dw_gate; p.dv = (bf16*)a.dv; p.dg = a.dg; p.dbeta = a.dbeta;
+  p.wide_list = ctrl + 1; p.err = ctrl;
+  p.T = T; p.H = H; p.NT = NT; p.total_chunks = B * H * NT; p.out_f32 = a.out_dtype == REWY_OUT_F32;
+  p.scale = a.scale;
+  switch (a.family) {
+    case REWY_DELTA: e = run<GATE_NONE, false>(tm, p, st); break;
+    case REWY_GDN: e = run<GATE_SCALAR, false>(tm, p, st); break;
+    case REWY_KDA: e = run<GATE_VECTOR, false>(tm, p, st); break;
+    default: e = run<GATE_VECTOR, true>(tm, p, st); break;
+  }
+  if (e != cudaSuccess) return e;
+  // chunks with a wide gate span: exact pairwise path of the warp-MMA kernel, driven by the list
+  return launch_chunk_adjoint_warp(a, s, ctrl + 1, st);
+}
+
+}  // namespace rewy

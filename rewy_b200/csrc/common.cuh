@@ -23,7 +23,10 @@ struct Dims {
 cudaError_t launch_prepare(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);
 cudaError_t launch_fwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);
 cudaError_t launch_bwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);
-cudaError_t launch_chunk_adjoint(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);
+// chunk adjoint: tensor-core kernel (ctrl = device int[2 + chunks]: status word, wide-chunk count, indices)
+// followed by the warp-MMA kernel on the listed wide-span chunks; or the warp-MMA kernel on every chunk.
+cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* ctrl, cudaStream_t st);
+cudaError_t launch_chunk_adjoint_warp(const RewyBwdArgs& a, const RewyStageBuffers& s, const int* list, cudaStream_t st);
 void count_launch(int n = 1);
 
 __host__ __device__ inline int gate_mode_of(int family) {

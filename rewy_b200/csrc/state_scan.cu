@@ -4,6 +4,7 @@
 // Forward (recompute policy):  h[n] stored; v_new = u - w h[n]; h <- lam*h + kg^T v_new
 //   replaces FLA chunk_gated_delta_rule_fwd_h as called at src/fast_delta_rule/backends/backward.py:117-118.
 // Reverse:  dh[n] stored; dR = kg dh[n] + Aqk^T dO; dh <- lam*dh + scale*qg^T dO - w^T dR; dh0
+//   (dh and dR enter their products as BF16 hi+lo pairs so the FP32 state does not drift over long sequences)
 //   replaces chunk_gated_delta_rule_bwd_dhu (src/fast_delta_rule/kernels/vector_state_gpu.py:12-67 and the
 //   FLA kernel bound at backends/backward.py:120-121) with the dv = Aqk^T dO product of FLA's
 //   chunk_kda_bwd_dAv / chunk_bwd_dv_local (backends/backward.py:119) folded in.
@@ -40,7 +41,8 @@ __global__ void __launch_bounds__(256) bwd_scan_kernel(
   bf16* sDh = sAqk + C * LD64;   // [128][72]
   bf16* sDR = sDh + DK * LD64;   // [64][72]
   bf16* sDRlo = sDR + C * LD64;  // [64][72]
-  float* sLam = reinterpret_cast<float*>(sDRlo + C * LD64);
+  bf16* sDhLo = sDRlo + C * LD64; // [128][72] low part of the state, used only in the dR product
+  float* sLam = reinterpret_cast<float*>(sDhLo + DK * LD64);
 
   const int v0 = blockIdx.x * BV, bh = blockIdx.y, b = bh / H, h = bh % H;
   const int NT = T / C;
@@ -67,7 +69,10 @@ __global__ void __launch_bounds__(256) bwd_scan_kernel(
     load_tile_bf16<C, 64>(sAqk, LD64, Aqk + base64, (size_t)H * 64);
     load_lambda<GATE>(sLam, g, base128 + (size_t)(C - 1) * ldt, row0 * H + h + (size_t)(C - 1) * H);
     state.for_each_pair([&](int r, int c, float& x0, float& x1) {
-      *reinterpret_cast<uint32_t*>(sDh + r * LD64 + c) = pack_bf16(x0, x1);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(x0, x1);
+      float2 hf = __bfloat1622float2(hi);
+      *reinterpret_cast<__nv_bfloat162*>(sDh + r * LD64 + c) = hi;
+      *reinterpret_cast<uint32_t*>(sDhLo + r * LD64 + c) = pack_bf16(x0 - hf.x, x1 - hf.y);
     });
     __syncthreads();
     store_tile_bf16<DK, BV>(dh + (((size_t)b * NT + n) * H + h) * DK * DV + v0, DV, sDh, LD64);
@@ -76,6 +81,7 @@ __global__ void __launch_bounds__(256) bwd_scan_kernel(
       Tile<64, 64, 2, 4> acc;
       acc.zero();
       acc.mma<128>(Operand<false>{sKg, LD128}, Operand<true>{sDh, LD64});
+      acc.mma<128>(Operand<false>{sKg, LD128}, Operand<true>{sDhLo, LD64});
       acc.mma<64>(Operand<true>{sAqk, LD64}, Operand<true>{sDO, LD64});
       acc.for_each_pair([&](int r, int c, float& x0, float& x1) {
         __nv_bfloat162 hi = __floats2bfloat162_rn(x0, x1);
@@ -101,6 +107,7 @@ __global__ void __launch_bounds__(256) bwd_scan_kernel(
             state.acc[i][j][e] = state.acc[i][j][e] * lam + scale * tmp.acc[i][j][e];
           }
       state.mma<64>(Operand<true, true>{sW, LD128}, Operand<true>{sDR, LD64});
+      state.mma<64>(Operand<true, true>{sW, LD128}, Operand<true>{sDRlo, LD64});
     }
     __syncthreads();
   }
@@ -168,7 +175,7 @@ __global__ void __launch_bounds__(256) fwd_scan_kernel(
   }
 }
 
-constexpr size_t BWD_SMEM = (size_t)(3 * C * LD128 + 4 * C * LD64 + DK * LD64) * sizeof(bf16) + DK * sizeof(float);
+constexpr size_t BWD_SMEM = (size_t)(3 * C * LD128 + 4 * C * LD64 + 2 * DK * LD64) * sizeof(bf16) + DK * sizeof(float);
 constexpr size_t FWD_SMEM = (size_t)(2 * C * LD128 + 2 * C * LD64 + DK * LD64) * sizeof(bf16) + DK * sizeof(float);
 
 template <int GATE>

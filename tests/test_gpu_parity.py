@@ -99,7 +99,10 @@ def _run_chunk_adjoint(op, xs, saved, dh, dR, out_f32=True, passes=0, dR_lo=None
         out["dbeta"] = nan((B, T, H), torch.float32)
     for n, t in out.items():
         setattr(a, n, _capi.ptr(t))
-    call_stage("rewy_stage_chunk_adjoint", a, stage_buffers(v_new=saved["v_new"], h=saved["h"], dh=dh, dR=dR, dR_lo=dR_lo), DEV)
+    ctrl = torch.zeros(2 + B * H * (T // 64), dtype=torch.int32, device=DEV)
+    call_stage("rewy_stage_chunk_adjoint", a, stage_buffers(v_new=saved["v_new"], h=saved["h"], dh=dh, dR=dR, dR_lo=dR_lo,
+                                                            ctrl=ctrl), DEV)
+    assert ctrl[0].item() == 0, f"device status word {ctrl[0].item()}: a bounded wait gave up"
     return out
 
 
@@ -133,7 +136,7 @@ def test_stage_chunk_adjoint(op):
 def _family_call(op, xs, saved, policy_saved, out_dtype=torch.float32, passes=None):
     from rewy_b200 import backward as bw
     common = dict(q=xs["q"], k=xs["k"], v=xs["v"], scale=128 ** -0.5, initial_state=xs.get("initial_state"),
-                  do=xs["do"], dht=xs.get("dht"), out_dtype=out_dtype, intra_passes=passes)
+                  do=xs["do"], dht=xs.get("dht"), out_dtype=out_dtype, intra_passes=passes, check_status=True)
     if op == "kda":
         r = bw.kda_backward(beta=xs["beta"], Aqk=saved["Aqk"], Akk=saved["Akk"], g=saved["g_cumsum"],
                             disable_recompute=policy_saved, w=saved["w"], u=saved["u"], qg=saved["qg"], kg=saved["kg"],
@@ -172,7 +175,9 @@ def test_family_backward_bf16_outputs_and_no_states(op):
     ref = oracle_backward(op, xs, saved)
     out = _family_call(op, xs, saved, op in ("kda", "gdn2"), out_dtype=torch.bfloat16)
     assert out["dh0"] is None and out["dq"].dtype == torch.bfloat16
-    _report(_grad_errs(op, ref, out), TOL)
+    # two values that agree to 1e-3 can still round to neighbouring BF16 numbers (1 ulp = 4e-3..8e-3 relative),
+    # so the comparison in the BF16 output domain carries that floor on top of the 2e-3 of the FP32 outputs
+    _report(_grad_errs(op, ref, out), 3e-3)
 
 
 @pytest.mark.parametrize("case", ["zero_beta", "tiny_beta", "beta_over_one", "strong_gate", "weak_gate", "zero_gate",
@@ -210,7 +215,7 @@ def test_kda_edge_cases(case):
     if state:
         errs["dh0"] = nrmse(ref["dh0"], out["dh0"])
     for n, t in out.items():
-        if t is not None:
+        if torch.is_tensor(t):
             assert torch.isfinite(t.float()).all(), f"{n} not finite"
     _report(errs, 4e-3 if case in ("strong_gate", "mixed_tiles") else TOL)
 
@@ -226,12 +231,44 @@ def test_strong_gate_pairwise_path(op):
     _report(errs, 4e-3)
 
 
+@pytest.mark.parametrize("op", OPS)
+def test_tensor_core_and_warp_mma_kernels_agree(op):
+    """The production (tcgen05) chunk kernel against the warp-MMA kernel on the same inputs."""
+    xs = _inputs(op, B=2, T=192, H=3, seed=21)
+    saved = forward_saved(op, xs)
+    lib = _capi.load()
+    try:
+        assert lib.rewy_set_chunk_variant(1) == 0
+        warp = _family_call(op, xs, saved, op in ("kda", "gdn2"))
+    finally:
+        lib.rewy_set_chunk_variant(0)
+    tc = _family_call(op, xs, saved, op in ("kda", "gdn2"))
+    errs = {n: nrmse(warp[n], tc[n]) for n in warp if warp[n] is not None and n != "wide_chunks"}
+    _report(errs, 1e-3)
+
+
+def test_wide_span_chunks_are_counted():
+    xs = _inputs("kda", T=192, H=2, seed=123)
+    xs["g"][:, 64:128, 0, :32] *= 30
+    saved = forward_saved("kda", xs)
+    out = _family_call("kda", xs, saved, True)
+    assert out["wide_chunks"] == 1
+    xs = _inputs("kda", T=192, H=2, seed=123)
+    out = _family_call("kda", xs, forward_saved("kda", xs), True)
+    assert out["wide_chunks"] == 0
+
+
 def test_single_pass_intra_is_selectable_and_close():
     xs = _inputs("kda", T=128, H=2, seed=3)
     saved = forward_saved("kda", xs)
     ref = oracle_backward("kda", xs, saved)
-    out1 = _family_call("kda", xs, saved, True, passes=1)
-    out3 = _family_call("kda", xs, saved, True, passes=3)
+    lib = _capi.load()
+    try:
+        lib.rewy_set_chunk_variant(1)      # the pass count is an option of the warp-MMA kernel
+        out1 = _family_call("kda", xs, saved, True, passes=1)
+        out3 = _family_call("kda", xs, saved, True, passes=3)
+    finally:
+        lib.rewy_set_chunk_variant(0)
     e1, e3 = _grad_errs("kda", ref, out1), _grad_errs("kda", ref, out3)
     _report(e3, TOL)
     _report(e1, 6e-3)
@@ -349,5 +386,5 @@ def test_full_size_headline_properties():
     saved_s = {n: (sl(t) if n != "h" else t[b0:b0 + 1, :, h0:h0 + 1].contiguous()) for n, t in saved.items()
                if t is not None and n not in ("o", "final_state")}
     ref = oracle_backward("kda", xs_s, saved_s)
-    got = {n: sl(t) for n, t in out.items() if t is not None}
+    got = {n: sl(t) for n, t in out.items() if torch.is_tensor(t)}
     _report(_grad_errs("kda", ref, got), TOL)

@@ -132,8 +132,8 @@ def test_argument_validation_without_a_gpu():
     a.T = 128
     assert lib.rewy_kda_bwd(a, None) == 1 and b"'q'" in lib.rewy_last_error()
     assert lib.rewy_gdn_bwd(a, None) == 7
-    assert lib.rewy_bwd_workspace_bytes(_capi.KDA, _capi.SAVED, 1, 128, 1) == 128 * (512 + 2 * 256)
-    assert lib.rewy_bwd_workspace_bytes(_capi.GDN, _capi.RECOMPUTE, 1, 128, 1) == 128 * (512 + 2 * 256 + 5 * 256 + 512 + 128)
+    assert lib.rewy_bwd_workspace_bytes(_capi.KDA, _capi.SAVED, 1, 128, 1) == 256 + 128 * (512 + 2 * 256)
+    assert lib.rewy_bwd_workspace_bytes(_capi.GDN, _capi.RECOMPUTE, 1, 128, 1) == 256 + 128 * (512 + 2 * 256 + 5 * 256 + 512 + 128)
 
 
 def test_forward_producer_matches_oracle_forward_on_cpu():
