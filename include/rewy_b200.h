@@ -156,7 +156,8 @@ int rewy_set_chunk_variant(int variant);
 /* Self-test of the tensor-core plumbing (no counterpart in the reference): one CTA pushes every shared-memory
  * operand form the stages use through tcgen05.mma.  Inputs row-major on the device: A [128x128] bf16,
  * B [64x128] bf16, Akk [64x64] bf16, dR [64x128] bf16, Y [128x64] f32, H [64x64] f32.  out [128x384] f32:
- * columns 0-63 A B^T, 64-127 -(A B^T), 128-255 (rows 0-63) Akk^T dR, 256-319 Y H^T, 320-383 Y H (TF32).
+ * columns 0-63 A B^T, 64-127 -(A B^T), 128-255 (rows 0-63) Akk^T dR, 256-319 Y H^T (TF32),
+ * 320-383 A[:, :64] B[:64, :64] (BF16 with B read MN-major).
  * err: device int, non-zero if a bounded wait inside the kernel gave up. */
 int rewy_selftest_tensor_core(const void* A, const void* B, const void* Akk, const void* dR, const float* Y,
                               const float* H, float* out, int* err, rewy_stream_t stream);

@@ -113,7 +113,13 @@ void timing_mark(int set, int idx, cudaStream_t st) {
 std::atomic<int> g_chunk_variant{0};  // 0 = tensor-core kernel (+ pairwise list), 1 = warp-MMA kernel everywhere
 
 cudaError_t run_chunk_adjoint(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
-  if (g_chunk_variant.load(std::memory_order_relaxed) == 1) return launch_chunk_adjoint_warp(a, s, nullptr, st);
+  if (g_chunk_variant.load(std::memory_order_relaxed) == 1) {
+    if (s.ctrl != nullptr) {  // keep the control block readable: no status, no wide chunks
+      cudaError_t e = cudaMemsetAsync(s.ctrl, 0, 2 * sizeof(int), st);
+      if (e != cudaSuccess) return e;
+    }
+    return launch_chunk_adjoint_warp(a, s, nullptr, st);
+  }
   return launch_chunk_adjoint_tc(a, s, static_cast<int*>(s.ctrl), st);
 }
 

@@ -49,12 +49,17 @@ struct Smem {
   static constexpr uint32_t ELO = EHI + 16384;
   static constexpr uint32_t QHI = DRHI;                // Qc^T hi/lo alias the dR tiles
   static constexpr uint32_t QLO = DRLO;
+  static constexpr uint32_t VT = HHI;                  // v tile (2 panels [64 i][64 v]) aliases the dAqk tiles until P is done
   static constexpr uint32_t TILES_END = ELO + 16384;   // 204800
   static constexpr uint32_t BETA = TILES_END;          // float[64]
   static constexpr uint32_t DBETA = BETA + 256;        // float[64]
   static constexpr uint32_t GS = DBETA + 256;          // float[64] scalar gate rows
   static constexpr uint32_t DGS = GS + 256;            // float[64] per-token gate sums (scalar gate)
-  static constexpr uint32_t BARS = DGS + 256;          // 8 mbarriers
+  static constexpr uint32_t MINMAX = DGS + 256;        // float[2][2][128] per-half min / max of the gate rows
+  static constexpr uint32_t HD = MINMAX + 2048;        // float[128] sum_v h*dh per channel
+  static constexpr uint32_t END = HD + 512;            // float[128] chunk-end gate term per channel
+  static constexpr uint32_t CARRY = END + 512;         // float[128] gate cumsum carried from tokens 32..63
+  static constexpr uint32_t BARS = CARRY + 512;        // 8 mbarriers
   static constexpr uint32_t TMEM = BARS + 64;          // uint32 tmem base (+ flags)
   static constexpr uint32_t TOTAL = TMEM + 64;
 };
@@ -75,6 +80,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&r)[16]) {
       : "memory");
 #pragma unroll
   for (int i = 0; i < 16; i++) r[i] = __uint_as_float(u[i]);
+}
+
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&r)[8]) {
+  uint32_t u[8];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7])
+               : "r"(taddr)
+               : "memory");
+#pragma unroll
+  for (int i = 0; i < 8; i++) r[i] = __uint_as_float(u[i]);
 }
 
 __device__ __forceinline__ void store_out1(void* base, size_t off, float x, int out_f32) {
@@ -124,22 +139,50 @@ __device__ __forceinline__ float warp_sum16(float (&x)[16], int lane) {
   return x[0] + __shfl_xor_sync(0xffffffffu, x[0], 16);
 }
 
+
+// 256 threads: thread = (key channel kch = tid & 127, token half wg = tid >> 7).  The two warpgroups share the
+// 128 TMEM lanes (warp w reads lanes 32*(w & 3) ..) and split the columns of every accumulator.
+constexpr int TPB = 256;
+constexpr int HALF = 32;  // tokens per thread
+
+// Same for 8 values: every lane returns the warp total of value index (lane & 7) (9 shuffles).
+__device__ __forceinline__ float warp_sum8(float (&x)[8], int lane) {
+#pragma unroll
+  for (int m = 4, n = 8; m >= 1; m >>= 1, n >>= 1) {
+    const bool up = (lane & m) != 0;
+#pragma unroll
+    for (int i = 0; i < n / 2; i++) {
+      float send = up ? x[i] : x[i + n / 2];
+      float keep = up ? x[i + n / 2] : x[i];
+      x[i] = keep + __shfl_xor_sync(0xffffffffu, send, m);
+    }
+  }
+  float s = x[0] + __shfl_xor_sync(0xffffffffu, x[0], 8);
+  return s + __shfl_xor_sync(0xffffffffu, s, 16);
+}
+
 template <int GATE, bool VB>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(TPB, 1)
 chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_constant__ CUtensorMap tmDRhi,
                         const __grid_constant__ CUtensorMap tmDRlo, const __grid_constant__ CUtensorMap tmDO,
                         const __grid_constant__ CUtensorMap tmR, const __grid_constant__ CUtensorMap tmH,
-                        const __grid_constant__ CUtensorMap tmDH, const TcParams p) {
+                        const __grid_constant__ CUtensorMap tmDH, const __grid_constant__ CUtensorMap tmV,
+                        const TcParams p) {
   extern __shared__ __align__(1024) unsigned char raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   float* sBeta = reinterpret_cast<float*>(sm + Smem::BETA);
   float* sDb = reinterpret_cast<float*>(sm + Smem::DBETA);
   float* sGs = reinterpret_cast<float*>(sm + Smem::GS);
   float* sDgs = reinterpret_cast<float*>(sm + Smem::DGS);
+  float* sMinMax = reinterpret_cast<float*>(sm + Smem::MINMAX);
+  float* sHd = reinterpret_cast<float*>(sm + Smem::HD);
+  float* sEnd = reinterpret_cast<float*>(sm + Smem::END);
+  float* sCarry = reinterpret_cast<float*>(sm + Smem::CARRY);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + Smem::BARS);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + Smem::TMEM);
   const uint32_t sb = smem_u32(sm);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kch = tid & 127, wg = tid >> 7, t0 = wg * HALF;
   const int T = p.T, H = p.H, NT = p.NT;
   const size_t ldt = (size_t)H * 128;
   const float scale = p.scale;
@@ -148,7 +191,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     for (int i = 0; i < 8; i++) mbar_init(&bars[i], 1);
     fence_barrier_init();
     prefetch_tmap(&tmAkk); prefetch_tmap(&tmDRhi); prefetch_tmap(&tmDRlo); prefetch_tmap(&tmDO);
-    prefetch_tmap(&tmR); prefetch_tmap(&tmH); prefetch_tmap(&tmDH);
+    prefetch_tmap(&tmR); prefetch_tmap(&tmH); prefetch_tmap(&tmDH); prefetch_tmap(&tmV);
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, 512);
@@ -158,9 +201,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tb = *tmem_slot;
-  const uint32_t tlane = tb + ((uint32_t)(warp * 32) << 16);  // this warp's TMEM lanes
-  uint32_t ph = 0;                                            // phase bit per barrier
-  bool alive = true;                                          // false once a bounded wait gave up
+  const uint32_t tlane = tb + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's TMEM lanes
+  uint32_t ph = 0;                                                  // phase bit per barrier
+  bool alive = true;                                                // false once a bounded wait gave up
 
   constexpr uint32_t ID_P = instr_desc(FMT_BF16, 128, 128, true, true);
   constexpr uint32_t ID_KK = instr_desc(FMT_BF16, 128, 64, false, false);
@@ -170,6 +213,27 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   auto wait = [&](int b, int code) {
     if (alive) alive = mbar_wait(&bars[b], (ph >> b) & 1u, p.err, code);
   };
+  // all tile loads of one chunk (issued by thread 0): A = {Akk, dR hi/lo, v}, B = {dO, R}, C = {h}
+  auto issue_loads = [&](int chunk) {
+    const int bh = chunk / NT, n = chunk % NT, b = bh / H, h = bh % H;
+    const int row0 = b * T + n * C, hrow0 = ((b * NT + n) * H + h) * 128;
+    mbar_expect_tx(&bars[BAR_A], 8192 + 3 * 16384);
+    tma_load_2d(sm + Smem::AKK, &tmAkk, h * 64, row0, &bars[BAR_A]);
+    for (int pn = 0; pn < 2; pn++) {
+      tma_load_2d(sm + Smem::DRHI + pn * 8192, &tmDRhi, h * 128 + 64 * pn, row0, &bars[BAR_A]);
+      tma_load_2d(sm + Smem::DRLO + pn * 8192, &tmDRlo, h * 128 + 64 * pn, row0, &bars[BAR_A]);
+      tma_load_2d(sm + Smem::VT + pn * 8192, &tmV, h * 128 + 64 * pn, row0, &bars[BAR_A]);
+    }
+    mbar_expect_tx(&bars[BAR_B], 2 * 16384);
+    mbar_expect_tx(&bars[BAR_C], 32768);
+    for (int pn = 0; pn < 2; pn++) {
+      tma_load_2d(sm + Smem::DOP + pn * 16384, &tmDO, h * 128 + 64 * pn, row0, &bars[BAR_B]);
+      tma_load_2d(sm + Smem::R + pn * 8192, &tmR, h * 128 + 64 * pn, row0, &bars[BAR_B]);
+      tma_load_2d(sm + Smem::HS + pn * 16384, &tmH, 64 * pn, hrow0, &bars[BAR_C]);
+    }
+  };
+
+  if (tid == 0 && (int)blockIdx.x < p.total_chunks) issue_loads(blockIdx.x);
 
   for (int chunk = blockIdx.x; chunk < p.total_chunks && alive; chunk += gridDim.x) {
     const int bh = chunk / NT, n = chunk % NT, b = bh / H, h = bh % H;
@@ -177,49 +241,47 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     const size_t base128 = ((size_t)row0 * H + h) * 128;
     const size_t base1 = (size_t)row0 * H + h;
     const int hrow0 = ((b * NT + n) * H + h) * 128;        // first row of this chunk's state in [B*NT*H*128]
-    uint32_t used = 0;
+    const int next_chunk = chunk + gridDim.x;
+    uint32_t used = (1u << BAR_A) | (1u << BAR_B) | (1u << BAR_C);
 
-    if (tid == 0) {
-      mbar_expect_tx(&bars[BAR_A], 8192 + 2 * 16384);
-      tma_load_2d(sm + Smem::AKK, &tmAkk, h * 64, row0, &bars[BAR_A]);
-      for (int pn = 0; pn < 2; pn++) {
-        tma_load_2d(sm + Smem::DRHI + pn * 8192, &tmDRhi, h * 128 + 64 * pn, row0, &bars[BAR_A]);
-        tma_load_2d(sm + Smem::DRLO + pn * 8192, &tmDRlo, h * 128 + 64 * pn, row0, &bars[BAR_A]);
-      }
-      mbar_expect_tx(&bars[BAR_B], 2 * 16384);
-      mbar_expect_tx(&bars[BAR_C], 32768);
-      for (int pn = 0; pn < 2; pn++) {
-        tma_load_2d(sm + Smem::DOP + pn * 16384, &tmDO, h * 128 + 64 * pn, row0, &bars[BAR_B]);
-        tma_load_2d(sm + Smem::R + pn * 8192, &tmR, h * 128 + 64 * pn, row0, &bars[BAR_B]);
-        tma_load_2d(sm + Smem::HS + pn * 16384, &tmH, 64 * pn, hrow0, &bars[BAR_C]);
-      }
-    }
-    used |= (1u << BAR_A) | (1u << BAR_B) | (1u << BAR_C);
     if (tid < C) {
       sBeta[tid] = VB ? 0.f : p.beta[base1 + (size_t)tid * H];
       sDb[tid] = 0.f;
       sDgs[tid] = 0.f;
       if (GATE == GATE_SCALAR) sGs[tid] = p.g[base1 + (size_t)tid * H];
     }
+    if (tid < 128) {
+      sHd[tid] = 0.f;
+      sEnd[tid] = 0.f;
+    }
+    // ---- this thread's 32 tokens of its key channel: k and q (packed BF16 pair) and the gate row ------------
+    uint32_t kq[HALF];
+    float g[HALF];
+#pragma unroll
+    for (int j = 0; j < HALF; j++) {
+      const size_t go = base128 + (size_t)(t0 + j) * ldt + kch;
+      const uint16_t kb = *reinterpret_cast<const uint16_t*>(p.k + go), qb = *reinterpret_cast<const uint16_t*>(p.q + go);
+      kq[j] = (uint32_t)kb | ((uint32_t)qb << 16);
+      g[j] = GATE == GATE_VECTOR ? p.g[go] : 0.f;
+    }
     __syncthreads();
-
-    // ---- gate rows of this thread's key channel, centre, span -----------------------------------
-    float g[C];
     float cen = 0.f;
     bool wide = false;
     if (GATE != GATE_NONE) {
       float lo = INFINITY, hi = -INFINITY;
 #pragma unroll
-      for (int t = 0; t < C; t++) {
-        g[t] = GATE == GATE_VECTOR ? p.g[base128 + (size_t)t * ldt + tid] : sGs[t];
-        lo = fminf(lo, g[t]);
-        hi = fmaxf(hi, g[t]);
+      for (int j = 0; j < HALF; j++) {
+        if (GATE == GATE_SCALAR) g[j] = sGs[t0 + j];
+        lo = fminf(lo, g[j]);
+        hi = fmaxf(hi, g[j]);
       }
+      sMinMax[(wg * 2 + 0) * 128 + kch] = lo;
+      sMinMax[(wg * 2 + 1) * 128 + kch] = hi;
+      __syncthreads();
+      lo = fminf(lo, sMinMax[((wg ^ 1) * 2 + 0) * 128 + kch]);
+      hi = fmaxf(hi, sMinMax[((wg ^ 1) * 2 + 1) * 128 + kch]);
       cen = 0.5f * (lo + hi);
       wide = !(hi - lo < SPAN_LIMIT);
-    } else {
-#pragma unroll
-      for (int t = 0; t < C; t++) g[t] = 0.f;
     }
     if (__syncthreads_or(wide ? 1 : 0)) {
       // wide gate span: leave the chunk to the exact pairwise kernel; drain the loads already in flight
@@ -230,8 +292,11 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       }
       ph ^= used;
       alive = __syncthreads_and(alive ? 1 : 0) != 0;
+      if (tid == 0 && alive && next_chunk < p.total_chunks) issue_loads(next_chunk);
       continue;
     }
+    auto kf = [&](int j) { return __uint_as_float(kq[j] << 16); };          // k of token t0 + j
+    auto qf = [&](int j) { return __uint_as_float(kq[j] & 0xFFFF0000u); };  // q of token t0 + j
 
     // ---- P = Akk^T (dR_hi + dR_lo) ----------------------------------------------------------------
     if (tid == 0) {
@@ -249,59 +314,59 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     }
     used |= 1u << BAR_P;
 
-    // ---- operand tiles of the matrix-intra products: Yc^T and Ec^T (row = this thread's channel) ----
+    // ---- operand tiles of the matrix-intra products: Yc^T and Ec^T (row = channel, 32 token columns) ----------
     const float ec = GATE == GATE_NONE ? 1.f : exp2f(cen);
 #pragma unroll
-    for (int t8 = 0; t8 < 8; t8++) {
+    for (int t8 = 0; t8 < HALF / 8; t8++) {
       float y[8], e[8];
 #pragma unroll
       for (int j = 0; j < 8; j++) {
-        const int t = t8 * 8 + j;
-        const size_t go = base128 + (size_t)t * ldt + tid;
-        const float kk = bf2f(p.k[go]);
-        const float a = GATE == GATE_NONE ? 1.f : exp2f(g[t] - cen), z = GATE == GATE_NONE ? 1.f : exp2f(cen - g[t]);
-        const float bb = VB ? bf2f(p.bg[go]) : sBeta[t];
+        const int jj = t8 * 8 + j;
+        const float kk = kf(jj);
+        const float a = GATE == GATE_NONE ? 1.f : exp2f(g[jj] - cen), z = GATE == GATE_NONE ? 1.f : exp2f(cen - g[jj]);
+        const float bb = VB ? bf2f(p.bg[base128 + (size_t)(t0 + jj) * ldt + kch]) : sBeta[t0 + jj];
         y[j] = kk * z;
         e[j] = bb * kk * a;
       }
+      const int ch = wg * 4 + t8;
       uint4 hi, lo;
       split8(y, hi, lo);
-      *reinterpret_cast<uint4*>(sm + Smem::YHI + swz(tid, t8)) = hi;
-      *reinterpret_cast<uint4*>(sm + Smem::YLO + swz(tid, t8)) = lo;
+      *reinterpret_cast<uint4*>(sm + Smem::YHI + swz(kch, ch)) = hi;
+      *reinterpret_cast<uint4*>(sm + Smem::YLO + swz(kch, ch)) = lo;
       split8(e, hi, lo);
-      *reinterpret_cast<uint4*>(sm + Smem::EHI + swz(tid, t8)) = hi;
-      *reinterpret_cast<uint4*>(sm + Smem::ELO + swz(tid, t8)) = lo;
+      *reinterpret_cast<uint4*>(sm + Smem::EHI + swz(kch, ch)) = hi;
+      *reinterpret_cast<uint4*>(sm + Smem::ELO + swz(kch, ch)) = lo;
     }
 
-    // ---- after P: Qc^T tiles over the dead dR tiles, P epilogue on the 64 row threads ------------------
+    // ---- after P: Qc^T tiles over the dead dR tiles; P epilogue (rows 0..63 live in TMEM lanes 0..63) ---------
     wait(BAR_P, 2);
     tc_fence_after_sync();
 #pragma unroll
-    for (int t8 = 0; t8 < 8; t8++) {
+    for (int t8 = 0; t8 < HALF / 8; t8++) {
       float x[8];
 #pragma unroll
       for (int j = 0; j < 8; j++) {
-        const int t = t8 * 8 + j;
-        const float a = GATE == GATE_NONE ? 1.f : exp2f(g[t] - cen);
-        x[j] = bf2f(p.q[base128 + (size_t)t * ldt + tid]) * a;
+        const int jj = t8 * 8 + j;
+        x[j] = qf(jj) * (GATE == GATE_NONE ? 1.f : exp2f(g[jj] - cen));
       }
       uint4 hi, lo;
       split8(x, hi, lo);
-      *reinterpret_cast<uint4*>(sm + Smem::QHI + swz(tid, t8)) = hi;
-      *reinterpret_cast<uint4*>(sm + Smem::QLO + swz(tid, t8)) = lo;
+      *reinterpret_cast<uint4*>(sm + Smem::QHI + swz(kch, wg * 4 + t8)) = hi;
+      *reinterpret_cast<uint4*>(sm + Smem::QLO + swz(kch, wg * 4 + t8)) = lo;
     }
-    if (tid < C && alive) {
-      const int i = tid;
-      const size_t go = base128 + (size_t)i * ldt;
+    if ((warp & 3) < 2 && alive) {
+      const int i = kch;                   // row (token) 0..63; this warpgroup handles value columns 64*wg ..
+      const size_t go = base128 + (size_t)i * ldt + 64 * wg;
       const float beta_i = sBeta[i];
       float dbv = 0.f;
 #pragma unroll 1
-      for (int c4 = 0; c4 < 8; c4++) {
+      for (int c4 = 0; c4 < 4; c4++) {
         float x[16];
-        tmem_ld16(tlane + TM_P + 16 * c4, x);
+        tmem_ld16(tlane + TM_P + 64 * wg + 16 * c4, x);
         tmem_ld_wait();
-        const int v0 = 16 * c4;
-        uint4 vraw[2] = {*reinterpret_cast<const uint4*>(p.v + go + v0), *reinterpret_cast<const uint4*>(p.v + go + v0 + 8)};
+        const int v0 = 16 * c4;            // column inside this 64-wide panel
+        uint4 vraw[2] = {*reinterpret_cast<const uint4*>(sm + Smem::VT + wg * 8192 + swz(i, 2 * c4)),
+                         *reinterpret_cast<const uint4*>(sm + Smem::VT + wg * 8192 + swz(i, 2 * c4 + 1))};
         const uint32_t* vu = reinterpret_cast<const uint32_t*>(vraw);
         uint32_t dvp[8], pp[8];
         float dwv[16];
@@ -343,12 +408,11 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
             *reinterpret_cast<uint4*>(o + 8) = make_uint4(dwp[4], dwp[5], dwp[6], dwp[7]);
           }
         }
-        const uint32_t ptile = Smem::DOP + (v0 >> 6) * 16384 + 8192;
-        const int ch = (v0 & 63) >> 3;
-        *reinterpret_cast<uint4*>(sm + ptile + swz(i, ch)) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
-        *reinterpret_cast<uint4*>(sm + ptile + swz(i, ch + 1)) = make_uint4(pp[4], pp[5], pp[6], pp[7]);
+        const uint32_t ptile = Smem::DOP + wg * 16384 + 8192;
+        *reinterpret_cast<uint4*>(sm + ptile + swz(i, 2 * c4)) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
+        *reinterpret_cast<uint4*>(sm + ptile + swz(i, 2 * c4 + 1)) = make_uint4(pp[4], pp[5], pp[6], pp[7]);
       }
-      sDb[i] = dbv;
+      if (!VB) atomicAdd(&sDb[i], dbv);
     }
     fence_async_smem();
     tc_fence_before_sync();
@@ -368,28 +432,29 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     wait(BAR_HD, 4);
     tc_fence_after_sync();
     if (alive) {
-      const int i = tid & 63;
-      const bool lower_incl = tid < C;  // rows 0..63: dAqk (diagonal kept); rows 64..127: dAkk (strictly lower)
+      const int i = kch & 63;
+      const bool lower_incl = kch < C;  // lanes 0..63: dAqk (diagonal kept); lanes 64..127: dAkk (strictly lower)
       const float mul = lower_incl ? scale : -1.f;
       const uint32_t thi = lower_incl ? Smem::HHI : Smem::DHI, tlo = lower_incl ? Smem::HLO : Smem::DLO;
-#pragma unroll 1
-      for (int c4 = 0; c4 < 4; c4++) {
+#pragma unroll
+      for (int c4 = 0; c4 < 2; c4++) {
         float x[16];
-        tmem_ld16(tlane + TM_HD + 16 * c4, x);
+        const int col0 = 32 * wg + 16 * c4;
+        tmem_ld16(tlane + TM_HD + col0, x);
         tmem_ld_wait();
 #pragma unroll
         for (int half = 0; half < 2; half++) {
           float y[8];
 #pragma unroll
           for (int j = 0; j < 8; j++) {
-            const int col = 16 * c4 + 8 * half + j;
+            const int col = col0 + 8 * half + j;
             const bool keep = lower_incl ? (col <= i) : (col < i);
             y[j] = keep ? mul * x[8 * half + j] : 0.f;
           }
           uint4 hi, lo;
           split8(y, hi, lo);
-          *reinterpret_cast<uint4*>(sm + thi + swz(i, 2 * c4 + half)) = hi;
-          *reinterpret_cast<uint4*>(sm + tlo + swz(i, 2 * c4 + half)) = lo;
+          *reinterpret_cast<uint4*>(sm + thi + swz(i, (col0 >> 3) + half)) = hi;
+          *reinterpret_cast<uint4*>(sm + tlo + swz(i, (col0 >> 3) + half)) = lo;
         }
       }
     }
@@ -415,25 +480,28 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       }
     }
     used |= 1u << BAR_C12;
-    // chunk-end gate term, part 1: sum_v h[k,v] dh[k,v] for this thread's channel (h row from the tile, dh row
-    // from global memory)
-    float hd = 0.f;
+    // chunk-end gate term, part 1: sum_v h[k,v] dh[k,v]; this thread takes the value columns 64*wg .. of its
+    // channel (h from the tile, dh from global memory, all eight 16-byte loads in flight together)
     if (GATE != GATE_NONE) {
+      uint4 d[8];
+      const bf16* dhrow = p.dh + (size_t)hrow0 * 128 + (size_t)kch * 128 + 64 * wg;
+#pragma unroll
+      for (int ch = 0; ch < 8; ch++) d[ch] = *reinterpret_cast<const uint4*>(dhrow + ch * 8);
       if (tid != 0) wait(BAR_C, 6);
+      float hd = 0.f;
       if (alive) {
-        const bf16* dhrow = p.dh + (size_t)hrow0 * 128 + (size_t)tid * 128;
-#pragma unroll 4
-        for (int ch = 0; ch < 16; ch++) {
-          uint4 a = *reinterpret_cast<const uint4*>(sm + Smem::HS + (ch >> 3) * 16384 + swz(tid, ch & 7));
-          uint4 d = *reinterpret_cast<const uint4*>(dhrow + ch * 8);
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) {
+          uint4 a = *reinterpret_cast<const uint4*>(sm + Smem::HS + wg * 16384 + swz(kch, ch));
           const uint32_t* au = reinterpret_cast<const uint32_t*>(&a);
-          const uint32_t* du = reinterpret_cast<const uint32_t*>(&d);
+          const uint32_t* du = reinterpret_cast<const uint32_t*>(&d[ch]);
 #pragma unroll
           for (int j = 0; j < 4; j++) {
             float2 x = unpack_bf16(au[j]), y = unpack_bf16(du[j]);
             hd += x.x * y.x + x.y * y.y;
           }
         }
+        atomicAdd(&sHd[kch], hd);
       }
     }
     __syncthreads();  // every generic read of the h tile is done before dh overwrites it
@@ -462,62 +530,66 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     used |= (1u << BAR_D) | (1u << BAR_C3);
     wait(BAR_C3, 10);
     tc_fence_after_sync();
+    // every tile of this chunk has been consumed: start the next chunk's loads under the epilogue
+    if (tid == 0 && alive && next_chunk < p.total_chunks) issue_loads(next_chunk);
 
-    // ---- epilogue: thread = key channel, tokens in reverse order (running reverse cumsum of the gate row) ----
-    if (alive) {
-      const int kch = tid;
-      const float gl = GATE == GATE_VECTOR ? p.g[base128 + (size_t)(C - 1) * ldt + kch] : (GATE == GATE_SCALAR ? sGs[C - 1] : 0.f);
-      const float en = GATE == GATE_NONE ? 1.f : exp2f(gl - cen);  // exp2(g_last - g) = zeta * en
-      float run = 0.f;  // reverse cumulative gate gradient of this channel
-      if (GATE != GATE_NONE) {
-        // chunk-end term: lam*sum_v h dh + sum_t k * exp2(g_last-g) * (R dh^T)
-        float colsum = 0.f;
-#pragma unroll 1
-        for (int tc4 = 0; tc4 < 4; tc4++) {
-          float x5[16];
-          tmem_ld16(tlane + TM_X5 + 16 * tc4, x5);
-          tmem_ld_wait();
+    // ---- epilogue: thread = (key channel, token half); tokens in reverse order -----------------------------
+    const float gl = GATE == GATE_VECTOR ? p.g[base128 + (size_t)(C - 1) * ldt + kch] : (GATE == GATE_SCALAR ? sGs[C - 1] : 0.f);
+    const float en = GATE == GATE_NONE ? 1.f : exp2f(gl - cen);  // exp2(g_last - g) = zeta * en
+    if (GATE != GATE_NONE && alive) {
+      // chunk-end term, part 2: sum_t k * exp2(g_last-g) * (R dh^T) over this thread's tokens
+      float colsum = 0.f;
 #pragma unroll
-          for (int j = 0; j < 16; j++) {
-            const int t = 16 * tc4 + j;
-            const float gt = GATE == GATE_VECTOR ? p.g[base128 + (size_t)t * ldt + kch] : sGs[t];
-            colsum += bf2f(p.k[base128 + (size_t)t * ldt + kch]) * exp2f(gl - gt) * x5[j];
-          }
-        }
-        run = exp2f(gl) * hd + colsum;
-        if (GATE == GATE_SCALAR) {
-          // scalar gate: the chunk-end term of every channel lands on the last token's sum
-          float s = run;
+      for (int c4 = 0; c4 < 2; c4++) {
+        float x5[16];
+        tmem_ld16(tlane + TM_X5 + t0 + 16 * c4, x5);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; j++) colsum += kf(16 * c4 + j) * exp2f(gl - g[16 * c4 + j]) * x5[j];
+      }
+      atomicAdd(&sEnd[kch], colsum);
+    }
+    __syncthreads();
+    // Tokens 32..63 (wg 1) write their reverse-cumulated gate gradient straight away; tokens 0..31 lack the carry
+    // from the upper half, park their partial sums in the (dead) Yc tile and add the carry after the barrier.
+    float* sPark = reinterpret_cast<float*>(sm + Smem::YHI);  // [32 tokens][128 channels]
+    float run = 0.f;
+    if (alive) {
+      if (GATE != GATE_NONE) {
+        const float endk = exp2f(gl) * sHd[kch] + sEnd[kch];
+        if (GATE == GATE_VECTOR) {
+          if (wg == 1) run = endk;  // the chunk-end term sits on token 63
+        } else if (wg == 1) {
+          float s = endk;
 #pragma unroll
           for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
           if (lane == 0) atomicAdd(&sDgs[C - 1], s);
-          run = 0.f;
         }
       }
-#pragma unroll 1
-      for (int tc4 = 3; tc4 >= 0; tc4--) {
-        float x1[16], x2[16], x3[16], x4[16], x5[16], x6[16];
-        tmem_ld16(tlane + TM_X1 + 16 * tc4, x1);
-        tmem_ld16(tlane + TM_X2 + 16 * tc4, x2);
-        tmem_ld16(tlane + TM_X3 + 16 * tc4, x3);
-        tmem_ld16(tlane + TM_X4 + 16 * tc4, x4);
-        tmem_ld16(tlane + TM_X5 + 16 * tc4, x5);
-        tmem_ld16(tlane + TM_X6 + 16 * tc4, x6);
-        tmem_ld_wait();
-        float dbp[16], dgp[16];
 #pragma unroll
-        for (int j = 15; j >= 0; j--) {
-          const int t = 16 * tc4 + j;
+      for (int c8 = 3; c8 >= 0; c8--) {
+        float x1[8], x2[8], x3[8], x4[8], x5[8], x6[8];
+        const int col = t0 + 8 * c8;
+        tmem_ld8(tlane + TM_X1 + col, x1);
+        tmem_ld8(tlane + TM_X2 + col, x2);
+        tmem_ld8(tlane + TM_X3 + col, x3);
+        tmem_ld8(tlane + TM_X4 + col, x4);
+        tmem_ld8(tlane + TM_X5 + col, x5);
+        tmem_ld8(tlane + TM_X6 + col, x6);
+        tmem_ld_wait();
+        float dbp[8], dgp[8];
+#pragma unroll
+        for (int j = 7; j >= 0; j--) {
+          const int jj = 8 * c8 + j, t = t0 + jj;
           const size_t go = base128 + (size_t)t * ldt + kch;
           float al = 1.f, ze = 1.f, ga = 1.f, f = 1.f;
           if (GATE != GATE_NONE) {
-            const float gt = GATE == GATE_VECTOR ? p.g[go] : sGs[t];
-            al = exp2f(gt - cen);
-            ze = exp2f(cen - gt);
+            al = exp2f(g[jj] - cen);
+            ze = exp2f(cen - g[jj]);
             ga = al * ec;
             f = ze * en;
           }
-          const float kk = bf2f(p.k[go]), qq = bf2f(p.q[go]);
+          const float kk = kf(jj), qq = qf(jj);
           const float bb = VB ? bf2f(p.bg[go]) : sBeta[t];
           const float dq = ga * scale * x1[j] + al * x2[j];
           const float e = ga * x3[j] + al * x4[j];   // gamma * eb
@@ -533,32 +605,43 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
             const float row = qq * dq + kk * (bb * e - y);
             if (GATE == GATE_VECTOR) {
               run += row;
-              p.dg[go] = run;
+              if (wg == 1)
+                p.dg[go] = run;
+              else
+                sPark[jj * 128 + kch] = run;
             } else {
               dgp[j] = row;
             }
           }
         }
         if (!VB) {
-          float s = warp_sum16(dbp, lane);
-          if (lane < 16) atomicAdd(&sDb[16 * tc4 + lane], s);
+          float s = warp_sum8(dbp, lane);
+          if (lane < 8) atomicAdd(&sDb[col + lane], s);
         }
         if (GATE == GATE_SCALAR) {
-          float s = warp_sum16(dgp, lane);
-          if (lane < 16) atomicAdd(&sDgs[16 * tc4 + lane], s);
+          float s = warp_sum8(dgp, lane);
+          if (lane < 8) atomicAdd(&sDgs[col + lane], s);
         }
       }
+      if (GATE == GATE_VECTOR && wg == 1) sCarry[kch] = run;
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     if (alive) {
+      if (GATE == GATE_VECTOR) {
+        if (wg == 0) {
+          const float carry = sCarry[kch];
+#pragma unroll 8
+          for (int jj = 0; jj < HALF; jj++) p.dg[base128 + (size_t)jj * ldt + kch] = sPark[jj * 128 + kch] + carry;
+        }
+      }
       if (!VB && tid < C) p.dbeta[base1 + (size_t)tid * H] = sDb[tid];
       if (GATE == GATE_SCALAR && tid == 0) {
-        float run = 0.f;
+        float r = 0.f;
         for (int t = C - 1; t >= 0; --t) {
-          run += sDgs[t];
-          p.dg[base1 + (size_t)t * H] = run;
+          r += sDgs[t];
+          p.dg[base1 + (size_t)t * H] = r;
         }
       }
     }
@@ -589,7 +672,7 @@ cudaError_t run(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
   if (e != cudaSuccess) return e;
   const int grid = p.total_chunks < sm_count() ? p.total_chunks : sm_count();
-  kern<<<grid, 128, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], p);
+  kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], p);
   count_launch();
   return cudaGetLastError();
 }
@@ -600,14 +683,15 @@ cudaError_t run(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
 cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* ctrl, cudaStream_t st) {
   const int B = a.B, T = a.T, H = a.H, NT = T / C;
   const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
-  CUtensorMap tm[7];
+  CUtensorMap tm[8];
   bool ok = encode_tmap_2d(&tm[0], a.Akk, 2, (uint64_t)H * 64, rows, (uint64_t)H * 128, 64, 64) &&
             encode_tmap_2d(&tm[1], s.dR, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
             encode_tmap_2d(&tm[2], s.dR_lo, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
             encode_tmap_2d(&tm[3], a.d_o, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
             encode_tmap_2d(&tm[4], s.v_new, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
             encode_tmap_2d(&tm[5], s.h, 2, 128, srows, 256, 64, 128) &&
-            encode_tmap_2d(&tm[6], s.dh, 2, 128, srows, 256, 64, 128);
+            encode_tmap_2d(&tm[6], s.dh, 2, 128, srows, 256, 64, 128) &&
+            encode_tmap_2d(&tm[7], a.v, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64);
   if (!ok) return cudaErrorInvalidValue;
   cudaError_t e = cudaMemsetAsync(ctrl, 0, 2 * sizeof(int), st);
   if (e != cudaSuccess) return e;

@@ -105,20 +105,21 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
         uint64_t bd = smem_desc(smem_u32(s.dr[0]) + ks * 2048, 8192, 1024);
         mma_f16(tb + 128, ad, bd, id2, ks > 0);
       }
-      // T3: cols 256..319 = Y H^T (TF32, both K-major, K = 64); T4: cols 320..383 = Y H (B MN-major)
+      // T3: cols 256..319 = Y H^T (TF32, both K-major, K = 64).  (TF32 with an MN-major B operand produced zeros
+      // on B200 and is not used.)
       constexpr uint32_t id3 = instr_desc(FMT_TF32, 128, 64, false, false);
-      constexpr uint32_t id4 = instr_desc(FMT_TF32, 128, 64, false, true);
       for (int ks = 0; ks < 8; ks++) {
         uint64_t ad = smem_desc(smem_u32(s.yf[ks >> 2]) + (ks & 3) * 32, 16, 1024);
         uint64_t bd = smem_desc(smem_u32(s.hf[ks >> 2]) + (ks & 3) * 32, 16, 1024);
         mma_tf32(tb + 256, ad, bd, id3, ks > 0);
-        // B MN-major: reduction index i = rows of the stored tile; N = j in two 32-wide panels (LBO = panel pitch)
-        uint64_t bd4 = smem_desc(smem_u32(s.hf[0]) + ks * 1024, 64 * 128, 1024);
-        mma_tf32(tb + 320, ad, bd4, id4, ks > 0);
-        uint64_t bd5 = smem_desc(smem_u32(s.hf[0]) + ks * 1024, 1024, 64 * 128);
-        mma_tf32(tb + 384, ad, bd5, id4, ks > 0);
-        uint64_t bd6 = smem_desc(smem_u32(s.hf[0]) + ks * 1024, 64 * 128, 512);
-        mma_tf32(tb + 448, ad, bd6, id4, ks > 0);
+      }
+      // T4: cols 320..383 = B64 (as [k = 64 rows][n = 128]) ... BF16 B MN-major with a K-major A:
+      //     out[m, n] = sum_r A[m, r] * Bt[r, n] for r < 64, n < 64, with Bt = first 64x64 block of B (n contiguous)
+      constexpr uint32_t id4 = instr_desc(FMT_BF16, 128, 64, false, true);
+      for (int ks = 0; ks < 4; ks++) {
+        uint64_t ad = smem_desc(smem_u32(s.a128[0]) + ks * 32, 16, 1024);
+        uint64_t bd = smem_desc(smem_u32(s.b64[0]) + ks * 2048, 8192, 1024);
+        mma_f16(tb + 320, ad, bd, id4, ks > 0);
       }
       mma_commit(&s.bar_mma);
     }
@@ -127,11 +128,11 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
   tc_fence_after_sync();
   if (ok && *reinterpret_cast<volatile int*>(err) == 0) {
     // out layout: [128 rows][384 columns]
-    for (int c0 = 0; c0 < 512; c0 += 32) {
+    for (int c0 = 0; c0 < 384; c0 += 32) {
       uint32_t r[32];
       tmem_ld32(tmem_addr(tb, warp * 32, c0), r);
       tmem_ld_wait();
-      for (int j = 0; j < 32; j++) out[(size_t)tid * 512 + c0 + j] = __uint_as_float(r[j]);
+      for (int j = 0; j < 32; j++) out[(size_t)tid * 384 + c0 + j] = __uint_as_float(r[j]);
     }
   }
   tc_fence_before_sync();
@@ -146,7 +147,7 @@ using namespace rewy;
 
 // A [128x128] bf16, B [64x128] bf16, Akk [64x64] bf16, dR [64x128] bf16, Y [128x64] f32, H [64x64] f32 (row-major,
 // device); out [128x384] f32: columns 0-63 A B^T, 64-127 -(A B^T), 128-255 rows 0-63 Akk^T dR, 256-319 Y H^T,
-// 320-383 Y H.  err: device int, set non-zero if a bounded wait gave up.
+// 320-383 A[:, :64] B[:64, :64] (BF16, B MN-major).  err: device int, set non-zero if a bounded wait gave up.
 extern "C" int rewy_selftest_tensor_core(const void* A, const void* B, const void* Akk, const void* dR, const float* Y,
                                          const float* H, float* out, int* err, rewy_stream_t stream) {
   CUtensorMap tmA, tmB, tmAkk, tmDR;

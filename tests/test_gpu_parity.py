@@ -248,14 +248,20 @@ def test_tensor_core_and_warp_mma_kernels_agree(op):
 
 
 def test_wide_span_chunks_are_counted():
-    xs = _inputs("kda", T=192, H=2, seed=123)
-    xs["g"][:, 64:128, 0, :32] *= 30
-    saved = forward_saved("kda", xs)
-    out = _family_call("kda", xs, saved, True)
-    assert out["wide_chunks"] == 1
-    xs = _inputs("kda", T=192, H=2, seed=123)
-    out = _family_call("kda", xs, forward_saved("kda", xs), True)
-    assert out["wide_chunks"] == 0
+    """Chunks whose gate span is too wide for centred factors are listed in the control block and handled by the
+    exact pairwise path (the reference counts such tiles too: kernels/endpoint_intra.py:301-304)."""
+    lib = _capi.load()
+    for scale_block, expect in ((30.0, 1), (1.0, 0)):
+        xs = _inputs("kda", T=192, H=2, seed=123)
+        xs["g"][:, 64:128, 0, :32] *= scale_block
+        saved = forward_saved("kda", xs)
+        ws = torch.empty(_capi.workspace_bytes(_capi.KDA, _capi.SAVED, 1, 192, 2), dtype=torch.uint8, device=DEV)
+        from rewy_b200 import backward as bw
+        bw.kda_backward(q=xs["q"], k=xs["k"], v=xs["v"], beta=xs["beta"], Aqk=saved["Aqk"], Akk=saved["Akk"],
+                        scale=128 ** -0.5, initial_state=xs["initial_state"], do=xs["do"], dht=xs["dht"],
+                        g=saved["g_cumsum"], disable_recompute=True, w=saved["w"], u=saved["u"], qg=saved["qg"],
+                        kg=saved["kg"], v_new=saved["v_new"], h=saved["h"], workspace=ws, check_status=True)
+        assert lib.rewy_wide_chunk_count(_capi.ptr(ws), _capi.current_stream(torch.device(DEV))) == expect
 
 
 def test_single_pass_intra_is_selectable_and_close():

@@ -21,7 +21,7 @@ def test_tensor_core_operand_forms():
     A, B = rn(128, 128).bfloat16(), rn(64, 128).bfloat16()
     Akk, dR = rn(64, 64).bfloat16(), rn(64, 128).bfloat16()
     Y, H = rn(128, 64), rn(64, 64)
-    out = torch.full((128, 512), float("nan"), device=DEV)
+    out = torch.full((128, 384), float("nan"), device=DEV)
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
     lib = _capi.load()
     p = lambda t: ctypes.c_void_p(t.data_ptr())
@@ -37,7 +37,7 @@ def test_tensor_core_operand_forms():
         "-(A B^T) (negated A)": (out[:, 64:128], -(Af @ Bf.T)),
         "Akk^T dR (MN-major BF16)": (out[:64, 128:256], Akk.double().T @ dR.double()),
         "Y H^T (TF32 K-major)": (out[:, 256:320], Yt @ Ht.T),
-        "Y H (TF32, B MN-major)": (out[:, 320:384], Yt @ Ht),
+        "A B (BF16, B MN-major)": (out[:, 320:384], Af[:, :64] @ Bf[:64, :64]),
     }
     errs = {n: ((got.double() - ref).norm() / ref.norm()).item() for n, (got, ref) in want.items()}
     assert all(e < 1e-5 for e in errs.values()), errs
