@@ -20,7 +20,7 @@ EXPORTS = (
     "rewy_kda_bwd", "rewy_gdn2_bwd", "rewy_gdn_bwd", "rewy_delta_bwd", "rewy_bwd_workspace_bytes",
     "rewy_stage_prepare", "rewy_stage_fwd_scan", "rewy_stage_bwd_scan", "rewy_stage_chunk_adjoint",
     "rewy_stage_timing_enable", "rewy_stage_timing_read", "rewy_selftest_tensor_core",
-    "rewy_device_status", "rewy_wide_chunk_count", "rewy_set_chunk_variant",
+    "rewy_device_status", "rewy_wide_chunk_count", "rewy_set_chunk_variant", "rewy_set_scan_variant",
     "rewy_last_error", "rewy_version", "rewy_kernel_launch_count",
 )
 
@@ -80,6 +80,8 @@ def load():
     lib.rewy_device_status.restype = c_int
     lib.rewy_wide_chunk_count.argtypes = [c_void_p, c_void_p]
     lib.rewy_wide_chunk_count.restype = c_int
+    lib.rewy_set_scan_variant.argtypes = [c_int]
+    lib.rewy_set_scan_variant.restype = c_int
     lib.rewy_set_chunk_variant.argtypes = [c_int]
     lib.rewy_set_chunk_variant.restype = c_int
     lib.rewy_last_error.restype = c_char_p

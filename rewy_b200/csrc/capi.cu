@@ -112,10 +112,23 @@ void timing_mark(int set, int idx, cudaStream_t st) {
 
 std::atomic<int> g_chunk_variant{0};  // 0 = tensor-core kernel (+ pairwise list), 1 = warp-MMA kernel everywhere
 
+std::atomic<int> g_scan_variant{0};   // 0 = tensor-core reverse scan, 1 = warp-MMA reverse scan
+
+cudaError_t run_bwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
+  if (g_scan_variant.load(std::memory_order_relaxed) == 1 || s.ctrl == nullptr) {
+    if (s.ctrl != nullptr) {
+      cudaError_t e = cudaMemsetAsync(s.ctrl, 0, sizeof(int), st);
+      if (e != cudaSuccess) return e;
+    }
+    return launch_bwd_scan(a, s, st);
+  }
+  return launch_bwd_scan_tc(a, s, static_cast<int*>(s.ctrl), st);
+}
+
 cudaError_t run_chunk_adjoint(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
   if (g_chunk_variant.load(std::memory_order_relaxed) == 1) {
-    if (s.ctrl != nullptr) {  // keep the control block readable: no status, no wide chunks
-      cudaError_t e = cudaMemsetAsync(s.ctrl, 0, 2 * sizeof(int), st);
+    if (s.ctrl != nullptr) {  // keep the control block readable: no wide chunks
+      cudaError_t e = cudaMemsetAsync(static_cast<int*>(s.ctrl) + 1, 0, sizeof(int), st);
       if (e != cudaSuccess) return e;
     }
     return launch_chunk_adjoint_warp(a, s, nullptr, st);
@@ -163,7 +176,7 @@ int run_family(const RewyBwdArgs* a, int family, cudaStream_t st) {
     if ((rc = check_cuda(launch_fwd_scan(*a, s, st), "forward state scan")) != REWY_OK) return rc;
   }
   timing_mark(set, 2, st);
-  if ((rc = check_cuda(launch_bwd_scan(*a, s, st), "reverse state scan")) != REWY_OK) return rc;
+  if ((rc = check_cuda(run_bwd_scan(*a, s, st), "reverse state scan")) != REWY_OK) return rc;
   timing_mark(set, 3, st);
   if ((rc = check_cuda(run_chunk_adjoint(*a, s, st), "chunk adjoint")) != REWY_OK) return rc;
   timing_mark(set, 4, st);
@@ -230,7 +243,7 @@ int rewy_stage_bwd_scan(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_st
   STAGE_PTR(s->qg, "qg"); STAGE_PTR(s->kg, "kg"); STAGE_PTR(s->w, "w"); STAGE_PTR(s->Aqk, "Aqk");
   STAGE_PTR(a->d_o, "d_o"); STAGE_PTR(s->dh, "dh"); STAGE_PTR(s->dR, "dR"); STAGE_PTR(s->dR_lo, "dR_lo");
   if (a->family != REWY_DELTA) STAGE_PTR(a->g, "g");
-  return check_cuda(launch_bwd_scan(*a, *s, (cudaStream_t)st), "reverse state scan");
+  return check_cuda(run_bwd_scan(*a, *s, (cudaStream_t)st), "reverse state scan");
 }
 
 int rewy_stage_chunk_adjoint(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_stream_t st) {
@@ -247,6 +260,10 @@ int rewy_stage_chunk_adjoint(const RewyBwdArgs* a, const RewyStageBuffers* s, re
     STAGE_PTR(a->dw_gate, "dw_gate");
   } else {
     STAGE_PTR(a->beta, "beta"); STAGE_PTR(a->dbeta, "dbeta");
+  }
+  if (s->ctrl != nullptr) {  // standalone stage call: start from a clean status word
+    int rc0 = check_cuda(cudaMemsetAsync(s->ctrl, 0, sizeof(int), (cudaStream_t)st), "chunk adjoint");
+    if (rc0 != REWY_OK) return rc0;
   }
   return check_cuda(run_chunk_adjoint(*a, *s, (cudaStream_t)st), "chunk adjoint");
 }
@@ -279,6 +296,12 @@ int rewy_stage_timing_read(float* ms_sum, int* calls) {
       prev = j;
     }
   }
+  return REWY_OK;
+}
+
+int rewy_set_scan_variant(int variant) {
+  if (variant != 0 && variant != 1) return fail(REWY_ERR_UNSUPPORTED, "scan variant must be 0 or 1%s");
+  g_scan_variant.store(variant, std::memory_order_relaxed);
   return REWY_OK;
 }
 

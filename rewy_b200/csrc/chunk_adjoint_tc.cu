@@ -679,7 +679,8 @@ cudaError_t run(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
 
 }  // namespace
 
-// ctrl: device int[2 + total_chunks]: [0] status word, [1] number of wide-span chunks, [2..] their indices.
+// ctrl: device int[2 + total_chunks]: [0] status word (zeroed by the caller), [1] number of wide-span chunks,
+// [2..] their indices.
 cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* ctrl, cudaStream_t st) {
   const int B = a.B, T = a.T, H = a.H, NT = T / C;
   const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
@@ -693,7 +694,7 @@ cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers
             encode_tmap_2d(&tm[6], s.dh, 2, 128, srows, 256, 64, 128) &&
             encode_tmap_2d(&tm[7], a.v, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64);
   if (!ok) return cudaErrorInvalidValue;
-  cudaError_t e = cudaMemsetAsync(ctrl, 0, 2 * sizeof(int), st);
+  cudaError_t e = cudaMemsetAsync(ctrl + 1, 0, sizeof(int), st);  // wide-chunk count; the status word is kept
   if (e != cudaSuccess) return e;
   TcParams p;
   p.q = (const bf16*)a.q; p.k = (const bf16*)a.k; p.v = (const bf16*)a.v; p.bg = (const bf16*)a.b_gate;

@@ -1,0 +1,363 @@
+// Reverse cross-chunk state-gradient scan on the Blackwell tensor cores.
+//
+// Same recurrence as bwd_scan_kernel in state_scan.cu (the reference functions it replaces are listed there):
+//   dh[n] stored;  dR = kg dh[n] + Aqk^T dO;  dh <- lam*dh + scale*qg^T dO - w^T dR;  dh0
+// One CTA owns one (batch, head) for the whole sequence.  The 128x128 FP32 state lives in TMEM for all T/64
+// chunks, stored as S' = dh/scale so that the scale never has to be folded into a tensor-core operand:
+//   per chunk   thread (key channel, value half) reads its S' row, writes dh = scale*S' as BF16 hi/lo tiles
+//               (hi also goes to global dh[n] by a TMA store), writes lam*S' back to TMEM;
+//   MMA 1       dR^T[v,i] = sum_k dh[k,v] kg[i,k] (hi and lo) + sum_j dO[j,v] Aqk[j,i]        M=128 N=64
+//   epilogue    thread (value channel, token half) stores dR as BF16 hi/lo to global and (dR/scale) hi/lo tiles
+//   MMA 2       S'[k,v] += sum_i qg[i,k] dO[i,v] - sum_i w[i,k] (dR/scale)[i,v]                 M=128 N=128
+// Every operand that comes from global memory is used exactly as TMA lands it (MN-major or K-major).
+#include "tc05.cuh"
+
+namespace rewy {
+namespace {
+using namespace tc;
+
+struct ScanParams {
+  const float *g, *dht;
+  bf16 *dR, *dRlo;
+  float* dh0;
+  int* err;
+  int T, H, NT;
+  float scale;
+};
+
+struct SS {  // shared-memory plan, byte offsets from a 1024-byte aligned base
+  static constexpr uint32_t KG = 0;               // [64 i][128 k] two panels              16 KB
+  static constexpr uint32_t W = KG + 16384;       // [64 i][128 k]                         16 KB
+  static constexpr uint32_t QG = W + 16384;       // [64 i][128 k]                         16 KB
+  static constexpr uint32_t DO0 = QG + 16384;     // [64 i][128 v] double buffered         2 x 16 KB
+  static constexpr uint32_t AQK = DO0 + 32768;    // [64 j][64 i]                          8 KB
+  static constexpr uint32_t DHHI = AQK + 8192;    // [128 k][128 v] two panels             32 KB
+  static constexpr uint32_t DHLO = DHHI + 32768;  //                                       32 KB
+  static constexpr uint32_t DRHI = DHLO + 32768;  // (dR/scale)^T [128 v][64 i]            16 KB
+  static constexpr uint32_t DRLO = DRHI + 16384;  //                                       16 KB
+  static constexpr uint32_t BARS = DRLO + 16384;  // 8 mbarriers
+  static constexpr uint32_t TMEM = BARS + 64;
+  static constexpr uint32_t TOTAL = TMEM + 64;
+};
+static_assert(SS::TOTAL + 1024 <= 232448, "shared memory plan exceeds the per-CTA limit");
+
+enum { B_L1 = 0, B_DO0, B_DO1, B_L2, B_DR, B_S };
+constexpr uint32_t TM_S = 0, TM_DR = 128;
+constexpr int TPB = 256;
+
+__device__ __forceinline__ void tmem_ld16f(uint32_t taddr, float (&r)[16]) {
+  uint32_t u[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+        "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 16; i++) r[i] = __uint_as_float(u[i]);
+}
+__device__ __forceinline__ void tmem_st16f(uint32_t taddr, const float (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(__float_as_uint(r[0])), "r"(__float_as_uint(r[1])), "r"(__float_as_uint(r[2])), "r"(__float_as_uint(r[3])),
+      "r"(__float_as_uint(r[4])), "r"(__float_as_uint(r[5])), "r"(__float_as_uint(r[6])), "r"(__float_as_uint(r[7])),
+      "r"(__float_as_uint(r[8])), "r"(__float_as_uint(r[9])), "r"(__float_as_uint(r[10])), "r"(__float_as_uint(r[11])),
+      "r"(__float_as_uint(r[12])), "r"(__float_as_uint(r[13])), "r"(__float_as_uint(r[14])), "r"(__float_as_uint(r[15]))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// shared -> global tile store through a tensor map (bulk async group of the issuing thread)
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, int c0, int c1, const void* src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ void split8s(const float (&x)[8], uint4& hi, uint4& lo) {
+  uint32_t h[4], l[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    __nv_bfloat162 hh = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+    float2 hf = __bfloat1622float2(hh);
+    h[i] = *reinterpret_cast<uint32_t*>(&hh);
+    l[i] = pack_bf16(x[2 * i] - hf.x, x[2 * i + 1] - hf.y);
+  }
+  hi = make_uint4(h[0], h[1], h[2], h[3]);
+  lo = make_uint4(l[0], l[1], l[2], l[3]);
+}
+
+template <int GATE>
+__global__ void __launch_bounds__(TPB, 1)
+bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_constant__ CUtensorMap tmW,
+                   const __grid_constant__ CUtensorMap tmQg, const __grid_constant__ CUtensorMap tmDO,
+                   const __grid_constant__ CUtensorMap tmAqk, const __grid_constant__ CUtensorMap tmDH,
+                   const ScanParams p) {
+  extern __shared__ __align__(1024) unsigned char raw[];
+  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SS::BARS);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + SS::TMEM);
+  const uint32_t sb = smem_u32(sm);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int ch = tid & 127, wg = tid >> 7;  // channel (key row of S / value row of dR^T), column half
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+  const int T = p.T, H = p.H, NT = p.NT;
+  const size_t ldt = (size_t)H * 128;
+  const float scale = p.scale, inv_scale = 1.f / p.scale;
+
+  if (tid == 0) {
+    for (int i = 0; i < 8; i++) mbar_init(&bars[i], 1);
+    fence_barrier_init();
+    prefetch_tmap(&tmKg); prefetch_tmap(&tmW); prefetch_tmap(&tmQg); prefetch_tmap(&tmDO);
+    prefetch_tmap(&tmAqk); prefetch_tmap(&tmDH);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tb = *tmem_slot;
+  const uint32_t tlane = tb + ((uint32_t)((warp & 3) * 32) << 16);
+  uint32_t ph = 0;
+  bool alive = true;
+  auto wait = [&](int bar, int code) {
+    if (alive) alive = mbar_wait(&bars[bar], (ph >> bar) & 1u, p.err, code);
+    ph ^= 1u << bar;
+  };
+
+  auto row_of = [&](int n) { return b * T + n * C; };
+  auto issue_l1 = [&](int n, int buf) {  // kg, Aqk and dO of chunk n
+    const int row0 = row_of(n);
+    mbar_expect_tx(&bars[B_L1], 16384 + 8192);
+    for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + SS::KG + pn * 8192, &tmKg, h * 128 + 64 * pn, row0, &bars[B_L1]);
+    tma_load_2d(sm + SS::AQK, &tmAqk, h * 64, row0, &bars[B_L1]);
+    mbar_expect_tx(&bars[B_DO0 + buf], 16384);
+    for (int pn = 0; pn < 2; pn++)
+      tma_load_2d(sm + SS::DO0 + buf * 16384 + pn * 8192, &tmDO, h * 128 + 64 * pn, row0, &bars[B_DO0 + buf]);
+  };
+  auto issue_l2 = [&](int n) {  // qg, w of chunk n
+    const int row0 = row_of(n);
+    mbar_expect_tx(&bars[B_L2], 32768);
+    for (int pn = 0; pn < 2; pn++) {
+      tma_load_2d(sm + SS::QG + pn * 8192, &tmQg, h * 128 + 64 * pn, row0, &bars[B_L2]);
+      tma_load_2d(sm + SS::W + pn * 8192, &tmW, h * 128 + 64 * pn, row0, &bars[B_L2]);
+    }
+  };
+  if (tid == 0) {
+    issue_l1(NT - 1, 0);
+    issue_l2(NT - 1);
+  }
+
+  // initial state S' = dht / scale
+  {
+    const float* src = p.dht == nullptr ? nullptr : p.dht + (size_t)bh * DK * DV + (size_t)ch * DV + 64 * wg;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      float x[16];
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) {
+        float4 v4 = src == nullptr ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(src + 16 * c + j);
+        x[j] = v4.x * inv_scale; x[j + 1] = v4.y * inv_scale; x[j + 2] = v4.z * inv_scale; x[j + 3] = v4.w * inv_scale;
+      }
+      tmem_st16f(tlane + TM_S + 64 * wg + 16 * c, x);
+    }
+    tmem_st_wait();
+  }
+
+  constexpr uint32_t ID_DR_A = instr_desc(FMT_BF16, 128, 64, true, false);   // A MN-major (dh^T), B K-major (kg)
+  constexpr uint32_t ID_DR_B = instr_desc(FMT_BF16, 128, 64, true, true);    // A MN-major (dO^T), B MN-major (Aqk)
+  constexpr uint32_t ID_S_Q = instr_desc(FMT_BF16, 128, 128, true, true);    // A MN-major (qg^T), B MN-major (dO)
+  constexpr uint32_t ID_S_W = instr_desc(FMT_BF16, 128, 128, true, false, true, false);  // -(w^T) (dR/scale)^T K-major
+
+  auto load_lambda = [&](int n) -> float {  // per-channel decay of chunk n (log2 gate of its last row)
+    const int last = row_of(n) + C - 1;
+    if (GATE == GATE_VECTOR) return p.g[((size_t)last * H + h) * 128 + ch];
+    if (GATE == GATE_SCALAR) return p.g[(size_t)last * H + h];
+    return 0.f;
+  };
+  float glast = load_lambda(NT - 1);
+  int it = 0;
+  for (int n = NT - 1; n >= 0; --n, ++it) {
+    const int buf = it & 1;
+    const int row0 = row_of(n);
+    // ---- (a) state row -> dh tiles (hi to global as well), decayed state back to TMEM ---------------------
+    if (it > 0) {
+      wait(B_S, 1);
+      tc_fence_after_sync();
+      if (tid == 0 && alive) issue_l2(n);  // qg / w buffers are free once the previous state update is complete
+    }
+    const float lam = GATE == GATE_NONE ? 1.f : exp2f(glast);
+    if (n > 0) glast = load_lambda(n - 1);  // in flight for a whole chunk before it is needed
+    if (alive) {
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        float x[16];
+        tmem_ld16f(tlane + TM_S + 64 * wg + 16 * c, x);
+        tmem_ld_wait();
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+          float y[8];
+#pragma unroll
+          for (int j = 0; j < 8; j++) y[j] = scale * x[8 * half + j];
+          uint4 hi, lo;
+          split8s(y, hi, lo);
+          *reinterpret_cast<uint4*>(sm + SS::DHHI + wg * 16384 + swz(ch, 2 * c + half)) = hi;
+          *reinterpret_cast<uint4*>(sm + SS::DHLO + wg * 16384 + swz(ch, 2 * c + half)) = lo;
+        }
+        if (GATE != GATE_NONE) {
+#pragma unroll
+          for (int j = 0; j < 16; j++) x[j] *= lam;
+          tmem_st16f(tlane + TM_S + 64 * wg + 16 * c, x);
+        }
+      }
+      if (GATE != GATE_NONE) tmem_st_wait();
+    }
+    fence_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (tid == 0) {
+      const int hrow0 = ((b * NT + n) * H + h) * 128;
+      if (alive) {
+        for (int pn = 0; pn < 2; pn++) tma_store_2d(&tmDH, 64 * pn, hrow0, sm + SS::DHHI + pn * 16384);
+        bulk_commit();
+      }
+      wait(B_L1, 2);
+      wait(B_DO0 + buf, 3);
+      if (alive) {
+        tc_fence_after_sync();
+        for (int pass = 0; pass < 2; pass++) {
+          const uint32_t a = sb + (pass == 0 ? SS::DHHI : SS::DHLO);
+          for (int ks = 0; ks < 8; ks++)
+            mma_f16(tb + TM_DR, smem_desc(a + ks * 2048, 16384, 1024),
+                    smem_desc(sb + SS::KG + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024), ID_DR_A, pass > 0 || ks > 0);
+        }
+        for (int ks = 0; ks < 4; ks++)
+          mma_f16(tb + TM_DR, smem_desc(sb + SS::DO0 + buf * 16384 + ks * 2048, 8192, 1024),
+                  smem_desc(sb + SS::AQK + ks * 2048, 8192, 1024), ID_DR_B, true);
+        mma_commit(&bars[B_DR]);
+      }
+    } else {
+      ph ^= (1u << B_L1) | (1u << (B_DO0 + buf));
+    }
+    // ---- (c) dR^T row -> global dR hi/lo, (dR/scale) tiles ----------------------------------------------
+    wait(B_DR, 4);
+    tc_fence_after_sync();
+    if (tid == 0 && alive && n > 0) issue_l1(n - 1, buf ^ 1);  // kg / Aqk are free; the other dO buffer too
+    if (alive) {
+      const size_t go = ((size_t)row0 * H + h) * 128 + ch;  // + token * ldt
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        float x[16];
+        tmem_ld16f(tlane + TM_DR + 32 * wg + 16 * c, x);
+        tmem_ld_wait();
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+          float y[8];
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const float v = x[8 * half + j];
+            const int tok = 32 * wg + 16 * c + 8 * half + j;
+            const bf16 hi = f2bf(v);
+            p.dR[go + (size_t)tok * ldt] = hi;
+            p.dRlo[go + (size_t)tok * ldt] = f2bf(v - bf2f(hi));
+            y[j] = v * inv_scale;
+          }
+          uint4 hi4, lo4;
+          split8s(y, hi4, lo4);
+          const int chunk16 = 4 * wg + 2 * c + half;
+          *reinterpret_cast<uint4*>(sm + SS::DRHI + swz(ch, chunk16)) = hi4;
+          *reinterpret_cast<uint4*>(sm + SS::DRLO + swz(ch, chunk16)) = lo4;
+        }
+      }
+    }
+    if (tid == 0) bulk_wait_read0();  // the dh store has finished reading its tile before anyone rewrites it
+    fence_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    // ---- (d) state update -----------------------------------------------------------------------------
+    if (tid == 0) {
+      wait(B_L2, 5);
+      if (alive) {
+        tc_fence_after_sync();
+        for (int ks = 0; ks < 4; ks++)
+          mma_f16(tb + TM_S, smem_desc(sb + SS::QG + ks * 2048, 8192, 1024),
+                  smem_desc(sb + SS::DO0 + buf * 16384 + ks * 2048, 8192, 1024), ID_S_Q, true);
+        for (int pass = 0; pass < 2; pass++)
+          for (int ks = 0; ks < 4; ks++)
+            mma_f16(tb + TM_S, smem_desc(sb + SS::W + ks * 2048, 8192, 1024),
+                    smem_desc(sb + (pass == 0 ? SS::DRHI : SS::DRLO) + ks * 32, 16, 1024), ID_S_W, true);
+        mma_commit(&bars[B_S]);
+      }
+    } else {
+      ph ^= 1u << B_L2;
+    }
+  }
+  // ---- dh0 = scale * S' ---------------------------------------------------------------------------------
+  wait(B_S, 6);
+  tc_fence_after_sync();
+  if (p.dh0 != nullptr && alive) {
+    float* dst = p.dh0 + (size_t)bh * DK * DV + (size_t)ch * DV + 64 * wg;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      float x[16];
+      tmem_ld16f(tlane + TM_S + 64 * wg + 16 * c, x);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; j += 4)
+        *reinterpret_cast<float4*>(dst + 16 * c + j) =
+            make_float4(scale * x[j], scale * x[j + 1], scale * x[j + 2], scale * x[j + 3]);
+    }
+  }
+  if (tid == 0) bulk_wait0();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tb, 256);
+}
+
+constexpr size_t SCAN_SMEM = SS::TOTAL + 1024;
+
+template <int GATE>
+cudaError_t run(const CUtensorMap* tm, const ScanParams& p, int grid, cudaStream_t st) {
+  auto kern = bwd_scan_tc_kernel<GATE>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SCAN_SMEM);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, TPB, SCAN_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], p);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+// err: device status word (set non-zero if a bounded wait gives up); must be zero on entry.
+cudaError_t launch_bwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* err, cudaStream_t st) {
+  const int B = a.B, T = a.T, H = a.H, NT = T / C;
+  const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
+  CUtensorMap tm[6];
+  bool ok = encode_tmap_2d(&tm[0], s.kg, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+            encode_tmap_2d(&tm[1], s.w, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+            encode_tmap_2d(&tm[2], s.qg, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+            encode_tmap_2d(&tm[3], a.d_o, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+            encode_tmap_2d(&tm[4], s.Aqk, 2, (uint64_t)H * 64, rows, (uint64_t)H * 128, 64, 64) &&
+            encode_tmap_2d(&tm[5], s.dh, 2, 128, srows, 256, 64, 128);
+  if (!ok) return cudaErrorInvalidValue;
+  cudaError_t e0 = cudaMemsetAsync(err, 0, sizeof(int), st);
+  if (e0 != cudaSuccess) return e0;
+  ScanParams p;
+  p.g = a.g; p.dht = a.dht; p.dR = (bf16*)s.dR; p.dRlo = (bf16*)s.dR_lo; p.dh0 = a.dh0; p.err = err;
+  p.T = T; p.H = H; p.NT = NT; p.scale = a.scale;
+  switch (gate_mode_of(a.family)) {
+    case GATE_NONE: return run<GATE_NONE>(tm, p, B * H, st);
+    case GATE_SCALAR: return run<GATE_SCALAR>(tm, p, B * H, st);
+    default: return run<GATE_VECTOR>(tm, p, B * H, st);
+  }
+}
+
+}  // namespace rewy

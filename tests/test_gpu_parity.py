@@ -71,8 +71,10 @@ def test_stage_reverse_scan(op):
     dR_lo = torch.full_like(saved["v_new"], float("nan"))
     dh0 = torch.full((xs["k"].shape[0], xs["k"].shape[2], 128, 128), float("nan"), device=DEV)
     a.dh0 = _capi.ptr(dh0)
+    ctrl = torch.zeros(8, dtype=torch.int32, device=DEV)
     call_stage("rewy_stage_bwd_scan", a, stage_buffers(qg=saved["qg"], kg=saved["kg"], w=saved["w"], Aqk=saved["Aqk"],
-                                                       dh=dh, dR=dR, dR_lo=dR_lo), DEV)
+                                                       dh=dh, dR=dR, dR_lo=dR_lo, ctrl=ctrl), DEV)
+    assert ctrl[0].item() == 0, f"device status word {ctrl[0].item()}: a bounded wait gave up"
     # dh is stored in BF16 (inter-stage contract), dR as a BF16 hi/lo pair
     _report(dict(dh=nrmse(ref["dh"], dh), dR=nrmse(ref["dR"], dR.float() + dR_lo.float()),
                  dh0=nrmse(ref["dh0"], dh0)), 3e-3)
@@ -233,15 +235,16 @@ def test_strong_gate_pairwise_path(op):
 
 @pytest.mark.parametrize("op", OPS)
 def test_tensor_core_and_warp_mma_kernels_agree(op):
-    """The production (tcgen05) chunk kernel against the warp-MMA kernel on the same inputs."""
+    """The production (tcgen05) scan and chunk kernels against the warp-MMA kernels on the same inputs."""
     xs = _inputs(op, B=2, T=192, H=3, seed=21)
     saved = forward_saved(op, xs)
     lib = _capi.load()
     try:
-        assert lib.rewy_set_chunk_variant(1) == 0
+        assert lib.rewy_set_chunk_variant(1) == 0 and lib.rewy_set_scan_variant(1) == 0
         warp = _family_call(op, xs, saved, op in ("kda", "gdn2"))
     finally:
         lib.rewy_set_chunk_variant(0)
+        lib.rewy_set_scan_variant(0)
     tc = _family_call(op, xs, saved, op in ("kda", "gdn2"))
     errs = {n: nrmse(warp[n], tc[n]) for n in warp if warp[n] is not None and n != "wide_chunks"}
     _report(errs, 1e-3)
