@@ -149,6 +149,26 @@ int rewy_stage_timing_read(float* ms_sum4, int* calls);
 int rewy_device_status(const void* ctrl, rewy_stream_t stream);
 int rewy_wide_chunk_count(const void* ctrl, rewy_stream_t stream);
 
+/* Chunk stage for hosts that cannot allocate device memory.  It has no counterpart in the reference (whose
+ * orchestrators allocate every intermediate with torch).  Same inputs, outputs and arithmetic as
+ * rewy_stage_chunk_adjoint (always the tensor-core kernel), but the control block is NOT taken from
+ * RewyStageBuffers.ctrl (that field is ignored): it is an array inside the library, one copy per device,
+ * large enough for REWY_STATIC_MAX_CHUNKS = 65536 chunks (B*H*T/64; 256 KB of device memory that every GPU
+ * which loads the library holds until the process exits).  Meant for callers that run out of a device arena
+ * they carved up front and therefore have nothing to allocate the block with: a C/C++ host without a caching
+ * allocator, or a job whose memory plan leaves no room for allocations after start-up.  The call makes no
+ * cudaMalloc/cudaFree and no allocating library call.
+ *  - Calls with more than REWY_STATIC_MAX_CHUNKS chunks are refused with REWY_ERR_SHAPE.
+ *  - The first call on each device resolves the array's device address (cudaGetSymbolAddress, with that device
+ *    current); make that first call outside of any stream capture.
+ *  - All calls on one device share the one array, and it keeps the previous call's contents; each call clears
+ *    the two words that must start at zero.  Two calls whose kernels may overlap on the GPU (different
+ *    streams) race on it - serialise them.
+ * rewy_static_device_status reads the array's status word on the current device (SYNCHRONISES the stream). */
+#define REWY_STATIC_MAX_CHUNKS 65536
+int rewy_stage_chunk_adjoint_static(const RewyBwdArgs* args, const RewyStageBuffers* buf, rewy_stream_t stream);
+int rewy_static_device_status(rewy_stream_t stream);
+
 /* Kernel variant of the chunk stage: 0 (default) tensor-core kernel, 1 warp-MMA kernel on every chunk
  * (cross-check).  Process-wide; no counterpart in the reference. */
 int rewy_set_chunk_variant(int variant);

@@ -21,6 +21,7 @@ EXPORTS = (
     "rewy_stage_prepare", "rewy_stage_fwd_scan", "rewy_stage_bwd_scan", "rewy_stage_chunk_adjoint",
     "rewy_stage_timing_enable", "rewy_stage_timing_read", "rewy_selftest_tensor_core",
     "rewy_device_status", "rewy_wide_chunk_count", "rewy_set_chunk_variant", "rewy_set_scan_variant",
+    "rewy_stage_chunk_adjoint_static", "rewy_static_device_status",
     "rewy_last_error", "rewy_version", "rewy_kernel_launch_count",
 )
 
@@ -64,7 +65,8 @@ def load():
         fn = getattr(lib, name)
         fn.argtypes = [ctypes.POINTER(BwdArgs), c_void_p]
         fn.restype = c_int
-    for name in ("rewy_stage_prepare", "rewy_stage_fwd_scan", "rewy_stage_bwd_scan", "rewy_stage_chunk_adjoint"):
+    for name in ("rewy_stage_prepare", "rewy_stage_fwd_scan", "rewy_stage_bwd_scan", "rewy_stage_chunk_adjoint",
+                 "rewy_stage_chunk_adjoint_static"):
         fn = getattr(lib, name)
         fn.argtypes = [ctypes.POINTER(BwdArgs), ctypes.POINTER(StageBuffers), c_void_p]
         fn.restype = c_int
@@ -80,6 +82,8 @@ def load():
     lib.rewy_device_status.restype = c_int
     lib.rewy_wide_chunk_count.argtypes = [c_void_p, c_void_p]
     lib.rewy_wide_chunk_count.restype = c_int
+    lib.rewy_static_device_status.argtypes = [c_void_p]
+    lib.rewy_static_device_status.restype = c_int
     lib.rewy_set_scan_variant.argtypes = [c_int]
     lib.rewy_set_scan_variant.restype = c_int
     lib.rewy_set_chunk_variant.argtypes = [c_int]

@@ -201,6 +201,11 @@ int validate_stage(const RewyBwdArgs* a, const RewyStageBuffers* s) {
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+int report_error(int code, const char* text) {
+  snprintf(g_error, sizeof(g_error), "%s", text);
+  return code;
+}
+
 }  // namespace rewy
 
 using namespace rewy;

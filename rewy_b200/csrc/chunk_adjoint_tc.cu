@@ -10,6 +10,7 @@
 // all 64 tokens, so gate factors are per-thread scalars per token and the reverse gate cumsum is a running sum
 // inside the thread.  Chunks whose cumulative gate spans 80 or more log2 units are not processed here: their
 // indices are appended to a list that the warp-MMA kernel (exact pairwise path) works off afterwards.
+#include <cstdio>
 #include "tc05.cuh"
 
 namespace rewy {
@@ -715,3 +716,97 @@ cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers
 }
 
 }  // namespace rewy
+
+// ---------------------------------------------------------------------------------------------------
+// Chunk stage without any caller-provided or allocated scratch.
+//
+// The chunk stage needs a small control block in global memory (status word, count and list of the chunks
+// that go to the pairwise path).  Hosts that drive this library from a fixed, pre-assigned device arena - a
+// C or C++ trainer that carved all of its memory up front, or a process whose memory budget forbids any
+// further device allocation - have no allocator to take that block from.  For them the block lives in the
+// library image itself: one array per device, sized for REWY_STATIC_MAX_CHUNKS chunks.
+namespace rewy {
+namespace {
+
+constexpr int STATIC_MAX_CHUNKS = 65536;  // B*H*(T/64) the static control block can describe
+static __device__ __align__(256) int g_static_ctrl[2 + STATIC_MAX_CHUNKS];
+
+constexpr int MAX_DEVICES = 64;
+int* g_static_ctrl_ptr[MAX_DEVICES] = {};  // device address of g_static_ctrl on each device, once resolved
+
+// Resolve the device address of the array for the current device.  The array's name is only a host-side handle;
+// kernels must be given the address cudaGetSymbolAddress returns for the device that is current.
+int* static_ctrl_for_current_device(char* why, size_t why_len) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+    snprintf(why, why_len, "cannot identify the current device: %s", cudaGetErrorString(e));
+    return nullptr;
+  }
+  int* ptr = __atomic_load_n(&g_static_ctrl_ptr[dev], __ATOMIC_ACQUIRE);
+  if (ptr != nullptr) return ptr;
+  void* addr = nullptr;
+  e = cudaGetSymbolAddress(&addr, g_static_ctrl);
+  if (e != cudaSuccess || addr == nullptr) {
+    snprintf(why, why_len, "cudaGetSymbolAddress(static control block) failed on device %d: %s", dev, cudaGetErrorString(e));
+    return nullptr;
+  }
+  __atomic_store_n(&g_static_ctrl_ptr[dev], static_cast<int*>(addr), __ATOMIC_RELEASE);
+  return static_cast<int*>(addr);
+}
+
+}  // namespace
+}  // namespace rewy
+
+extern "C" int rewy_stage_chunk_adjoint_static(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_stream_t stream) {
+  using namespace rewy;
+  char why[256];
+  if (a == nullptr || s == nullptr) return report_error(REWY_ERR_NULL, "args or buffers is NULL");
+  if (a->family < REWY_DELTA || a->family > REWY_GDN2) return report_error(REWY_ERR_UNSUPPORTED, "unknown family");
+  if (a->B <= 0 || a->H <= 0 || a->T < C || a->T % C != 0) return report_error(REWY_ERR_SHAPE, "bad B/T/H");
+  const long long chunks = (long long)a->B * a->H * (a->T / C);
+  if (chunks > STATIC_MAX_CHUNKS) {
+    snprintf(why, sizeof(why),
+             "rewy_stage_chunk_adjoint_static handles at most %d chunks (B*H*T/64); this call has %lld - use "
+             "rewy_stage_chunk_adjoint with a caller-provided control block",
+             STATIC_MAX_CHUNKS, chunks);
+    return report_error(REWY_ERR_SHAPE, why);
+  }
+  const void* need[] = {a->q, a->k, a->v, a->Akk, a->d_o, s->v_new, s->h, s->dh, s->dR, s->dR_lo, a->dq, a->dk, a->dv};
+  for (const void* ptr : need) {
+    if (ptr == nullptr) return report_error(REWY_ERR_NULL, "a required input or output pointer is NULL");
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return report_error(REWY_ERR_ALIGN, "a pointer is not 16-byte aligned");
+  }
+  if (a->family != REWY_DELTA && (a->g == nullptr || a->dg == nullptr)) return report_error(REWY_ERR_NULL, "g or dg is NULL");
+  if (a->family == REWY_GDN2) {
+    if (a->b_gate == nullptr || a->w_gate == nullptr || a->db_gate == nullptr || a->dw_gate == nullptr)
+      return report_error(REWY_ERR_NULL, "a GDN2 gate pointer is NULL");
+  } else if (a->beta == nullptr || a->dbeta == nullptr) {
+    return report_error(REWY_ERR_NULL, "beta or dbeta is NULL");
+  }
+  int* ctrl = static_ctrl_for_current_device(why, sizeof(why));
+  if (ctrl == nullptr) return report_error(REWY_ERR_LAUNCH, why);
+  cudaStream_t st = (cudaStream_t)stream;
+  // The block keeps whatever the previous call left in it: the status word and the count must start at zero
+  // (the list entries beyond the count are never read).
+  cudaError_t e = cudaMemsetAsync(ctrl, 0, 2 * sizeof(int), st);
+  if (e == cudaSuccess) e = launch_chunk_adjoint_tc(*a, *s, ctrl, st);
+  if (e != cudaSuccess) {
+    snprintf(why, sizeof(why), "chunk adjoint (static control block): %s", cudaGetErrorString(e));
+    return report_error(REWY_ERR_LAUNCH, why);
+  }
+  return REWY_OK;
+}
+
+extern "C" int rewy_static_device_status(rewy_stream_t stream) {
+  using namespace rewy;
+  char why[256];
+  int* ctrl = static_ctrl_for_current_device(why, sizeof(why));
+  if (ctrl == nullptr) return report_error(REWY_ERR_LAUNCH, why);
+  int word = 0;
+  cudaError_t e = cudaMemcpyAsync(&word, ctrl, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return report_error(REWY_ERR_LAUNCH, cudaGetErrorString(e));
+  if (word != 0) return report_error(REWY_ERR_DEVICE, "a kernel gave up on a bounded wait (static control block)");
+  return REWY_OK;
+}

@@ -29,6 +29,7 @@ cudaError_t launch_bwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, 
 cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* ctrl, cudaStream_t st);
 cudaError_t launch_chunk_adjoint_warp(const RewyBwdArgs& a, const RewyStageBuffers& s, const int* list, cudaStream_t st);
 void count_launch(int n = 1);
+int report_error(int code, const char* text);  // stores the text rewy_last_error() returns; gives back `code`
 
 __host__ __device__ inline int gate_mode_of(int family) {
   return family == REWY_DELTA ? GATE_NONE : (family == REWY_GDN ? GATE_SCALAR : GATE_VECTOR);
