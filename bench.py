@@ -142,6 +142,7 @@ def main():
     import torch.distributed as dist
     from rewy_b200 import _capi, backward as bw
     from rewy_b200.forward import chunk_forward
+    from rewy_b200.sharding import shard
     from rewy_b200.synthetic import CONFIGS, make_inputs
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -164,7 +165,7 @@ def main():
     H = cfg["H"]
     # weak scaling: rank r owns batches [r*B, (r+1)*B) of a global batch of world*B sequences
     xs = make_inputs(op, world * B, T, H, seed=42, device=dev, gate=cfg["gate"], gate_scale=cfg["gate_scale"],
-                     state=cfg["state"], batches=range(rank * B, (rank + 1) * B))
+                     state=cfg["state"], batches=shard(world * B, H, world, rank)[0])
     saved = chunk_forward(op, xs["q"], xs["k"], xs["v"], g=xs["g"], beta=xs["beta"], initial_state=xs["initial_state"],
                           output_final_state=False)
     beta32 = xs["beta"].float()
