@@ -56,11 +56,11 @@ struct Smem {
   static constexpr uint32_t DBETA = BETA + 256;        // float[64]
   static constexpr uint32_t GS = DBETA + 256;          // float[64] scalar gate rows
   static constexpr uint32_t DGS = GS + 256;            // float[64] per-token gate sums (scalar gate)
-  static constexpr uint32_t MINMAX = DGS + 256;        // float[2][2][128] per-half min / max of the gate rows
-  static constexpr uint32_t HD = MINMAX + 2048;        // float[128] sum_v h*dh per channel
+  static constexpr uint32_t MINMAX = DGS + 256;        // float[4][2][128] per-quarter min / max of the gate rows
+  static constexpr uint32_t HD = MINMAX + 4096;        // float[128] sum_v h*dh per channel
   static constexpr uint32_t END = HD + 512;            // float[128] chunk-end gate term per channel
-  static constexpr uint32_t CARRY = END + 512;         // float[128] gate cumsum carried from tokens 32..63
-  static constexpr uint32_t BARS = CARRY + 512;        // 8 mbarriers
+  static constexpr uint32_t CARRY = END + 512;         // float[4][128] gate-gradient totals of each token quarter
+  static constexpr uint32_t BARS = CARRY + 2048;        // 8 mbarriers
   static constexpr uint32_t TMEM = BARS + 64;          // uint32 tmem base (+ flags)
   static constexpr uint32_t TOTAL = TMEM + 64;
 };
@@ -141,10 +141,17 @@ __device__ __forceinline__ float warp_sum16(float (&x)[16], int lane) {
 }
 
 
-// 256 threads: thread = (key channel kch = tid & 127, token half wg = tid >> 7).  The two warpgroups share the
-// 128 TMEM lanes (warp w reads lanes 32*(w & 3) ..) and split the columns of every accumulator.
-constexpr int TPB = 256;
-constexpr int HALF = 32;  // tokens per thread
+// 512 threads: thread = (key channel kch = tid & 127, token quarter wg = tid >> 7).  The four warpgroups share
+// the 128 TMEM lanes (warp w reads lanes 32*(w & 3) ..) and split the columns of every accumulator.
+constexpr int TPB = 512;
+constexpr int NWG = 4;
+constexpr int HALF = 16;  // tokens per thread
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 // Same for 8 values: every lane returns the warp total of value index (lane & 7) (9 shuffles).
 __device__ __forceinline__ float warp_sum8(float (&x)[8], int lane) {
@@ -279,8 +286,11 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       sMinMax[(wg * 2 + 0) * 128 + kch] = lo;
       sMinMax[(wg * 2 + 1) * 128 + kch] = hi;
       __syncthreads();
-      lo = fminf(lo, sMinMax[((wg ^ 1) * 2 + 0) * 128 + kch]);
-      hi = fmaxf(hi, sMinMax[((wg ^ 1) * 2 + 1) * 128 + kch]);
+#pragma unroll
+      for (int w2 = 0; w2 < NWG; w2++) {
+        lo = fminf(lo, sMinMax[(w2 * 2 + 0) * 128 + kch]);
+        hi = fmaxf(hi, sMinMax[(w2 * 2 + 1) * 128 + kch]);
+      }
       cen = 0.5f * (lo + hi);
       wide = !(hi - lo < SPAN_LIMIT);
     }
@@ -316,7 +326,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     used |= 1u << BAR_P;
 
     // ---- operand tiles of the matrix-intra products: Yc^T and Ec^T (row = channel, 32 token columns) ----------
-    const float ec = GATE == GATE_NONE ? 1.f : exp2f(cen);
+    const float ec = GATE == GATE_NONE ? 1.f : ex2(cen);
 #pragma unroll
     for (int t8 = 0; t8 < HALF / 8; t8++) {
       float y[8], e[8];
@@ -324,12 +334,12 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       for (int j = 0; j < 8; j++) {
         const int jj = t8 * 8 + j;
         const float kk = kf(jj);
-        const float a = GATE == GATE_NONE ? 1.f : exp2f(g[jj] - cen), z = GATE == GATE_NONE ? 1.f : exp2f(cen - g[jj]);
+        const float a = GATE == GATE_NONE ? 1.f : ex2(g[jj] - cen), z = GATE == GATE_NONE ? 1.f : ex2(cen - g[jj]);
         const float bb = VB ? bf2f(p.bg[base128 + (size_t)(t0 + jj) * ldt + kch]) : sBeta[t0 + jj];
         y[j] = kk * z;
         e[j] = bb * kk * a;
       }
-      const int ch = wg * 4 + t8;
+      const int ch = wg * (HALF / 8) + t8;
       uint4 hi, lo;
       split8(y, hi, lo);
       *reinterpret_cast<uint4*>(sm + Smem::YHI + swz(kch, ch)) = hi;
@@ -348,26 +358,27 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 #pragma unroll
       for (int j = 0; j < 8; j++) {
         const int jj = t8 * 8 + j;
-        x[j] = qf(jj) * (GATE == GATE_NONE ? 1.f : exp2f(g[jj] - cen));
+        x[j] = qf(jj) * (GATE == GATE_NONE ? 1.f : ex2(g[jj] - cen));
       }
       uint4 hi, lo;
       split8(x, hi, lo);
-      *reinterpret_cast<uint4*>(sm + Smem::QHI + swz(kch, wg * 4 + t8)) = hi;
-      *reinterpret_cast<uint4*>(sm + Smem::QLO + swz(kch, wg * 4 + t8)) = lo;
+      *reinterpret_cast<uint4*>(sm + Smem::QHI + swz(kch, wg * (HALF / 8) + t8)) = hi;
+      *reinterpret_cast<uint4*>(sm + Smem::QLO + swz(kch, wg * (HALF / 8) + t8)) = lo;
     }
     if ((warp & 3) < 2 && alive) {
-      const int i = kch;                   // row (token) 0..63; this warpgroup handles value columns 64*wg ..
-      const size_t go = base128 + (size_t)i * ldt + 64 * wg;
+      const int i = kch;                   // row (token) 0..63; this warpgroup handles value columns 32*wg ..
+      const size_t go = base128 + (size_t)i * ldt;
       const float beta_i = sBeta[i];
       float dbv = 0.f;
 #pragma unroll 1
-      for (int c4 = 0; c4 < 4; c4++) {
+      for (int c4 = 0; c4 < 2; c4++) {
         float x[16];
-        tmem_ld16(tlane + TM_P + 64 * wg + 16 * c4, x);
+        const int v0 = 32 * wg + 16 * c4;  // value column
+        const int vp = v0 >> 6, vc = (v0 & 63) >> 3;  // 64-wide panel, 16-byte chunk inside its rows
+        tmem_ld16(tlane + TM_P + v0, x);
         tmem_ld_wait();
-        const int v0 = 16 * c4;            // column inside this 64-wide panel
-        uint4 vraw[2] = {*reinterpret_cast<const uint4*>(sm + Smem::VT + wg * 8192 + swz(i, 2 * c4)),
-                         *reinterpret_cast<const uint4*>(sm + Smem::VT + wg * 8192 + swz(i, 2 * c4 + 1))};
+        uint4 vraw[2] = {*reinterpret_cast<const uint4*>(sm + Smem::VT + vp * 8192 + swz(i, vc)),
+                         *reinterpret_cast<const uint4*>(sm + Smem::VT + vp * 8192 + swz(i, vc + 1))};
         const uint32_t* vu = reinterpret_cast<const uint32_t*>(vraw);
         uint32_t dvp[8], pp[8];
         float dwv[16];
@@ -409,9 +420,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
             *reinterpret_cast<uint4*>(o + 8) = make_uint4(dwp[4], dwp[5], dwp[6], dwp[7]);
           }
         }
-        const uint32_t ptile = Smem::DOP + wg * 16384 + 8192;
-        *reinterpret_cast<uint4*>(sm + ptile + swz(i, 2 * c4)) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
-        *reinterpret_cast<uint4*>(sm + ptile + swz(i, 2 * c4 + 1)) = make_uint4(pp[4], pp[5], pp[6], pp[7]);
+        const uint32_t ptile = Smem::DOP + vp * 16384 + 8192;
+        *reinterpret_cast<uint4*>(sm + ptile + swz(i, vc)) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
+        *reinterpret_cast<uint4*>(sm + ptile + swz(i, vc + 1)) = make_uint4(pp[4], pp[5], pp[6], pp[7]);
       }
       if (!VB) atomicAdd(&sDb[i], dbv);
     }
@@ -437,10 +448,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       const bool lower_incl = kch < C;  // lanes 0..63: dAqk (diagonal kept); lanes 64..127: dAkk (strictly lower)
       const float mul = lower_incl ? scale : -1.f;
       const uint32_t thi = lower_incl ? Smem::HHI : Smem::DHI, tlo = lower_incl ? Smem::HLO : Smem::DLO;
-#pragma unroll
-      for (int c4 = 0; c4 < 2; c4++) {
+      {
         float x[16];
-        const int col0 = 32 * wg + 16 * c4;
+        const int col0 = 16 * wg;
         tmem_ld16(tlane + TM_HD + col0, x);
         tmem_ld_wait();
 #pragma unroll
@@ -481,19 +491,19 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       }
     }
     used |= 1u << BAR_C12;
-    // chunk-end gate term, part 1: sum_v h[k,v] dh[k,v]; this thread takes the value columns 64*wg .. of its
-    // channel (h from the tile, dh from global memory, all eight 16-byte loads in flight together)
+    // chunk-end gate term, part 1: sum_v h[k,v] dh[k,v]; this thread takes the value columns 32*wg .. of its
+    // channel (h from the tile, dh from global memory, all four 16-byte loads in flight together)
     if (GATE != GATE_NONE) {
-      uint4 d[8];
-      const bf16* dhrow = p.dh + (size_t)hrow0 * 128 + (size_t)kch * 128 + 64 * wg;
+      uint4 d[4];
+      const bf16* dhrow = p.dh + (size_t)hrow0 * 128 + (size_t)kch * 128 + 32 * wg;
 #pragma unroll
-      for (int ch = 0; ch < 8; ch++) d[ch] = *reinterpret_cast<const uint4*>(dhrow + ch * 8);
+      for (int ch = 0; ch < 4; ch++) d[ch] = *reinterpret_cast<const uint4*>(dhrow + ch * 8);
       if (tid != 0) wait(BAR_C, 6);
       float hd = 0.f;
       if (alive) {
 #pragma unroll
-        for (int ch = 0; ch < 8; ch++) {
-          uint4 a = *reinterpret_cast<const uint4*>(sm + Smem::HS + wg * 16384 + swz(kch, ch));
+        for (int ch = 0; ch < 4; ch++) {
+          uint4 a = *reinterpret_cast<const uint4*>(sm + Smem::HS + (wg >> 1) * 16384 + swz(kch, (wg & 1) * 4 + ch));
           const uint32_t* au = reinterpret_cast<const uint32_t*>(&a);
           const uint32_t* du = reinterpret_cast<const uint32_t*>(&d[ch]);
 #pragma unroll
@@ -536,31 +546,31 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 
     // ---- epilogue: thread = (key channel, token half); tokens in reverse order -----------------------------
     const float gl = GATE == GATE_VECTOR ? p.g[base128 + (size_t)(C - 1) * ldt + kch] : (GATE == GATE_SCALAR ? sGs[C - 1] : 0.f);
-    const float en = GATE == GATE_NONE ? 1.f : exp2f(gl - cen);  // exp2(g_last - g) = zeta * en
+    const float en = GATE == GATE_NONE ? 1.f : ex2(gl - cen);  // exp2(g_last - g) = zeta * en
     if (GATE != GATE_NONE && alive) {
       // chunk-end term, part 2: sum_t k * exp2(g_last-g) * (R dh^T) over this thread's tokens
       float colsum = 0.f;
-#pragma unroll
-      for (int c4 = 0; c4 < 2; c4++) {
+      {
         float x5[16];
-        tmem_ld16(tlane + TM_X5 + t0 + 16 * c4, x5);
+        tmem_ld16(tlane + TM_X5 + t0, x5);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 16; j++) colsum += kf(16 * c4 + j) * exp2f(gl - g[16 * c4 + j]) * x5[j];
+        for (int j = 0; j < 16; j++) colsum += kf(j) * ex2(gl - g[j]) * x5[j];
       }
       atomicAdd(&sEnd[kch], colsum);
     }
     __syncthreads();
-    // Tokens 32..63 (wg 1) write their reverse-cumulated gate gradient straight away; tokens 0..31 lack the carry
-    // from the upper half, park their partial sums in the (dead) Yc tile and add the carry after the barrier.
-    float* sPark = reinterpret_cast<float*>(sm + Smem::YHI);  // [32 tokens][128 channels]
+    // Tokens 48..63 (wg 3) write their reverse-cumulated gate gradient straight away; the other quarters lack the
+    // totals of the tokens after them, park their partial sums in the (dead) Yc tiles and add the carry after
+    // the barrier.
+    float* sPark = reinterpret_cast<float*>(sm + Smem::YHI);  // [48 tokens][128 channels] over YHI + YLO
     float run = 0.f;
     if (alive) {
       if (GATE != GATE_NONE) {
-        const float endk = exp2f(gl) * sHd[kch] + sEnd[kch];
+        const float endk = ex2(gl) * sHd[kch] + sEnd[kch];
         if (GATE == GATE_VECTOR) {
-          if (wg == 1) run = endk;  // the chunk-end term sits on token 63
-        } else if (wg == 1) {
+          if (wg == NWG - 1) run = endk;  // the chunk-end term sits on token 63
+        } else if (wg == NWG - 1) {
           float s = endk;
 #pragma unroll
           for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
@@ -568,7 +578,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         }
       }
 #pragma unroll
-      for (int c8 = 3; c8 >= 0; c8--) {
+      for (int c8 = HALF / 8 - 1; c8 >= 0; c8--) {
         float x1[8], x2[8], x3[8], x4[8], x5[8], x6[8];
         const int col = t0 + 8 * c8;
         tmem_ld8(tlane + TM_X1 + col, x1);
@@ -585,8 +595,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           const size_t go = base128 + (size_t)t * ldt + kch;
           float al = 1.f, ze = 1.f, ga = 1.f, f = 1.f;
           if (GATE != GATE_NONE) {
-            al = exp2f(g[jj] - cen);
-            ze = exp2f(cen - g[jj]);
+            al = ex2(g[jj] - cen);
+            ze = ex2(cen - g[jj]);
             ga = al * ec;
             f = ze * en;
           }
@@ -606,10 +616,10 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
             const float row = qq * dq + kk * (bb * e - y);
             if (GATE == GATE_VECTOR) {
               run += row;
-              if (wg == 1)
+              if (wg == NWG - 1)
                 p.dg[go] = run;
               else
-                sPark[jj * 128 + kch] = run;
+                sPark[t * 128 + kch] = run;
             } else {
               dgp[j] = row;
             }
@@ -624,17 +634,19 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           if (lane < 8) atomicAdd(&sDgs[col + lane], s);
         }
       }
-      if (GATE == GATE_VECTOR && wg == 1) sCarry[kch] = run;
+      if (GATE == GATE_VECTOR) sCarry[wg * 128 + kch] = run;
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     if (alive) {
       if (GATE == GATE_VECTOR) {
-        if (wg == 0) {
-          const float carry = sCarry[kch];
-#pragma unroll 8
-          for (int jj = 0; jj < HALF; jj++) p.dg[base128 + (size_t)jj * ldt + kch] = sPark[jj * 128 + kch] + carry;
+        if (wg < NWG - 1) {
+          float carry = 0.f;
+          for (int w2 = wg + 1; w2 < NWG; w2++) carry += sCarry[w2 * 128 + kch];
+#pragma unroll
+          for (int jj = 0; jj < HALF; jj++)
+            p.dg[base128 + (size_t)(t0 + jj) * ldt + kch] = sPark[(t0 + jj) * 128 + kch] + carry;
         }
       }
       if (!VB && tid < C) p.dbeta[base1 + (size_t)tid * H] = sDb[tid];
