@@ -12,7 +12,8 @@ CSRC = PKG / "csrc"
 OBJ = PKG / "csrc" / "build"
 LIB = PKG / "librewy_b200.so"
 SOURCES = ("capi.cu", "prepare.cu", "state_scan.cu", "state_scan_tc.cu", "chunk_adjoint.cu", "chunk_adjoint_tc.cu", "tc_selftest.cu")
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+EXTRA = os.environ.get("REWY_NVCC_EXTRA", "").split()
+NVCC_FLAGS = EXTRA + ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "--expt-extended-lambda", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 
 

@@ -29,6 +29,9 @@ struct TcParams {
   int* err;         // device status word: non-zero if a bounded wait gave up
   int T, H, NT, total_chunks, out_f32;
   float scale;
+#ifdef REWY_PHASE_PROF
+  long long* prof;  // [CTA 0's chunk iteration][16] clock64 stamps (debug builds only)
+#endif
 };
 
 // Shared-memory plan (byte offsets from a 1024-byte aligned base).  "t0" tiles are dead once P is computed and
@@ -50,6 +53,9 @@ struct Smem {
   static constexpr uint32_t ELO = EHI + 16384;
   static constexpr uint32_t QHI = DRHI;                // Qc^T hi/lo alias the dR tiles
   static constexpr uint32_t QLO = DRLO;
+  static constexpr uint32_t KT = DHI;                  // k tile of the NEXT chunk (2 panels [64 t][64 k]) lands in the dAkk
+                                                       // tiles once they are dead and is read into registers at chunk start
+  static constexpr uint32_t GT = EHI;                  // g tile of the next chunk (4 panels [64 t][32 k] FP32) lands in the Ec tiles
   static constexpr uint32_t VT = HHI;                  // v tile (2 panels [64 i][64 v]) aliases the dAqk tiles until P is done
   static constexpr uint32_t TILES_END = ELO + 16384;   // 204800
   static constexpr uint32_t BETA = TILES_END;          // float[64]
@@ -61,12 +67,12 @@ struct Smem {
   static constexpr uint32_t END = HD + 512;            // float[128] chunk-end gate term per channel
   static constexpr uint32_t CARRY = END + 512;         // float[4][128] gate-gradient totals of each token quarter
   static constexpr uint32_t BARS = CARRY + 2048;        // 8 mbarriers
-  static constexpr uint32_t TMEM = BARS + 64;          // uint32 tmem base (+ flags)
+  static constexpr uint32_t TMEM = BARS + 128;         // uint32 tmem base (+ flags)
   static constexpr uint32_t TOTAL = TMEM + 64;
 };
 static_assert(Smem::TOTAL + 1024 <= 232448, "shared memory plan exceeds the 227 KB per-CTA limit");
 
-enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C12, BAR_C3 };
+enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C12, BAR_C3, BAR_G, NUM_BARS };
 
 // TMEM column plan (512 columns allocated).
 constexpr uint32_t TM_P = 0, TM_HD = 128, TM_X1 = 192, TM_X2 = 256, TM_X3 = 320, TM_X4 = 384, TM_X5 = 0, TM_X6 = 64;
@@ -175,6 +181,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
                         const __grid_constant__ CUtensorMap tmDRlo, const __grid_constant__ CUtensorMap tmDO,
                         const __grid_constant__ CUtensorMap tmR, const __grid_constant__ CUtensorMap tmH,
                         const __grid_constant__ CUtensorMap tmDH, const __grid_constant__ CUtensorMap tmV,
+                        const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmG,
                         const TcParams p) {
   extern __shared__ __align__(1024) unsigned char raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
@@ -196,10 +203,11 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   const float scale = p.scale;
 
   if (tid == 0) {
-    for (int i = 0; i < 8; i++) mbar_init(&bars[i], 1);
+    for (int i = 0; i < NUM_BARS; i++) mbar_init(&bars[i], 1);
     fence_barrier_init();
     prefetch_tmap(&tmAkk); prefetch_tmap(&tmDRhi); prefetch_tmap(&tmDRlo); prefetch_tmap(&tmDO);
     prefetch_tmap(&tmR); prefetch_tmap(&tmH); prefetch_tmap(&tmDH); prefetch_tmap(&tmV);
+    prefetch_tmap(&tmK); prefetch_tmap(&tmG);
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, 512);
@@ -225,6 +233,11 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   auto issue_loads = [&](int chunk) {
     const int bh = chunk / NT, n = chunk % NT, b = bh / H, h = bh % H;
     const int row0 = b * T + n * C, hrow0 = ((b * NT + n) * H + h) * 128;
+    // k (and the vector gate) of the chunk: read into registers at its start, so they get a barrier of their own
+    mbar_expect_tx(&bars[BAR_G], 16384 + (GATE == GATE_VECTOR ? 32768 : 0));
+    for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::KT + pn * 8192, &tmK, h * 128 + 64 * pn, row0, &bars[BAR_G]);
+    if (GATE == GATE_VECTOR)
+      for (int pn = 0; pn < 4; pn++) tma_load_2d(sm + Smem::GT + pn * 8192, &tmG, h * 128 + 32 * pn, row0, &bars[BAR_G]);
     mbar_expect_tx(&bars[BAR_A], 8192 + 3 * 16384);
     tma_load_2d(sm + Smem::AKK, &tmAkk, h * 64, row0, &bars[BAR_A]);
     for (int pn = 0; pn < 2; pn++) {
@@ -243,14 +256,21 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 
   if (tid == 0 && (int)blockIdx.x < p.total_chunks) issue_loads(blockIdx.x);
 
+#ifdef REWY_PHASE_PROF
+  int prof_it = 0;
+#define STAMP(i) do { if (p.prof != nullptr && blockIdx.x == 0 && tid == 32 && prof_it < 64) p.prof[prof_it * 16 + (i)] = clock64(); } while (0)
+#else
+#define STAMP(i) do {} while (0)
+#endif
   for (int chunk = blockIdx.x; chunk < p.total_chunks && alive; chunk += gridDim.x) {
+    STAMP(0);
     const int bh = chunk / NT, n = chunk % NT, b = bh / H, h = bh % H;
     const int row0 = b * T + n * C;                       // first token row in [B*T]
     const size_t base128 = ((size_t)row0 * H + h) * 128;
     const size_t base1 = (size_t)row0 * H + h;
     const int hrow0 = ((b * NT + n) * H + h) * 128;        // first row of this chunk's state in [B*NT*H*128]
     const int next_chunk = chunk + gridDim.x;
-    uint32_t used = (1u << BAR_A) | (1u << BAR_B) | (1u << BAR_C);
+    uint32_t used = (1u << BAR_A) | (1u << BAR_B) | (1u << BAR_C) | (1u << BAR_G);
 
     if (tid < C) {
       sBeta[tid] = VB ? 0.f : p.beta[base1 + (size_t)tid * H];
@@ -265,14 +285,21 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     // ---- this thread's 32 tokens of its key channel: k and q (packed BF16 pair) and the gate row ------------
     uint32_t kq[HALF];
     float g[HALF];
+    // q straight from global memory (first needed after P, so its latency hides behind the tile building);
+    // k and g from the tiles TMA brought in while the previous chunk's epilogue ran
+#pragma unroll
+    for (int j = 0; j < HALF; j++)
+      kq[j] = (uint32_t)(*reinterpret_cast<const uint16_t*>(p.q + base128 + (size_t)(t0 + j) * ldt + kch)) << 16;
+    wait(BAR_G, 11);
 #pragma unroll
     for (int j = 0; j < HALF; j++) {
-      const size_t go = base128 + (size_t)(t0 + j) * ldt + kch;
-      const uint16_t kb = *reinterpret_cast<const uint16_t*>(p.k + go), qb = *reinterpret_cast<const uint16_t*>(p.q + go);
-      kq[j] = (uint32_t)kb | ((uint32_t)qb << 16);
-      g[j] = GATE == GATE_VECTOR ? p.g[go] : 0.f;
+      const int t = t0 + j;
+      kq[j] |= *reinterpret_cast<const uint16_t*>(sm + Smem::KT + (kch >> 6) * 8192 + swz(t, (kch & 63) >> 3) + (kch & 7) * 2);
+      g[j] = GATE == GATE_VECTOR
+                 ? *reinterpret_cast<const float*>(sm + Smem::GT + (kch >> 5) * 8192 + swz(t, (kch & 31) >> 2) + (kch & 3) * 4)
+                 : 0.f;
     }
-    __syncthreads();
+    __syncthreads();  // everyone has its k / g out of the tiles before they are rebuilt as Ec / dAkk tiles
     float cen = 0.f;
     bool wide = false;
     if (GATE != GATE_NONE) {
@@ -306,6 +333,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       if (tid == 0 && alive && next_chunk < p.total_chunks) issue_loads(next_chunk);
       continue;
     }
+    STAMP(1);  // operands in registers, centre known
     auto kf = [&](int j) { return __uint_as_float(kq[j] << 16); };          // k of token t0 + j
     auto qf = [&](int j) { return __uint_as_float(kq[j] & 0xFFFF0000u); };  // q of token t0 + j
 
@@ -349,9 +377,11 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       *reinterpret_cast<uint4*>(sm + Smem::ELO + swz(kch, ch)) = lo;
     }
 
+    STAMP(2);  // Yc/Ec tiles built
     // ---- after P: Qc^T tiles over the dead dR tiles; P epilogue (rows 0..63 live in TMEM lanes 0..63) ---------
     wait(BAR_P, 2);
     tc_fence_after_sync();
+    STAMP(3);  // P ready
 #pragma unroll
     for (int t8 = 0; t8 < HALF / 8; t8++) {
       float x[8];
@@ -431,6 +461,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     __syncthreads();
     tc_fence_after_sync();
 
+    STAMP(4);  // P epilogue + Qc done (after barrier)
     // ---- [dAqk/scale ; -dAkk] = [dO ; P] R^T ---------------------------------------------------------
     if (tid == 0) {
       wait(BAR_B, 3);
@@ -441,8 +472,20 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       }
     }
     used |= 1u << BAR_HD;
+    // this thread's 32 values of its channel's h row, kept for the chunk-end gate term (the h tile is gone by
+    // the time dh arrives)
+    uint4 hrow[4];
+    if (GATE != GATE_NONE) {
+      wait(BAR_C, 6);
+#pragma unroll
+      for (int ch = 0; ch < 4; ch++)
+        hrow[ch] = *reinterpret_cast<const uint4*>(sm + Smem::HS + (wg >> 1) * 16384 + swz(kch, (wg & 1) * 4 + ch));
+    } else if (tid == 0) {
+      wait(BAR_C, 6);
+    }
     wait(BAR_HD, 4);
     tc_fence_after_sync();
+    STAMP(5);  // HD ready
     if (alive) {
       const int i = kch & 63;
       const bool lower_incl = kch < C;  // lanes 0..63: dAqk (diagonal kept); lanes 64..127: dAkk (strictly lower)
@@ -474,73 +517,64 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     __syncthreads();
     tc_fence_after_sync();
 
+    STAMP(6);  // HD epilogue done (after barrier)
     // ---- products that read h: X1 = h dO^T, X2 = Yc^T dAqk^T, X3 = -(h P^T), X4 = Yc^T dAkk^T ---------------
-    if (tid == 0) {
-      wait(BAR_C, 5);
-      if (alive) {
-        tc_fence_after_sync();
-        mma_kmajor(tb + TM_X1, sb + Smem::HS, 16384, sb + Smem::DOP, 16384, 8, ID_KK, false);
-        mma_kmajor(tb + TM_X2, sb + Smem::YHI, 0, sb + Smem::HHI, 0, 4, ID_KK, false);
-        mma_kmajor(tb + TM_X2, sb + Smem::YLO, 0, sb + Smem::HHI, 0, 4, ID_KK, true);
-        mma_kmajor(tb + TM_X2, sb + Smem::YHI, 0, sb + Smem::HLO, 0, 4, ID_KK, true);
-        mma_kmajor(tb + TM_X3, sb + Smem::HS, 16384, sb + Smem::DOP + 8192, 16384, 8, ID_KK_NEG, false);
-        mma_kmajor(tb + TM_X4, sb + Smem::YHI, 0, sb + Smem::DHI, 0, 4, ID_KK, false);
-        mma_kmajor(tb + TM_X4, sb + Smem::YLO, 0, sb + Smem::DHI, 0, 4, ID_KK, true);
-        mma_kmajor(tb + TM_X4, sb + Smem::YHI, 0, sb + Smem::DLO, 0, 4, ID_KK, true);
-        mma_commit(&bars[BAR_C12]);
-      }
+    if (tid == 0 && alive) {
+      tc_fence_after_sync();
+      // the two products that read h go first and get a commit of their own: as soon as they are done the h
+      // buffer can take dh, while the matrix-intra products still run
+      mma_kmajor(tb + TM_X1, sb + Smem::HS, 16384, sb + Smem::DOP, 16384, 8, ID_KK, false);
+      mma_kmajor(tb + TM_X3, sb + Smem::HS, 16384, sb + Smem::DOP + 8192, 16384, 8, ID_KK_NEG, false);
+      mma_commit(&bars[BAR_C12]);
+      mma_kmajor(tb + TM_X2, sb + Smem::YHI, 0, sb + Smem::HHI, 0, 4, ID_KK, false);
+      mma_kmajor(tb + TM_X2, sb + Smem::YLO, 0, sb + Smem::HHI, 0, 4, ID_KK, true);
+      mma_kmajor(tb + TM_X2, sb + Smem::YHI, 0, sb + Smem::HLO, 0, 4, ID_KK, true);
+      mma_kmajor(tb + TM_X4, sb + Smem::YHI, 0, sb + Smem::DHI, 0, 4, ID_KK, false);
+      mma_kmajor(tb + TM_X4, sb + Smem::YLO, 0, sb + Smem::DHI, 0, 4, ID_KK, true);
+      mma_kmajor(tb + TM_X4, sb + Smem::YHI, 0, sb + Smem::DLO, 0, 4, ID_KK, true);
     }
-    used |= 1u << BAR_C12;
-    // chunk-end gate term, part 1: sum_v h[k,v] dh[k,v]; this thread takes the value columns 32*wg .. of its
-    // channel (h from the tile, dh from global memory, all four 16-byte loads in flight together)
-    if (GATE != GATE_NONE) {
-      uint4 d[4];
-      const bf16* dhrow = p.dh + (size_t)hrow0 * 128 + (size_t)kch * 128 + 32 * wg;
-#pragma unroll
-      for (int ch = 0; ch < 4; ch++) d[ch] = *reinterpret_cast<const uint4*>(dhrow + ch * 8);
-      if (tid != 0) wait(BAR_C, 6);
-      float hd = 0.f;
-      if (alive) {
-#pragma unroll
-        for (int ch = 0; ch < 4; ch++) {
-          uint4 a = *reinterpret_cast<const uint4*>(sm + Smem::HS + (wg >> 1) * 16384 + swz(kch, (wg & 1) * 4 + ch));
-          const uint32_t* au = reinterpret_cast<const uint32_t*>(&a);
-          const uint32_t* du = reinterpret_cast<const uint32_t*>(&d[ch]);
-#pragma unroll
-          for (int j = 0; j < 4; j++) {
-            float2 x = unpack_bf16(au[j]), y = unpack_bf16(du[j]);
-            hd += x.x * y.x + x.y * y.y;
-          }
-        }
-        atomicAdd(&sHd[kch], hd);
-      }
-    }
-    __syncthreads();  // every generic read of the h tile is done before dh overwrites it
-
-    // ---- dh into the h buffer, then X5 = dh R^T and X6 = Qc^T dAqk + Ec^T dAkk ----------------------------
+    used |= (1u << BAR_C12) | (1u << BAR_D) | (1u << BAR_C3);
     if (tid == 0) {
       wait(BAR_C12, 7);
       if (alive) {
         mbar_expect_tx(&bars[BAR_D], 32768);
         for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::HS + pn * 16384, &tmDH, 64 * pn, hrow0, &bars[BAR_D]);
       }
-      wait(BAR_D, 8);
-      if (alive) {
-        tc_fence_after_sync();
-        mma_kmajor(tb + TM_X5, sb + Smem::HS, 16384, sb + Smem::R, 8192, 8, ID_KK, false);
-        // B operand stored [reduction row i][n = j contiguous]: MN-major, a K=16 step spans two 8-row atoms
-        const uint32_t amat[6] = {Smem::QHI, Smem::QLO, Smem::QHI, Smem::EHI, Smem::ELO, Smem::EHI};
-        const uint32_t bmat[6] = {Smem::HHI, Smem::HHI, Smem::HLO, Smem::DHI, Smem::DHI, Smem::DLO};
-        for (int m = 0; m < 6; m++)
-          for (int ks = 0; ks < 4; ks++)
-            mma_f16(tb + TM_X6, smem_desc(sb + amat[m] + ks * 32, 16, 1024),
-                    smem_desc(sb + bmat[m] + ks * 2048, 8192, 1024), ID_KMN, m > 0 || ks > 0);
-        mma_commit(&bars[BAR_C3]);
-      }
     }
-    used |= (1u << BAR_D) | (1u << BAR_C3);
+    wait(BAR_D, 8);
+    STAMP(7);  // dh tile landed
+    if (tid == 0 && alive) {
+      tc_fence_after_sync();
+      mma_kmajor(tb + TM_X5, sb + Smem::HS, 16384, sb + Smem::R, 8192, 8, ID_KK, false);
+      // B operand stored [reduction row i][n = j contiguous]: MN-major, a K=16 step spans two 8-row atoms
+      const uint32_t amat[6] = {Smem::QHI, Smem::QLO, Smem::QHI, Smem::EHI, Smem::ELO, Smem::EHI};
+      const uint32_t bmat[6] = {Smem::HHI, Smem::HHI, Smem::HLO, Smem::DHI, Smem::DHI, Smem::DLO};
+      for (int m = 0; m < 6; m++)
+        for (int ks = 0; ks < 4; ks++)
+          mma_f16(tb + TM_X6, smem_desc(sb + amat[m] + ks * 32, 16, 1024),
+                  smem_desc(sb + bmat[m] + ks * 2048, 8192, 1024), ID_KMN, m > 0 || ks > 0);
+      mma_commit(&bars[BAR_C3]);
+    }
+    // chunk-end gate term, part 1: sum_v h[k,v] dh[k,v] over this thread's 32 value columns (h from registers,
+    // dh from the tile that just landed)
+    if (GATE != GATE_NONE && alive) {
+      float hd = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 4; ch++) {
+        uint4 d = *reinterpret_cast<const uint4*>(sm + Smem::HS + (wg >> 1) * 16384 + swz(kch, (wg & 1) * 4 + ch));
+        const uint32_t* au = reinterpret_cast<const uint32_t*>(&hrow[ch]);
+        const uint32_t* du = reinterpret_cast<const uint32_t*>(&d);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          float2 x = unpack_bf16(au[j]), y = unpack_bf16(du[j]);
+          hd += x.x * y.x + x.y * y.y;
+        }
+      }
+      atomicAdd(&sHd[kch], hd);
+    }
     wait(BAR_C3, 10);
     tc_fence_after_sync();
+    STAMP(8);  // all products done
     // every tile of this chunk has been consumed: start the next chunk's loads under the epilogue
     if (tid == 0 && alive && next_chunk < p.total_chunks) issue_loads(next_chunk);
 
@@ -564,6 +598,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     // totals of the tokens after them, park their partial sums in the (dead) Yc tiles and add the carry after
     // the barrier.
     float* sPark = reinterpret_cast<float*>(sm + Smem::YHI);  // [48 tokens][128 channels] over YHI + YLO
+    STAMP(9);  // colsum done
     float run = 0.f;
     if (alive) {
       if (GATE != GATE_NONE) {
@@ -658,8 +693,12 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         }
       }
     }
+    STAMP(10);  // epilogue done
     ph ^= used;
     alive = __syncthreads_and(alive ? 1 : 0) != 0;
+#ifdef REWY_PHASE_PROF
+    prof_it++;
+#endif
   }
 
   tc_fence_before_sync();
@@ -667,6 +706,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   if (warp == 0) tmem_dealloc(tb, 512);
 }
 
+#ifdef REWY_PHASE_PROF
+long long* g_prof = nullptr;
+#endif
 constexpr size_t TC_SMEM = Smem::TOTAL + 1024;
 
 int sm_count() {
@@ -685,7 +727,7 @@ cudaError_t run(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
   if (e != cudaSuccess) return e;
   const int grid = p.total_chunks < sm_count() ? p.total_chunks : sm_count();
-  kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], p);
+  kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9], p);
   count_launch();
   return cudaGetLastError();
 }
@@ -697,7 +739,7 @@ cudaError_t run(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
 cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* ctrl, cudaStream_t st) {
   const int B = a.B, T = a.T, H = a.H, NT = T / C;
   const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
-  CUtensorMap tm[8];
+  CUtensorMap tm[10];
   bool ok = encode_tmap_2d(&tm[0], a.Akk, 2, (uint64_t)H * 64, rows, (uint64_t)H * 128, 64, 64) &&
             encode_tmap_2d(&tm[1], s.dR, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
             encode_tmap_2d(&tm[2], s.dR_lo, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
@@ -705,7 +747,12 @@ cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers
             encode_tmap_2d(&tm[4], s.v_new, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
             encode_tmap_2d(&tm[5], s.h, 2, 128, srows, 256, 64, 128) &&
             encode_tmap_2d(&tm[6], s.dh, 2, 128, srows, 256, 64, 128) &&
-            encode_tmap_2d(&tm[7], a.v, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64);
+            encode_tmap_2d(&tm[7], a.v, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+            encode_tmap_2d(&tm[8], a.k, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64);
+  if (ok && gate_mode_of(a.family) == GATE_VECTOR)
+    ok = encode_tmap_2d(&tm[9], a.g, 4, (uint64_t)H * 128, rows, (uint64_t)H * 512, 32, 64);
+  else
+    tm[9] = tm[8];  // never dereferenced without a vector gate
   if (!ok) return cudaErrorInvalidValue;
   cudaError_t e = cudaMemsetAsync(ctrl + 1, 0, sizeof(int), st);  // wide-chunk count; the status word is kept
   if (e != cudaSuccess) return e;
@@ -714,6 +761,9 @@ cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers
   p.wg = (const bf16*)a.w_gate; p.dh = (const bf16*)s.dh; p.g = a.g; p.beta = a.beta;
   p.dq = a.dq; p.dk = a.dk; p.dbg = a.db_gate; p.dwg = a.dw_gate; p.dv = (bf16*)a.dv; p.dg = a.dg; p.dbeta = a.dbeta;
   p.wide_list = ctrl + 1; p.err = ctrl;
+#ifdef REWY_PHASE_PROF
+  p.prof = g_prof;
+#endif
   p.T = T; p.H = H; p.NT = NT; p.total_chunks = B * H * NT; p.out_f32 = a.out_dtype == REWY_OUT_F32;
   p.scale = a.scale;
   switch (a.family) {
@@ -822,3 +872,7 @@ extern "C" int rewy_static_device_status(rewy_stream_t stream) {
   if (word != 0) return report_error(REWY_ERR_DEVICE, "a kernel gave up on a bounded wait (static control block)");
   return REWY_OK;
 }
+
+#ifdef REWY_PHASE_PROF
+extern "C" void rewy_debug_set_prof(long long* ptr) { rewy::g_prof = ptr; }
+#endif
