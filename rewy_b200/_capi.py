@@ -9,7 +9,8 @@ from ctypes import c_char_p, c_float, c_int, c_int32, c_size_t, c_void_p
 from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
-LIB_PATH = PKG / "librewy_b200.so"
+import os as _os
+LIB_PATH = PKG / _os.environ.get("REWY_LIB_NAME", "librewy_b200.so")
 
 DELTA, GDN, KDA, GDN2 = 0, 1, 2, 3
 FAMILY_ID = {"delta": DELTA, "gdn": GDN, "kda": KDA, "gdn2": GDN2}

@@ -51,8 +51,9 @@ struct Smem {
   static constexpr uint32_t YLO = YHI + 16384;
   static constexpr uint32_t EHI = YLO + 16384;         // Ec^T hi
   static constexpr uint32_t ELO = EHI + 16384;
-  static constexpr uint32_t QHI = DRHI;                // Qc^T hi/lo alias the dR tiles
-  static constexpr uint32_t QLO = DRLO;
+  static constexpr uint32_t DHT = DRHI;                // dh tile (2 panels [128 k][64 v]) takes the dR tiles once P is done
+  static constexpr uint32_t QHI = HS;                  // Qc^T hi/lo take the h buffer once the products that read h are done
+  static constexpr uint32_t QLO = HS + 16384;
   static constexpr uint32_t KT = DHI;                  // k tile of the NEXT chunk (2 panels [64 t][64 k]) lands in the dAkk
                                                        // tiles once they are dead and is read into registers at chunk start
   static constexpr uint32_t GT = EHI;                  // g tile of the next chunk (4 panels [64 t][32 k] FP32) lands in the Ec tiles
@@ -175,7 +176,7 @@ __device__ __forceinline__ float warp_sum8(float (&x)[8], int lane) {
   return s + __shfl_xor_sync(0xffffffffu, s, 16);
 }
 
-template <int GATE, bool VB>
+template <int GATE, bool VB, bool OUTF32>
 __global__ void __launch_bounds__(TPB, 1)
 chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_constant__ CUtensorMap tmDRhi,
                         const __grid_constant__ CUtensorMap tmDRlo, const __grid_constant__ CUtensorMap tmDO,
@@ -287,14 +288,14 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     float g[HALF];
     // q straight from global memory (first needed after P, so its latency hides behind the tile building);
     // k and g from the tiles TMA brought in while the previous chunk's epilogue ran
+    uint32_t qv[HALF];  // merged into kq only when q is first needed, so nothing waits on these loads early
 #pragma unroll
-    for (int j = 0; j < HALF; j++)
-      kq[j] = (uint32_t)(*reinterpret_cast<const uint16_t*>(p.q + base128 + (size_t)(t0 + j) * ldt + kch)) << 16;
+    for (int j = 0; j < HALF; j++) qv[j] = *reinterpret_cast<const uint16_t*>(p.q + base128 + (size_t)(t0 + j) * ldt + kch);
     wait(BAR_G, 11);
 #pragma unroll
     for (int j = 0; j < HALF; j++) {
       const int t = t0 + j;
-      kq[j] |= *reinterpret_cast<const uint16_t*>(sm + Smem::KT + (kch >> 6) * 8192 + swz(t, (kch & 63) >> 3) + (kch & 7) * 2);
+      kq[j] = *reinterpret_cast<const uint16_t*>(sm + Smem::KT + (kch >> 6) * 8192 + swz(t, (kch & 63) >> 3) + (kch & 7) * 2);
       g[j] = GATE == GATE_VECTOR
                  ? *reinterpret_cast<const float*>(sm + Smem::GT + (kch >> 5) * 8192 + swz(t, (kch & 31) >> 2) + (kch & 3) * 4)
                  : 0.f;
@@ -353,48 +354,33 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     }
     used |= 1u << BAR_P;
 
-    // ---- operand tiles of the matrix-intra products: Yc^T and Ec^T (row = channel, 32 token columns) ----------
+    // ---- operand tile Yc^T of the matrix-intra products (row = channel, 16 token columns per thread) ---------
     const float ec = GATE == GATE_NONE ? 1.f : ex2(cen);
 #pragma unroll
     for (int t8 = 0; t8 < HALF / 8; t8++) {
-      float y[8], e[8];
+      float y[8];
 #pragma unroll
       for (int j = 0; j < 8; j++) {
         const int jj = t8 * 8 + j;
-        const float kk = kf(jj);
-        const float a = GATE == GATE_NONE ? 1.f : ex2(g[jj] - cen), z = GATE == GATE_NONE ? 1.f : ex2(cen - g[jj]);
-        const float bb = VB ? bf2f(p.bg[base128 + (size_t)(t0 + jj) * ldt + kch]) : sBeta[t0 + jj];
-        y[j] = kk * z;
-        e[j] = bb * kk * a;
+        y[j] = kf(jj) * (GATE == GATE_NONE ? 1.f : ex2(cen - g[jj]));
       }
       const int ch = wg * (HALF / 8) + t8;
       uint4 hi, lo;
       split8(y, hi, lo);
       *reinterpret_cast<uint4*>(sm + Smem::YHI + swz(kch, ch)) = hi;
       *reinterpret_cast<uint4*>(sm + Smem::YLO + swz(kch, ch)) = lo;
-      split8(e, hi, lo);
-      *reinterpret_cast<uint4*>(sm + Smem::EHI + swz(kch, ch)) = hi;
-      *reinterpret_cast<uint4*>(sm + Smem::ELO + swz(kch, ch)) = lo;
     }
 
-    STAMP(2);  // Yc/Ec tiles built
-    // ---- after P: Qc^T tiles over the dead dR tiles; P epilogue (rows 0..63 live in TMEM lanes 0..63) ---------
+    STAMP(2);  // Yc tiles built
+    // ---- after P: dh takes the place of the dR tiles; P epilogue (rows 0..63 live in TMEM lanes 0..63) ---------
     wait(BAR_P, 2);
     tc_fence_after_sync();
     STAMP(3);  // P ready
-#pragma unroll
-    for (int t8 = 0; t8 < HALF / 8; t8++) {
-      float x[8];
-#pragma unroll
-      for (int j = 0; j < 8; j++) {
-        const int jj = t8 * 8 + j;
-        x[j] = qf(jj) * (GATE == GATE_NONE ? 1.f : ex2(g[jj] - cen));
-      }
-      uint4 hi, lo;
-      split8(x, hi, lo);
-      *reinterpret_cast<uint4*>(sm + Smem::QHI + swz(kch, wg * (HALF / 8) + t8)) = hi;
-      *reinterpret_cast<uint4*>(sm + Smem::QLO + swz(kch, wg * (HALF / 8) + t8)) = lo;
+    if (tid == 0 && alive) {
+      mbar_expect_tx(&bars[BAR_D], 32768);
+      for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::DHT + pn * 16384, &tmDH, 64 * pn, hrow0, &bars[BAR_D]);
     }
+    used |= 1u << BAR_D;
     if ((warp & 3) < 2 && alive) {
       const int i = kch;                   // row (token) 0..63; this warpgroup handles value columns 32*wg ..
       const size_t go = base128 + (size_t)i * ldt;
@@ -436,7 +422,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         *reinterpret_cast<uint4*>(p.dv + go + v0) = make_uint4(dvp[0], dvp[1], dvp[2], dvp[3]);
         *reinterpret_cast<uint4*>(p.dv + go + v0 + 8) = make_uint4(dvp[4], dvp[5], dvp[6], dvp[7]);
         if (VB) {
-          if (p.out_f32) {
+          if (OUTF32) {
             float* o = reinterpret_cast<float*>(p.dwg) + go + v0;
 #pragma unroll
             for (int j = 0; j < 4; j++)
@@ -472,6 +458,21 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       }
     }
     used |= 1u << BAR_HD;
+    // Ec^T tiles while the stacked product runs (first needed by the last product group)
+#pragma unroll
+    for (int t8 = 0; t8 < HALF / 8; t8++) {
+      float e[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int jj = t8 * 8 + j;
+        const float bb = VB ? bf2f(p.bg[base128 + (size_t)(t0 + jj) * ldt + kch]) : sBeta[t0 + jj];
+        e[j] = bb * kf(jj) * (GATE == GATE_NONE ? 1.f : ex2(g[jj] - cen));
+      }
+      uint4 hi, lo;
+      split8(e, hi, lo);
+      *reinterpret_cast<uint4*>(sm + Smem::EHI + swz(kch, wg * (HALF / 8) + t8)) = hi;
+      *reinterpret_cast<uint4*>(sm + Smem::ELO + swz(kch, wg * (HALF / 8) + t8)) = lo;
+    }
     // this thread's 32 values of its channel's h row, kept for the chunk-end gate term (the h tile is gone by
     // the time dh arrives)
     uint4 hrow[4];
@@ -522,7 +523,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     if (tid == 0 && alive) {
       tc_fence_after_sync();
       // the two products that read h go first and get a commit of their own: as soon as they are done the h
-      // buffer can take dh, while the matrix-intra products still run
+      // buffer can take the Qc tiles, while the matrix-intra products still run
       mma_kmajor(tb + TM_X1, sb + Smem::HS, 16384, sb + Smem::DOP, 16384, 8, ID_KK, false);
       mma_kmajor(tb + TM_X3, sb + Smem::HS, 16384, sb + Smem::DOP + 8192, 16384, 8, ID_KK_NEG, false);
       mma_commit(&bars[BAR_C12]);
@@ -532,27 +533,44 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       mma_kmajor(tb + TM_X4, sb + Smem::YHI, 0, sb + Smem::DHI, 0, 4, ID_KK, false);
       mma_kmajor(tb + TM_X4, sb + Smem::YLO, 0, sb + Smem::DHI, 0, 4, ID_KK, true);
       mma_kmajor(tb + TM_X4, sb + Smem::YHI, 0, sb + Smem::DLO, 0, 4, ID_KK, true);
-    }
-    used |= (1u << BAR_C12) | (1u << BAR_D) | (1u << BAR_C3);
-    if (tid == 0) {
-      wait(BAR_C12, 7);
-      if (alive) {
-        mbar_expect_tx(&bars[BAR_D], 32768);
-        for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::HS + pn * 16384, &tmDH, 64 * pn, hrow0, &bars[BAR_D]);
-      }
-    }
-    wait(BAR_D, 8);
-    STAMP(7);  // dh tile landed
-    if (tid == 0 && alive) {
-      tc_fence_after_sync();
-      mma_kmajor(tb + TM_X5, sb + Smem::HS, 16384, sb + Smem::R, 8192, 8, ID_KK, false);
-      // B operand stored [reduction row i][n = j contiguous]: MN-major, a K=16 step spans two 8-row atoms
-      const uint32_t amat[6] = {Smem::QHI, Smem::QLO, Smem::QHI, Smem::EHI, Smem::ELO, Smem::EHI};
-      const uint32_t bmat[6] = {Smem::HHI, Smem::HHI, Smem::HLO, Smem::DHI, Smem::DHI, Smem::DLO};
-      for (int m = 0; m < 6; m++)
+      // X6, Ec part: B stored [reduction row i][n = j contiguous] = MN-major, a K=16 step spans two 8-row atoms
+      const uint32_t amat[3] = {Smem::EHI, Smem::ELO, Smem::EHI};
+      const uint32_t bmat[3] = {Smem::DHI, Smem::DHI, Smem::DLO};
+      for (int m = 0; m < 3; m++)
         for (int ks = 0; ks < 4; ks++)
           mma_f16(tb + TM_X6, smem_desc(sb + amat[m] + ks * 32, 16, 1024),
                   smem_desc(sb + bmat[m] + ks * 2048, 8192, 1024), ID_KMN, m > 0 || ks > 0);
+    }
+    used |= (1u << BAR_C12) | (1u << BAR_C3);
+    // Qc^T tiles into the h buffer as soon as X1 and X3 are done with it
+    wait(BAR_C12, 7);
+#pragma unroll
+    for (int t8 = 0; t8 < HALF / 8; t8++) {
+      float x[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int jj = t8 * 8 + j;
+        kq[jj] |= qv[jj] << 16;
+        x[j] = qf(jj) * (GATE == GATE_NONE ? 1.f : ex2(g[jj] - cen));
+      }
+      uint4 hi, lo;
+      split8(x, hi, lo);
+      *reinterpret_cast<uint4*>(sm + Smem::QHI + swz(kch, wg * (HALF / 8) + t8)) = hi;
+      *reinterpret_cast<uint4*>(sm + Smem::QLO + swz(kch, wg * (HALF / 8) + t8)) = lo;
+    }
+    wait(BAR_D, 8);
+    fence_async_smem();
+    __syncthreads();
+    STAMP(7);  // Qc tiles written, dh tile landed
+    if (tid == 0 && alive) {
+      tc_fence_after_sync();
+      mma_kmajor(tb + TM_X5, sb + Smem::DHT, 16384, sb + Smem::R, 8192, 8, ID_KK, false);
+      const uint32_t amat[3] = {Smem::QHI, Smem::QLO, Smem::QHI};
+      const uint32_t bmat[3] = {Smem::HHI, Smem::HHI, Smem::HLO};
+      for (int m = 0; m < 3; m++)
+        for (int ks = 0; ks < 4; ks++)
+          mma_f16(tb + TM_X6, smem_desc(sb + amat[m] + ks * 32, 16, 1024),
+                  smem_desc(sb + bmat[m] + ks * 2048, 8192, 1024), ID_KMN, true);
       mma_commit(&bars[BAR_C3]);
     }
     // chunk-end gate term, part 1: sum_v h[k,v] dh[k,v] over this thread's 32 value columns (h from registers,
@@ -561,7 +579,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       float hd = 0.f;
 #pragma unroll
       for (int ch = 0; ch < 4; ch++) {
-        uint4 d = *reinterpret_cast<const uint4*>(sm + Smem::HS + (wg >> 1) * 16384 + swz(kch, (wg & 1) * 4 + ch));
+        uint4 d = *reinterpret_cast<const uint4*>(sm + Smem::DHT + (wg >> 1) * 16384 + swz(kch, (wg & 1) * 4 + ch));
         const uint32_t* au = reinterpret_cast<const uint32_t*>(&hrow[ch]);
         const uint32_t* du = reinterpret_cast<const uint32_t*>(&d);
 #pragma unroll
@@ -575,8 +593,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     wait(BAR_C3, 10);
     tc_fence_after_sync();
     STAMP(8);  // all products done
-    // every tile of this chunk has been consumed: start the next chunk's loads under the epilogue
-    if (tid == 0 && alive && next_chunk < p.total_chunks) issue_loads(next_chunk);
 
     // ---- epilogue: thread = (key channel, token half); tokens in reverse order -----------------------------
     const float gl = GATE == GATE_VECTOR ? p.g[base128 + (size_t)(C - 1) * ldt + kch] : (GATE == GATE_SCALAR ? sGs[C - 1] : 0.f);
@@ -594,10 +610,12 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       atomicAdd(&sEnd[kch], colsum);
     }
     __syncthreads();
-    // Tokens 48..63 (wg 3) write their reverse-cumulated gate gradient straight away; the other quarters lack the
-    // totals of the tokens after them, park their partial sums in the (dead) Yc tiles and add the carry after
-    // the barrier.
-    float* sPark = reinterpret_cast<float*>(sm + Smem::YHI);  // [48 tokens][128 channels] over YHI + YLO
+    // every tile of this chunk has been consumed by the tensor core and (barrier above) by the threads: start the
+    // next chunk's loads under the epilogue
+    if (tid == 0 && alive && next_chunk < p.total_chunks) issue_loads(next_chunk);
+    // Every token quarter lacks the totals of the tokens after it: the partial reverse sums are parked in the
+    // (dead) Yc tiles and the carry is added after the barrier.
+    float* sPark = reinterpret_cast<float*>(sm + Smem::YHI);  // [64 tokens][128 channels] over YHI + YLO
     STAMP(9);  // colsum done
     float run = 0.f;
     if (alive) {
@@ -612,6 +630,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           if (lane == 0) atomicAdd(&sDgs[C - 1], s);
         }
       }
+      // Factored forms: dq = al*(ec*s*x1 + x2), gamma*eb = al*(ec*x3 + x4), yb/gamma = ze*(x6 + en*x5).
+      const float ecs = ec * scale;
+      const size_t go0 = base128 + (size_t)t0 * ldt + kch;
 #pragma unroll
       for (int c8 = HALF / 8 - 1; c8 >= 0; c8--) {
         float x1[8], x2[8], x3[8], x4[8], x5[8], x6[8];
@@ -627,34 +648,33 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 #pragma unroll
         for (int j = 7; j >= 0; j--) {
           const int jj = 8 * c8 + j, t = t0 + jj;
-          const size_t go = base128 + (size_t)t * ldt + kch;
-          float al = 1.f, ze = 1.f, ga = 1.f, f = 1.f;
+          const size_t go = go0 + (size_t)jj * ldt;
+          float al = 1.f, ze = 1.f;
           if (GATE != GATE_NONE) {
             al = ex2(g[jj] - cen);
             ze = ex2(cen - g[jj]);
-            ga = al * ec;
-            f = ze * en;
           }
           const float kk = kf(jj), qq = qf(jj);
           const float bb = VB ? bf2f(p.bg[go]) : sBeta[t];
-          const float dq = ga * scale * x1[j] + al * x2[j];
-          const float e = ga * x3[j] + al * x4[j];   // gamma * eb
-          const float y = ze * x6[j] + f * x5[j];    // yb / gamma
-          const float dk = bb * e + y;
-          store_out1(p.dq, go, dq, p.out_f32);
-          store_out1(p.dk, go, dk, p.out_f32);
-          if (VB)
-            store_out1(p.dbg, go, kk * e, p.out_f32);
-          else
-            dbp[j] = kk * e;
+          const float dq = al * fmaf(ecs, x1[j], x2[j]);
+          const float e = al * fmaf(ec, x3[j], x4[j]);   // gamma * eb
+          const float y = ze * fmaf(en, x5[j], x6[j]);   // yb / gamma
+          const float be = bb * e;
+          if (OUTF32) {
+            reinterpret_cast<float*>(p.dq)[go] = dq;
+            reinterpret_cast<float*>(p.dk)[go] = be + y;
+            if (VB) reinterpret_cast<float*>(p.dbg)[go] = kk * e;
+          } else {
+            reinterpret_cast<bf16*>(p.dq)[go] = f2bf(dq);
+            reinterpret_cast<bf16*>(p.dk)[go] = f2bf(be + y);
+            if (VB) reinterpret_cast<bf16*>(p.dbg)[go] = f2bf(kk * e);
+          }
+          if (!VB) dbp[j] = kk * e;
           if (GATE != GATE_NONE) {
-            const float row = qq * dq + kk * (bb * e - y);
+            const float row = fmaf(qq, dq, kk * (be - y));
             if (GATE == GATE_VECTOR) {
               run += row;
-              if (wg == NWG - 1)
-                p.dg[go] = run;
-              else
-                sPark[t * 128 + kch] = run;
+              sPark[t * 128 + kch] = run;
             } else {
               dgp[j] = row;
             }
@@ -671,18 +691,18 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       }
       if (GATE == GATE_VECTOR) sCarry[wg * 128 + kch] = run;
     }
+    STAMP(11);  // main epilogue loop done
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    STAMP(12);  // after its barrier
     if (alive) {
       if (GATE == GATE_VECTOR) {
-        if (wg < NWG - 1) {
-          float carry = 0.f;
-          for (int w2 = wg + 1; w2 < NWG; w2++) carry += sCarry[w2 * 128 + kch];
+        float carry = 0.f;
+        for (int w2 = wg + 1; w2 < NWG; w2++) carry += sCarry[w2 * 128 + kch];
 #pragma unroll
-          for (int jj = 0; jj < HALF; jj++)
-            p.dg[base128 + (size_t)(t0 + jj) * ldt + kch] = sPark[(t0 + jj) * 128 + kch] + carry;
-        }
+        for (int jj = 0; jj < HALF; jj++)
+          p.dg[base128 + (size_t)(t0 + jj) * ldt + kch] = sPark[(t0 + jj) * 128 + kch] + carry;
       }
       if (!VB && tid < C) p.dbeta[base1 + (size_t)tid * H] = sDb[tid];
       if (GATE == GATE_SCALAR && tid == 0) {
@@ -721,15 +741,20 @@ int sm_count() {
   return n;
 }
 
-template <int GATE, bool VB>
-cudaError_t run(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
-  auto kern = chunk_adjoint_tc_kernel<GATE, VB>;
+template <int GATE, bool VB, bool OUTF32>
+cudaError_t run1(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
+  auto kern = chunk_adjoint_tc_kernel<GATE, VB, OUTF32>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
   if (e != cudaSuccess) return e;
   const int grid = p.total_chunks < sm_count() ? p.total_chunks : sm_count();
   kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9], p);
   count_launch();
   return cudaGetLastError();
+}
+
+template <int GATE, bool VB>
+cudaError_t run(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
+  return p.out_f32 ? run1<GATE, VB, true>(tm, p, st) : run1<GATE, VB, false>(tm, p, st);
 }
 
 }  // namespace
