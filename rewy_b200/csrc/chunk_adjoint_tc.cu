@@ -67,13 +67,14 @@ struct Smem {
   static constexpr uint32_t HD = MINMAX + 4096;        // float[128] sum_v h*dh per channel
   static constexpr uint32_t END = HD + 512;            // float[128] chunk-end gate term per channel
   static constexpr uint32_t CARRY = END + 512;         // float[4][128] gate-gradient totals of each token quarter
-  static constexpr uint32_t BARS = CARRY + 2048;        // 8 mbarriers
+  static constexpr uint32_t GL = CARRY + 2048;         // float[128] last-row gate of the chunk per channel
+  static constexpr uint32_t BARS = GL + 512;        // 8 mbarriers
   static constexpr uint32_t TMEM = BARS + 128;         // uint32 tmem base (+ flags)
   static constexpr uint32_t TOTAL = TMEM + 64;
 };
 static_assert(Smem::TOTAL + 1024 <= 232448, "shared memory plan exceeds the 227 KB per-CTA limit");
 
-enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C12, BAR_C3, BAR_G, NUM_BARS };
+enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C12, BAR_C3, BAR_G, BAR_Q, NUM_BARS };
 
 // TMEM column plan (512 columns allocated).
 constexpr uint32_t TM_P = 0, TM_HD = 128, TM_X1 = 192, TM_X2 = 256, TM_X3 = 320, TM_X4 = 384, TM_X5 = 0, TM_X6 = 64;
@@ -194,6 +195,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   float* sHd = reinterpret_cast<float*>(sm + Smem::HD);
   float* sEnd = reinterpret_cast<float*>(sm + Smem::END);
   float* sCarry = reinterpret_cast<float*>(sm + Smem::CARRY);
+  float* sGl = reinterpret_cast<float*>(sm + Smem::GL);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + Smem::BARS);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + Smem::TMEM);
   const uint32_t sb = smem_u32(sm);
@@ -256,6 +258,16 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   };
 
   if (tid == 0 && (int)blockIdx.x < p.total_chunks) issue_loads(blockIdx.x);
+  // beta (and the scalar gate) of a chunk are fetched one chunk ahead into a register of threads 0..63
+  auto row_base1 = [&](int chunk) -> size_t {
+    const int bh = chunk / NT, n = chunk % NT;
+    return ((size_t)(bh / H) * T + (size_t)n * C) * H + bh % H;
+  };
+  float beta_pref = 0.f, gs_pref = 0.f;
+  if (tid < C && (int)blockIdx.x < p.total_chunks) {
+    if (!VB) beta_pref = p.beta[row_base1(blockIdx.x) + (size_t)tid * H];
+    if (GATE == GATE_SCALAR) gs_pref = p.g[row_base1(blockIdx.x) + (size_t)tid * H];
+  }
 
 #ifdef REWY_PHASE_PROF
   int prof_it = 0;
@@ -274,10 +286,14 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     uint32_t used = (1u << BAR_A) | (1u << BAR_B) | (1u << BAR_C) | (1u << BAR_G);
 
     if (tid < C) {
-      sBeta[tid] = VB ? 0.f : p.beta[base1 + (size_t)tid * H];
+      sBeta[tid] = beta_pref;
       sDb[tid] = 0.f;
       sDgs[tid] = 0.f;
-      if (GATE == GATE_SCALAR) sGs[tid] = p.g[base1 + (size_t)tid * H];
+      if (GATE == GATE_SCALAR) sGs[tid] = gs_pref;
+      if (next_chunk < p.total_chunks) {
+        if (!VB) beta_pref = p.beta[row_base1(next_chunk) + (size_t)tid * H];
+        if (GATE == GATE_SCALAR) gs_pref = p.g[row_base1(next_chunk) + (size_t)tid * H];
+      }
     }
     if (tid < 128) {
       sHd[tid] = 0.f;
@@ -291,7 +307,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     uint32_t qv[HALF];  // merged into kq only when q is first needed, so nothing waits on these loads early
 #pragma unroll
     for (int j = 0; j < HALF; j++) qv[j] = *reinterpret_cast<const uint16_t*>(p.q + base128 + (size_t)(t0 + j) * ldt + kch);
+    STAMP(13);
     wait(BAR_G, 11);
+    STAMP(14);
 #pragma unroll
     for (int j = 0; j < HALF; j++) {
       const int t = t0 + j;
@@ -300,7 +318,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
                  ? *reinterpret_cast<const float*>(sm + Smem::GT + (kch >> 5) * 8192 + swz(t, (kch & 31) >> 2) + (kch & 3) * 4)
                  : 0.f;
     }
+    if (GATE == GATE_VECTOR && wg == NWG - 1) sGl[kch] = g[HALF - 1];
     __syncthreads();  // everyone has its k / g out of the tiles before they are rebuilt as Ec / dAkk tiles
+    STAMP(15);
     float cen = 0.f;
     bool wide = false;
     if (GATE != GATE_NONE) {
@@ -530,6 +550,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       mma_kmajor(tb + TM_X2, sb + Smem::YHI, 0, sb + Smem::HHI, 0, 4, ID_KK, false);
       mma_kmajor(tb + TM_X2, sb + Smem::YLO, 0, sb + Smem::HHI, 0, 4, ID_KK, true);
       mma_kmajor(tb + TM_X2, sb + Smem::YHI, 0, sb + Smem::HLO, 0, 4, ID_KK, true);
+      mma_commit(&bars[BAR_Q]);  // X1 and X2 complete: dq can be finished while the rest still runs
       mma_kmajor(tb + TM_X4, sb + Smem::YHI, 0, sb + Smem::DHI, 0, 4, ID_KK, false);
       mma_kmajor(tb + TM_X4, sb + Smem::YLO, 0, sb + Smem::DHI, 0, 4, ID_KK, true);
       mma_kmajor(tb + TM_X4, sb + Smem::YHI, 0, sb + Smem::DLO, 0, 4, ID_KK, true);
@@ -541,7 +562,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           mma_f16(tb + TM_X6, smem_desc(sb + amat[m] + ks * 32, 16, 1024),
                   smem_desc(sb + bmat[m] + ks * 2048, 8192, 1024), ID_KMN, m > 0 || ks > 0);
     }
-    used |= (1u << BAR_C12) | (1u << BAR_C3);
+    used |= (1u << BAR_C12) | (1u << BAR_C3) | (1u << BAR_Q);
     // Qc^T tiles into the h buffer as soon as X1 and X3 are done with it
     wait(BAR_C12, 7);
 #pragma unroll
@@ -559,20 +580,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       *reinterpret_cast<uint4*>(sm + Smem::QLO + swz(kch, wg * (HALF / 8) + t8)) = lo;
     }
     wait(BAR_D, 8);
-    fence_async_smem();
-    __syncthreads();
-    STAMP(7);  // Qc tiles written, dh tile landed
-    if (tid == 0 && alive) {
-      tc_fence_after_sync();
-      mma_kmajor(tb + TM_X5, sb + Smem::DHT, 16384, sb + Smem::R, 8192, 8, ID_KK, false);
-      const uint32_t amat[3] = {Smem::QHI, Smem::QLO, Smem::QHI};
-      const uint32_t bmat[3] = {Smem::HHI, Smem::HHI, Smem::HLO};
-      for (int m = 0; m < 3; m++)
-        for (int ks = 0; ks < 4; ks++)
-          mma_f16(tb + TM_X6, smem_desc(sb + amat[m] + ks * 32, 16, 1024),
-                  smem_desc(sb + bmat[m] + ks * 2048, 8192, 1024), ID_KMN, true);
-      mma_commit(&bars[BAR_C3]);
-    }
     // chunk-end gate term, part 1: sum_v h[k,v] dh[k,v] over this thread's 32 value columns (h from registers,
     // dh from the tile that just landed)
     if (GATE != GATE_NONE && alive) {
@@ -590,55 +597,65 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       }
       atomicAdd(&sHd[kch], hd);
     }
+    fence_async_smem();
+    __syncthreads();  // Qc tiles visible to the tensor core; every generic read of the dh tile is done
+    STAMP(7);  // Qc tiles written, dh tile landed
+    if (tid == 0 && alive) {
+      tc_fence_after_sync();
+      mma_kmajor(tb + TM_X5, sb + Smem::DHT, 16384, sb + Smem::R, 8192, 8, ID_KK, false);
+      const uint32_t amat[3] = {Smem::QHI, Smem::QLO, Smem::QHI};
+      const uint32_t bmat[3] = {Smem::HHI, Smem::HHI, Smem::HLO};
+      for (int m = 0; m < 3; m++)
+        for (int ks = 0; ks < 4; ks++)
+          mma_f16(tb + TM_X6, smem_desc(sb + amat[m] + ks * 32, 16, 1024),
+                  smem_desc(sb + bmat[m] + ks * 2048, 8192, 1024), ID_KMN, true);
+      mma_commit(&bars[BAR_C3]);
+    }
+
+    // ---- epilogue, thread = (key channel, token quarter) ------------------------------------------------------
+    // Factored forms: dq = al*(ec*s*x1 + x2), gamma*eb = al*(ec*x3 + x4), yb/gamma = ze*(x6 + en*x5).
+    // Every token quarter lacks the totals of the tokens after it: partial reverse sums are parked in the (dead) Yc
+    // tiles and the carry (plus the chunk-end term) is added after the barrier.
+    const float gl = GATE == GATE_VECTOR ? sGl[kch] : (GATE == GATE_SCALAR ? sGs[C - 1] : 0.f);
+    const float en = GATE == GATE_NONE ? 1.f : ex2(gl - cen);  // exp2(g_last - g) = zeta * en
+    float* sPark = reinterpret_cast<float*>(sm + Smem::YHI);  // [64 tokens][128 channels] over YHI + YLO
+    const size_t go0 = base128 + (size_t)t0 * ldt + kch;
+    // pass A (needs X1, X2 only): dq, and q*dq parked for the gate row
+    wait(BAR_Q, 12);
+    tc_fence_after_sync();
+    if (alive) {
+      const float ecs = ec * scale;
+      float x1[16], x2[16];
+      tmem_ld16(tlane + TM_X1 + t0, x1);
+      tmem_ld16(tlane + TM_X2 + t0, x2);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < HALF; j++) {
+        const size_t go = go0 + (size_t)j * ldt;
+        const float al = GATE == GATE_NONE ? 1.f : ex2(g[j] - cen);
+        const float dq = al * fmaf(ecs, x1[j], x2[j]);
+        if (OUTF32)
+          reinterpret_cast<float*>(p.dq)[go] = dq;
+        else
+          reinterpret_cast<bf16*>(p.dq)[go] = f2bf(dq);
+        if (GATE != GATE_NONE) sPark[(t0 + j) * 128 + kch] = qf(j) * dq;
+      }
+    }
     wait(BAR_C3, 10);
     tc_fence_after_sync();
     STAMP(8);  // all products done
-
-    // ---- epilogue: thread = (key channel, token half); tokens in reverse order -----------------------------
-    const float gl = GATE == GATE_VECTOR ? p.g[base128 + (size_t)(C - 1) * ldt + kch] : (GATE == GATE_SCALAR ? sGs[C - 1] : 0.f);
-    const float en = GATE == GATE_NONE ? 1.f : ex2(gl - cen);  // exp2(g_last - g) = zeta * en
-    if (GATE != GATE_NONE && alive) {
-      // chunk-end term, part 2: sum_t k * exp2(g_last-g) * (R dh^T) over this thread's tokens
-      float colsum = 0.f;
-      {
-        float x5[16];
-        tmem_ld16(tlane + TM_X5 + t0, x5);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; j++) colsum += kf(j) * ex2(gl - g[j]) * x5[j];
-      }
-      atomicAdd(&sEnd[kch], colsum);
-    }
-    __syncthreads();
     // every tile of this chunk has been consumed by the tensor core and (barrier above) by the threads: start the
-    // next chunk's loads under the epilogue
+    // next chunk's loads under the rest of the epilogue
     if (tid == 0 && alive && next_chunk < p.total_chunks) issue_loads(next_chunk);
-    // Every token quarter lacks the totals of the tokens after it: the partial reverse sums are parked in the
-    // (dead) Yc tiles and the carry is added after the barrier.
-    float* sPark = reinterpret_cast<float*>(sm + Smem::YHI);  // [64 tokens][128 channels] over YHI + YLO
-    STAMP(9);  // colsum done
+    STAMP(9);
+    // pass B: dk, db, gate rows in reverse token order
     float run = 0.f;
     if (alive) {
-      if (GATE != GATE_NONE) {
-        const float endk = ex2(gl) * sHd[kch] + sEnd[kch];
-        if (GATE == GATE_VECTOR) {
-          if (wg == NWG - 1) run = endk;  // the chunk-end term sits on token 63
-        } else if (wg == NWG - 1) {
-          float s = endk;
-#pragma unroll
-          for (int m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
-          if (lane == 0) atomicAdd(&sDgs[C - 1], s);
-        }
-      }
-      // Factored forms: dq = al*(ec*s*x1 + x2), gamma*eb = al*(ec*x3 + x4), yb/gamma = ze*(x6 + en*x5).
-      const float ecs = ec * scale;
-      const size_t go0 = base128 + (size_t)t0 * ldt + kch;
+      float colsum = 0.f;  // chunk-end term, part 2: sum_t k * exp2(g_last-g) * (R dh^T) over this thread's tokens
 #pragma unroll
       for (int c8 = HALF / 8 - 1; c8 >= 0; c8--) {
-        float x1[8], x2[8], x3[8], x4[8], x5[8], x6[8];
+        float x3[8], x4[8], x5[8], x6[8];
         const int col = t0 + 8 * c8;
-        tmem_ld8(tlane + TM_X1 + col, x1);
-        tmem_ld8(tlane + TM_X2 + col, x2);
         tmem_ld8(tlane + TM_X3 + col, x3);
         tmem_ld8(tlane + TM_X4 + col, x4);
         tmem_ld8(tlane + TM_X5 + col, x5);
@@ -654,24 +671,22 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
             al = ex2(g[jj] - cen);
             ze = ex2(cen - g[jj]);
           }
-          const float kk = kf(jj), qq = qf(jj);
+          const float kk = kf(jj);
           const float bb = VB ? bf2f(p.bg[go]) : sBeta[t];
-          const float dq = al * fmaf(ecs, x1[j], x2[j]);
           const float e = al * fmaf(ec, x3[j], x4[j]);   // gamma * eb
           const float y = ze * fmaf(en, x5[j], x6[j]);   // yb / gamma
           const float be = bb * e;
           if (OUTF32) {
-            reinterpret_cast<float*>(p.dq)[go] = dq;
             reinterpret_cast<float*>(p.dk)[go] = be + y;
             if (VB) reinterpret_cast<float*>(p.dbg)[go] = kk * e;
           } else {
-            reinterpret_cast<bf16*>(p.dq)[go] = f2bf(dq);
             reinterpret_cast<bf16*>(p.dk)[go] = f2bf(be + y);
             if (VB) reinterpret_cast<bf16*>(p.dbg)[go] = f2bf(kk * e);
           }
           if (!VB) dbp[j] = kk * e;
           if (GATE != GATE_NONE) {
-            const float row = fmaf(qq, dq, kk * (be - y));
+            colsum = fmaf(kk * ze * en, x5[j], colsum);
+            const float row = fmaf(kk, be - y, sPark[t * 128 + kch]);
             if (GATE == GATE_VECTOR) {
               run += row;
               sPark[t * 128 + kch] = run;
@@ -689,6 +704,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           if (lane < 8) atomicAdd(&sDgs[col + lane], s);
         }
       }
+      if (GATE != GATE_NONE) atomicAdd(&sEnd[kch], colsum);
       if (GATE == GATE_VECTOR) sCarry[wg * 128 + kch] = run;
     }
     STAMP(11);  // main epilogue loop done
@@ -698,14 +714,24 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     STAMP(12);  // after its barrier
     if (alive) {
       if (GATE == GATE_VECTOR) {
-        float carry = 0.f;
+        float carry = ex2(gl) * sHd[kch] + sEnd[kch];  // the chunk-end term sits on token 63: part of every carry
         for (int w2 = wg + 1; w2 < NWG; w2++) carry += sCarry[w2 * 128 + kch];
 #pragma unroll
         for (int jj = 0; jj < HALF; jj++)
           p.dg[base128 + (size_t)(t0 + jj) * ldt + kch] = sPark[(t0 + jj) * 128 + kch] + carry;
       }
       if (!VB && tid < C) p.dbeta[base1 + (size_t)tid * H] = sDb[tid];
-      if (GATE == GATE_SCALAR && tid == 0) {
+      if (GATE == GATE_SCALAR && wg == 0) {
+        // scalar gate: the chunk-end term of every channel lands on the last token's sum
+        float se = ex2(gl) * sHd[kch] + sEnd[kch];
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) se += __shfl_xor_sync(0xffffffffu, se, m);
+        if (lane == 0) atomicAdd(&sDgs[C - 1], se);
+      }
+    }
+    if (GATE == GATE_SCALAR) {
+      __syncthreads();
+      if (tid == 0 && alive) {
         float r = 0.f;
         for (int t = C - 1; t >= 0; --t) {
           r += sDgs[t];
