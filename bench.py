@@ -238,13 +238,18 @@ def main():
         "bwd_scan": 4 * 256 + 128 + 8 + 512 + 2 * 256,
         "chunk_adjoint": 5 * 256 + 512 + 4 + 128 + 2 * 512 + 2 * 256 + 3 * 256 + 512 + 4,
     }
+    # DRAM bytes per token-head from the ncu captures summarised under profiles/ (B=1,T=2048,H=32; per-token-head
+    # traffic of these kernels does not depend on B or T), scaled to this launch
+    ncu_traffic = {"chunk_adjoint": 4325, "bwd_scan": 1595}
     dom = max(stages_head, key=lambda s: stages_head[s])
     dom_ms = stages_head[dom]
     achieved = alg[dom] * n_th / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
     path_bytes = (4616 if head_saved else 3080) * n_th + state_bytes
     roofline = {
         "bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-        "traffic": None, "peak_source": peak_src, "ms_per_launch": dom_ms,
+        "traffic": ncu_traffic[dom] * n_th if dom in ncu_traffic else None,
+        "traffic_source": "profiles/ (ncu dram__bytes_read+write per token-head on a smaller case, scaled)",
+        "peak_source": peak_src, "ms_per_launch": dom_ms,
         "algorithmic_bytes_per_token_head": alg[dom],
         "whole_path": {"algorithmic_bytes_per_token_head": path_bytes / n_th,
                        "achieved": path_bytes / (ms_head * 1e-3) / 1e9, "frac": path_bytes / (ms_head * 1e-3) / 1e9 / peak},
