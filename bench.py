@@ -92,7 +92,7 @@ class ClockSampler:
 
 # ---------------------------------------------------------------------------------------------
 # CPU arm: the reference's naive chunked PyTorch backward on the host cores
-def cpu_sample(steps, warmup, T=512, H=4, heads_of_workload=32):
+def cpu_sample(steps, warmup, T=2048, H=32, heads_of_workload=32):
     """Times the oracle's port of the reference's naive FP32 chunk path (autograd on CPU) on a bounded sample
     of the workload: B=1, T and H as given; tokens/s are normalised to the workload's head count."""
     import torch
@@ -118,13 +118,14 @@ def run_reference(args):
     if rank != 0:
         return
     import torch
-    steps, warmup = max(1, min(args.steps, 20)), max(1, min(args.warmup, 3))
+    steps, warmup = max(1, min(args.steps, 12)), max(1, min(args.warmup, 2))
     base, t = cpu_sample(steps, warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "KDA backward B=8 T=8192 H=32 K=V=128 chunk=64 (cfg2), CPU arm on a bounded sample"},
+        "config": {"workload": "KDA backward B=8 T=8192 H=32 K=V=128 chunk=64 (cfg2); CPU arm: each step is a bounded "
+                               "sample (B=1, T=2048, all 32 heads) of it"},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -311,7 +312,7 @@ def main():
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu_baseline, _ = cpu_sample(steps=3, warmup=1)
+        cpu_baseline, _ = cpu_sample(steps=2, warmup=1)
 
     if rank == 0:
         line = {
