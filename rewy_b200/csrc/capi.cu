@@ -114,6 +114,11 @@ std::atomic<int> g_chunk_variant{0};  // 0 = tensor-core kernel (+ pairwise list
 
 std::atomic<int> g_scan_variant{0};   // 0 = tensor-core reverse scan, 1 = warp-MMA reverse scan
 
+cudaError_t run_fwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
+  if (g_scan_variant.load(std::memory_order_relaxed) == 1 || s.ctrl == nullptr) return launch_fwd_scan(a, s, st);
+  return launch_fwd_scan_tc(a, s, static_cast<int*>(s.ctrl), st);
+}
+
 cudaError_t run_bwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
   if (g_scan_variant.load(std::memory_order_relaxed) == 1 || s.ctrl == nullptr) {
     if (s.ctrl != nullptr) {
@@ -173,7 +178,7 @@ int run_family(const RewyBwdArgs* a, int family, cudaStream_t st) {
   if (p.prepare) {
     if ((rc = check_cuda(launch_prepare(*a, s, st), "prepare")) != REWY_OK) return rc;
     timing_mark(set, 1, st);
-    if ((rc = check_cuda(launch_fwd_scan(*a, s, st), "forward state scan")) != REWY_OK) return rc;
+    if ((rc = check_cuda(run_fwd_scan(*a, s, st), "forward state scan")) != REWY_OK) return rc;
   }
   timing_mark(set, 2, st);
   if ((rc = check_cuda(run_bwd_scan(*a, s, st), "reverse state scan")) != REWY_OK) return rc;
@@ -239,7 +244,7 @@ int rewy_stage_fwd_scan(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_st
   if (rc != REWY_OK) return rc;
   STAGE_PTR(s->kg, "kg"); STAGE_PTR(s->w, "w"); STAGE_PTR(s->u, "u"); STAGE_PTR(s->h, "h"); STAGE_PTR(s->v_new, "v_new");
   if (a->family != REWY_DELTA) STAGE_PTR(a->g, "g");
-  return check_cuda(launch_fwd_scan(*a, *s, (cudaStream_t)st), "forward state scan");
+  return check_cuda(run_fwd_scan(*a, *s, (cudaStream_t)st), "forward state scan");
 }
 
 int rewy_stage_bwd_scan(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_stream_t st) {

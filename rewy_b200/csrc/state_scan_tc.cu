@@ -322,6 +322,220 @@ bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_consta
   if (warp == 0) tmem_dealloc(tb, 256);
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// Forward state scan (recompute policy):  h[n] stored;  v_new = u - w h[n];  h <- lam*h + kg^T v_new.
+// Replaces FLA chunk_gated_delta_rule_fwd_h (src/fast_delta_rule/backends/backward.py:117-118).  Same layout
+// tricks as the reverse scan; operands are single BF16 (h and v_new are exactly the tensors that get saved), so it
+// needs 97 KB of shared memory and 192 TMEM columns and two CTAs share an SM.
+struct FwdParams {
+  const float *g, *h0;
+  bf16* v_new;
+  int* err;
+  int T, H, NT;
+};
+struct FS {
+  static constexpr uint32_t W = 0;                // [64 i][128 k] two panels   16 KB
+  static constexpr uint32_t KG = W + 16384;       // [64 i][128 k]              16 KB
+  static constexpr uint32_t U = KG + 16384;       // [64 i][128 v]              16 KB
+  static constexpr uint32_t HT = U + 16384;       // h tile [128 k][128 v]      32 KB
+  static constexpr uint32_t VNT = HT + 32768;     // v_new^T [128 v][64 i]      16 KB
+  static constexpr uint32_t BARS = VNT + 16384;
+  static constexpr uint32_t TMEM = BARS + 64;
+  static constexpr uint32_t TOTAL = TMEM + 64;
+};
+enum { F_W = 0, F_KG, F_U, F_V, F_S };
+constexpr uint32_t TMF_S = 0, TMF_V = 128;
+
+template <int GATE>
+__global__ void __launch_bounds__(TPB, 2)
+fwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmKg,
+                   const __grid_constant__ CUtensorMap tmU, const __grid_constant__ CUtensorMap tmH, const FwdParams p) {
+  extern __shared__ __align__(1024) unsigned char raw[];
+  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + FS::BARS);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + FS::TMEM);
+  const uint32_t sb = smem_u32(sm);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int ch = tid & 127, wg = tid >> 7;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+  const int T = p.T, H = p.H, NT = p.NT;
+  const size_t ldt = (size_t)H * 128;
+
+  if (tid == 0) {
+    for (int i = 0; i < 8; i++) mbar_init(&bars[i], 1);
+    fence_barrier_init();
+    prefetch_tmap(&tmW); prefetch_tmap(&tmKg); prefetch_tmap(&tmU); prefetch_tmap(&tmH);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tb = *tmem_slot;
+  const uint32_t tlane = tb + ((uint32_t)((warp & 3) * 32) << 16);
+  uint32_t ph = 0;
+  bool alive = true;
+  auto wait = [&](int bar, int code) {
+    if (alive) alive = mbar_wait(&bars[bar], (ph >> bar) & 1u, p.err, code);
+    ph ^= 1u << bar;
+  };
+  auto row_of = [&](int n) { return b * T + n * C; };
+  auto load2 = [&](uint32_t dst, const CUtensorMap* m, int n, int bar) {
+    mbar_expect_tx(&bars[bar], 16384);
+    for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + dst + pn * 8192, m, h * 128 + 64 * pn, row_of(n), &bars[bar]);
+  };
+  if (tid == 0) {
+    load2(FS::W, &tmW, 0, F_W);
+    load2(FS::U, &tmU, 0, F_U);
+    load2(FS::KG, &tmKg, 0, F_KG);
+  }
+  {  // initial state
+    const float* src = p.h0 == nullptr ? nullptr : p.h0 + (size_t)bh * DK * DV + (size_t)ch * DV + 64 * wg;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      float x[16];
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) {
+        float4 v4 = src == nullptr ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(src + 16 * c + j);
+        x[j] = v4.x; x[j + 1] = v4.y; x[j + 2] = v4.z; x[j + 3] = v4.w;
+      }
+      tmem_st16f(tlane + TMF_S + 64 * wg + 16 * c, x);
+    }
+    tmem_st_wait();
+  }
+  constexpr uint32_t ID_V = instr_desc(FMT_BF16, 128, 64, true, false, true, false);  // -(h^T) w^T: A MN-major negated
+  constexpr uint32_t ID_S = instr_desc(FMT_BF16, 128, 128, true, false);              // kg^T (v_new^T)^T
+  auto load_lambda = [&](int n) -> float {
+    const int last = row_of(n) + C - 1;
+    if (GATE == GATE_VECTOR) return p.g[((size_t)last * H + h) * 128 + ch];
+    if (GATE == GATE_SCALAR) return p.g[(size_t)last * H + h];
+    return 0.f;
+  };
+  float glast = load_lambda(0);
+  for (int n = 0; n < NT; ++n) {
+    const int row0 = row_of(n);
+    if (n > 0) {
+      wait(F_S, 1);
+      tc_fence_after_sync();
+      if (tid == 0 && alive) load2(FS::KG, &tmKg, n, F_KG);  // kg buffer is free once the previous update is done
+    }
+    const float lam = GATE == GATE_NONE ? 1.f : exp2f(glast);
+    if (n + 1 < NT) glast = load_lambda(n + 1);
+    if (alive) {
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        float x[16];
+        tmem_ld16f(tlane + TMF_S + 64 * wg + 16 * c, x);
+        tmem_ld_wait();
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int j = 0; j < 4; j++) pk[j] = pack_bf16(x[8 * half + 2 * j], x[8 * half + 2 * j + 1]);
+          *reinterpret_cast<uint4*>(sm + FS::HT + wg * 16384 + swz(ch, 2 * c + half)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+        if (GATE != GATE_NONE) {
+#pragma unroll
+          for (int j = 0; j < 16; j++) x[j] *= lam;
+          tmem_st16f(tlane + TMF_S + 64 * wg + 16 * c, x);
+        }
+      }
+      if (GATE != GATE_NONE) tmem_st_wait();
+    }
+    fence_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (tid == 0) {
+      const int hrow0 = ((b * NT + n) * H + h) * 128;
+      if (alive) {
+        for (int pn = 0; pn < 2; pn++) tma_store_2d(&tmH, 64 * pn, hrow0, sm + FS::HT + pn * 16384);
+        bulk_commit();
+      }
+      wait(F_W, 2);
+      if (alive) {
+        tc_fence_after_sync();
+        for (int ks = 0; ks < 8; ks++)
+          mma_f16(tb + TMF_V, smem_desc(sb + FS::HT + ks * 2048, 16384, 1024),
+                  smem_desc(sb + FS::W + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024), ID_V, ks > 0);
+        mma_commit(&bars[F_V]);
+      }
+    } else {
+      ph ^= 1u << F_W;
+    }
+    // v_new^T row = u - (w h)^T: to global (token-major) and to the K-major tile of the state update
+    wait(F_V, 3);
+    tc_fence_after_sync();
+    if (tid == 0 && alive && n + 1 < NT) load2(FS::W, &tmW, n + 1, F_W);
+    wait(F_U, 4);
+    if (alive) {
+      const size_t go = ((size_t)row0 * H + h) * 128 + ch;
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        float x[16];
+        tmem_ld16f(tlane + TMF_V + 32 * wg + 16 * c, x);
+        tmem_ld_wait();
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            bf16 r2[2];
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+              const int tok = 32 * wg + 16 * c + 8 * half + j + e;
+              const bf16 uu = *reinterpret_cast<const bf16*>(sm + FS::U + (ch >> 6) * 8192 + swz(tok, (ch & 63) >> 3) + (ch & 7) * 2);
+              r2[e] = f2bf(bf2f(uu) + x[8 * half + j + e]);
+              p.v_new[go + (size_t)tok * ldt] = r2[e];
+            }
+            pk[j >> 1] = (uint32_t)(*reinterpret_cast<uint16_t*>(&r2[0])) | ((uint32_t)(*reinterpret_cast<uint16_t*>(&r2[1])) << 16);
+          }
+          *reinterpret_cast<uint4*>(sm + FS::VNT + swz(ch, 4 * wg + 2 * c + half)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+      }
+    }
+    if (tid == 0) bulk_wait_read0();
+    fence_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (tid == 0) {
+      if (alive && n + 1 < NT) load2(FS::U, &tmU, n + 1, F_U);  // every thread is done with this chunk's u tile
+      wait(F_KG, 5);
+      if (alive) {
+        tc_fence_after_sync();
+        for (int ks = 0; ks < 4; ks++)
+          mma_f16(tb + TMF_S, smem_desc(sb + FS::KG + ks * 2048, 8192, 1024),
+                  smem_desc(sb + FS::VNT + ks * 32, 16, 1024), ID_S, true);
+        mma_commit(&bars[F_S]);
+      }
+    } else {
+      ph ^= 1u << F_KG;
+    }
+  }
+  wait(F_S, 6);
+  if (tid == 0) bulk_wait0();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tb, 256);
+}
+
+constexpr size_t FWD_SCAN_SMEM = FS::TOTAL + 1024;
+static_assert(2 * (FWD_SCAN_SMEM + 1024) <= 233472, "two forward-scan CTAs must fit one SM");
+
+template <int GATE>
+cudaError_t run_fwd(const CUtensorMap* tm, const FwdParams& p, int grid, cudaStream_t st) {
+  auto kern = fwd_scan_tc_kernel<GATE>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FWD_SCAN_SMEM);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, TPB, FWD_SCAN_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], p);
+  count_launch();
+  return cudaGetLastError();
+}
+
 constexpr size_t SCAN_SMEM = SS::TOTAL + 1024;
 
 template <int GATE>
@@ -357,6 +571,27 @@ cudaError_t launch_bwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, 
     case GATE_NONE: return run<GATE_NONE>(tm, p, B * H, st);
     case GATE_SCALAR: return run<GATE_SCALAR>(tm, p, B * H, st);
     default: return run<GATE_VECTOR>(tm, p, B * H, st);
+  }
+}
+
+// err: device status word; must be zero on entry (the reverse scan that follows clears it again).
+cudaError_t launch_fwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* err, cudaStream_t st) {
+  const int B = a.B, T = a.T, H = a.H, NT = T / C;
+  const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
+  CUtensorMap tm[4];
+  bool ok = encode_tmap_2d(&tm[0], s.w, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+            encode_tmap_2d(&tm[1], s.kg, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+            encode_tmap_2d(&tm[2], s.u, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+            encode_tmap_2d(&tm[3], s.h, 2, 128, srows, 256, 64, 128);
+  if (!ok) return cudaErrorInvalidValue;
+  cudaError_t e0 = cudaMemsetAsync(err, 0, sizeof(int), st);
+  if (e0 != cudaSuccess) return e0;
+  FwdParams p;
+  p.g = a.g; p.h0 = a.h0; p.v_new = (bf16*)s.v_new; p.err = err; p.T = T; p.H = H; p.NT = NT;
+  switch (gate_mode_of(a.family)) {
+    case GATE_NONE: return run_fwd<GATE_NONE>(tm, p, B * H, st);
+    case GATE_SCALAR: return run_fwd<GATE_SCALAR>(tm, p, B * H, st);
+    default: return run_fwd<GATE_VECTOR>(tm, p, B * H, st);
   }
 }
 

@@ -56,7 +56,10 @@ def test_stage_forward_scan(op):
     a, keep = base_args(op, xs, saved)
     h = torch.full_like(saved["h"], float("nan"))
     v_new = torch.full_like(saved["v_new"], float("nan"))
-    call_stage("rewy_stage_fwd_scan", a, stage_buffers(w=saved["w"], u=saved["u"], kg=saved["kg"], h=h, v_new=v_new), DEV)
+    ctrl = torch.zeros(8, dtype=torch.int32, device=DEV)
+    call_stage("rewy_stage_fwd_scan", a, stage_buffers(w=saved["w"], u=saved["u"], kg=saved["kg"], h=h, v_new=v_new,
+                                                       ctrl=ctrl), DEV)
+    assert ctrl[0].item() == 0, f"device status word {ctrl[0].item()}: a bounded wait gave up"
     _report(dict(h=nrmse(saved["h"], h), v_new=nrmse(saved["v_new"], v_new)), 4e-3)
 
 
