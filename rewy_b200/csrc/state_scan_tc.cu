@@ -25,23 +25,27 @@ struct ScanParams {
   float scale;
 };
 
-struct SS {  // shared-memory plan, byte offsets from a 1024-byte aligned base
+// Shared-memory plan, byte offsets from a 1024-byte aligned base.  The 64 KB region X is time-shared inside a chunk:
+// first the dh hi/lo tiles (operands of the dR product), then - once that product is done - qg, w and the
+// (dR/scale) hi/lo tiles (operands of the state update).  That keeps a CTA at 105 KB so two CTAs share an SM and
+// hide each other's waits.
+struct SS {
   static constexpr uint32_t KG = 0;               // [64 i][128 k] two panels              16 KB
-  static constexpr uint32_t W = KG + 16384;       // [64 i][128 k]                         16 KB
-  static constexpr uint32_t QG = W + 16384;       // [64 i][128 k]                         16 KB
-  static constexpr uint32_t DO0 = QG + 16384;     // [64 i][128 v] double buffered         2 x 16 KB
-  static constexpr uint32_t AQK = DO0 + 32768;    // [64 j][64 i]                          8 KB
-  static constexpr uint32_t DHHI = AQK + 8192;    // [128 k][128 v] two panels             32 KB
-  static constexpr uint32_t DHLO = DHHI + 32768;  //                                       32 KB
-  static constexpr uint32_t DRHI = DHLO + 32768;  // (dR/scale)^T [128 v][64 i]            16 KB
-  static constexpr uint32_t DRLO = DRHI + 16384;  //                                       16 KB
-  static constexpr uint32_t BARS = DRLO + 16384;  // 8 mbarriers
+  static constexpr uint32_t DO0 = KG + 16384;     // [64 i][128 v]                         16 KB
+  static constexpr uint32_t AQK = DO0 + 16384;    // [64 j][64 i]                          8 KB
+  static constexpr uint32_t DHHI = AQK + 8192;    // X: [128 k][128 v] two panels          32 KB
+  static constexpr uint32_t DHLO = DHHI + 32768;  // X:                                    32 KB
+  static constexpr uint32_t QG = DHHI;            // X: [64 i][128 k]                      16 KB
+  static constexpr uint32_t W = DHHI + 16384;     // X: [64 i][128 k]                      16 KB
+  static constexpr uint32_t DRHI = DHLO;          // X: (dR/scale)^T [128 v][64 i]         16 KB
+  static constexpr uint32_t DRLO = DHLO + 16384;  // X:                                    16 KB
+  static constexpr uint32_t BARS = DHLO + 32768;  // 8 mbarriers
   static constexpr uint32_t TMEM = BARS + 64;
   static constexpr uint32_t TOTAL = TMEM + 64;
 };
-static_assert(SS::TOTAL + 1024 <= 232448, "shared memory plan exceeds the per-CTA limit");
+static_assert(2 * (SS::TOTAL + 2048) <= 233472, "two reverse-scan CTAs must fit one SM");
 
-enum { B_L1 = 0, B_DO0, B_DO1, B_L2, B_DR, B_S };
+enum { B_L1 = 0, B_DO, B_L2, B_DR, B_S };
 constexpr uint32_t TM_S = 0, TM_DR = 128;
 constexpr int TPB = 256;
 
@@ -92,7 +96,7 @@ __device__ __forceinline__ void split8s(const float (&x)[8], uint4& hi, uint4& l
 }
 
 template <int GATE>
-__global__ void __launch_bounds__(TPB, 1)
+__global__ void __launch_bounds__(TPB, 2)
 bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_constant__ CUtensorMap tmW,
                    const __grid_constant__ CUtensorMap tmQg, const __grid_constant__ CUtensorMap tmDO,
                    const __grid_constant__ CUtensorMap tmAqk, const __grid_constant__ CUtensorMap tmDH,
@@ -132,14 +136,16 @@ bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_consta
   };
 
   auto row_of = [&](int n) { return b * T + n * C; };
-  auto issue_l1 = [&](int n, int buf) {  // kg, Aqk and dO of chunk n
+  auto issue_l1 = [&](int n) {  // kg and Aqk of chunk n
     const int row0 = row_of(n);
     mbar_expect_tx(&bars[B_L1], 16384 + 8192);
     for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + SS::KG + pn * 8192, &tmKg, h * 128 + 64 * pn, row0, &bars[B_L1]);
     tma_load_2d(sm + SS::AQK, &tmAqk, h * 64, row0, &bars[B_L1]);
-    mbar_expect_tx(&bars[B_DO0 + buf], 16384);
+  };
+  auto issue_do = [&](int n) {  // dO of chunk n (read by both products of the chunk)
+    mbar_expect_tx(&bars[B_DO], 16384);
     for (int pn = 0; pn < 2; pn++)
-      tma_load_2d(sm + SS::DO0 + buf * 16384 + pn * 8192, &tmDO, h * 128 + 64 * pn, row0, &bars[B_DO0 + buf]);
+      tma_load_2d(sm + SS::DO0 + pn * 8192, &tmDO, h * 128 + 64 * pn, row_of(n), &bars[B_DO]);
   };
   auto issue_l2 = [&](int n) {  // qg, w of chunk n
     const int row0 = row_of(n);
@@ -150,8 +156,8 @@ bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_consta
     }
   };
   if (tid == 0) {
-    issue_l1(NT - 1, 0);
-    issue_l2(NT - 1);
+    issue_l1(NT - 1);
+    issue_do(NT - 1);
   }
 
   // initial state S' = dht / scale
@@ -184,13 +190,12 @@ bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_consta
   float glast = load_lambda(NT - 1);
   int it = 0;
   for (int n = NT - 1; n >= 0; --n, ++it) {
-    const int buf = it & 1;
     const int row0 = row_of(n);
     // ---- (a) state row -> dh tiles (hi to global as well), decayed state back to TMEM ---------------------
     if (it > 0) {
       wait(B_S, 1);
       tc_fence_after_sync();
-      if (tid == 0 && alive) issue_l2(n);  // qg / w buffers are free once the previous state update is complete
+      if (tid == 0 && alive) issue_do(n);  // the dO buffer is free once the previous state update is complete
     }
     const float lam = GATE == GATE_NONE ? 1.f : exp2f(glast);
     if (n > 0) glast = load_lambda(n - 1);  // in flight for a whole chunk before it is needed
@@ -229,7 +234,6 @@ bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_consta
         bulk_commit();
       }
       wait(B_L1, 2);
-      wait(B_DO0 + buf, 3);
       if (alive) {
         tc_fence_after_sync();
         for (int pass = 0; pass < 2; pass++) {
@@ -238,18 +242,27 @@ bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_consta
             mma_f16(tb + TM_DR, smem_desc(a + ks * 2048, 16384, 1024),
                     smem_desc(sb + SS::KG + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024), ID_DR_A, pass > 0 || ks > 0);
         }
+      }
+      wait(B_DO, 3);  // dO was requested at the top of the chunk: its latency hides behind the products above
+      if (alive) {
         for (int ks = 0; ks < 4; ks++)
-          mma_f16(tb + TM_DR, smem_desc(sb + SS::DO0 + buf * 16384 + ks * 2048, 8192, 1024),
+          mma_f16(tb + TM_DR, smem_desc(sb + SS::DO0 + ks * 2048, 8192, 1024),
                   smem_desc(sb + SS::AQK + ks * 2048, 8192, 1024), ID_DR_B, true);
         mma_commit(&bars[B_DR]);
       }
     } else {
-      ph ^= (1u << B_L1) | (1u << (B_DO0 + buf));
+      ph ^= (1u << B_L1) | (1u << B_DO);
     }
     // ---- (c) dR^T row -> global dR hi/lo, (dR/scale) tiles ----------------------------------------------
     wait(B_DR, 4);
     tc_fence_after_sync();
-    if (tid == 0 && alive && n > 0) issue_l1(n - 1, buf ^ 1);  // kg / Aqk are free; the other dO buffer too
+    if (tid == 0) {
+      bulk_wait_read0();  // the dh store has finished reading the hi tile: region X may now be refilled
+      if (alive) {
+        issue_l2(n);                    // qg, w into the first half of X
+        if (n > 0) issue_l1(n - 1);     // kg / Aqk buffers are free as well
+      }
+    }
     if (alive) {
       const size_t go = ((size_t)row0 * H + h) * 128 + ch;  // + token * ldt
 #pragma unroll
@@ -277,7 +290,6 @@ bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_consta
         }
       }
     }
-    if (tid == 0) bulk_wait_read0();  // the dh store has finished reading its tile before anyone rewrites it
     fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();
@@ -289,7 +301,7 @@ bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_consta
         tc_fence_after_sync();
         for (int ks = 0; ks < 4; ks++)
           mma_f16(tb + TM_S, smem_desc(sb + SS::QG + ks * 2048, 8192, 1024),
-                  smem_desc(sb + SS::DO0 + buf * 16384 + ks * 2048, 8192, 1024), ID_S_Q, true);
+                  smem_desc(sb + SS::DO0 + ks * 2048, 8192, 1024), ID_S_Q, true);
         for (int pass = 0; pass < 2; pass++)
           for (int ks = 0; ks < 4; ks++)
             mma_f16(tb + TM_S, smem_desc(sb + SS::W + ks * 2048, 8192, 1024),
