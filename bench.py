@@ -239,9 +239,9 @@ def main():
         "bwd_scan": 4 * 256 + 128 + 8 + 512 + 2 * 256,
         "chunk_adjoint": 5 * 256 + 512 + 4 + 128 + 2 * 512 + 2 * 256 + 3 * 256 + 512 + 4,
     }
-    # DRAM bytes per token-head from the ncu captures summarised under profiles/ (B=1,T=2048,H=32; per-token-head
+    # DRAM bytes per token-head from the ncu captures summarised under profiles/ (B=4,T=2048,H=32; per-token-head
     # traffic of these kernels does not depend on B or T), scaled to this launch
-    ncu_traffic = {"chunk_adjoint": 4325, "bwd_scan": 1595}
+    ncu_traffic = {"chunk_adjoint": 4649, "bwd_scan": 2036}
     dom = max(stages_head, key=lambda s: stages_head[s])
     dom_ms = stages_head[dom]
     achieved = alg[dom] * n_th / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
