@@ -58,16 +58,21 @@ struct Smem {
                                                        // tiles once they are dead and is read into registers at chunk start
   static constexpr uint32_t GT = EHI;                  // g tile of the next chunk (4 panels [64 t][32 k] FP32) lands in the Ec tiles
   static constexpr uint32_t VT = HHI;                  // v tile (2 panels [64 i][64 v]) aliases the dAqk tiles until P is done
-  static constexpr uint32_t TILES_END = ELO + 16384;   // 204800
+  static constexpr uint32_t TILES_END = ELO + 16384;   // 221184
+  // Per-channel partial sums of the gate epilogue live in the first P tile: it is dead from the moment the
+  // products that read P are complete until the next chunk's P epilogue.
+  static constexpr uint32_t HD = DOP + 8192;           // float[4][128] sum_v h*dh per channel, one row per value quarter
+  static constexpr uint32_t END = HD + 2048;           // float[4][128] chunk-end gate term per channel, per token quarter
+  static constexpr uint32_t CARRY = END + 2048;        // float[4][128] gate-gradient totals of each token quarter
   static constexpr uint32_t BETA = TILES_END;          // float[64]
   static constexpr uint32_t DBETA = BETA + 256;        // float[64]
   static constexpr uint32_t GS = DBETA + 256;          // float[64] scalar gate rows
   static constexpr uint32_t DGS = GS + 256;            // float[64] per-token gate sums (scalar gate)
-  static constexpr uint32_t MINMAX = DGS + 256;        // float[4][2][128] per-quarter min / max of the gate rows
-  static constexpr uint32_t HD = MINMAX + 4096;        // float[128] sum_v h*dh per channel
-  static constexpr uint32_t END = HD + 512;            // float[128] chunk-end gate term per channel
-  static constexpr uint32_t CARRY = END + 512;         // float[4][128] gate-gradient totals of each token quarter
-  static constexpr uint32_t GL = CARRY + 2048;         // float[128] last-row gate of the chunk per channel
+  static constexpr uint32_t MINMAX = DGS + 256;        // float[4][2][128] per-quarter min / max of the gate rows (chunk start)
+  static constexpr uint32_t DBP = MINMAX;              // float[8][64] sum_v v*P per token, one row per 16 value columns
+  static constexpr uint32_t DBW = DBP + 2048;          // float[16 warps][16 tokens] sum_k k*(gamma eb) of the warp's channels
+  static constexpr uint32_t DGW = DBW + 1024;          // float[16][16] same for the scalar-gate rows
+  static constexpr uint32_t GL = MINMAX + 4096;        // float[128] last-row gate of the chunk per channel
   static constexpr uint32_t BARS = GL + 512;        // 8 mbarriers
   static constexpr uint32_t TMEM = BARS + 128;         // uint32 tmem base (+ flags)
   static constexpr uint32_t TOTAL = TMEM + 64;
@@ -122,14 +127,20 @@ __device__ __forceinline__ void split8(const float (&x)[8], uint4& hi, uint4& lo
   lo = make_uint4(l[0], l[1], l[2], l[3]);
 }
 
-// K-major BF16 product over `ksteps` K=16 steps; tiles made of 64-element (128-byte) panels `panel_*` bytes apart.
+// K-major BF16 product over KSTEPS K=16 steps; tiles made of 64-element (128-byte) panels `a_panel` / `b_panel` bytes
+// apart.  `a` and `b` are descriptor low words (desc_lo) of the tile bases; all offsets fold into immediates.
+template <int KSTEPS>
 __device__ __forceinline__ void mma_kmajor(uint32_t d, uint32_t a, uint32_t a_panel, uint32_t b, uint32_t b_panel,
-                                           int ksteps, uint32_t idesc, bool accumulate) {
-  for (int ks = 0; ks < ksteps; ks++) {
-    uint64_t ad = smem_desc(a + (ks >> 2) * a_panel + (ks & 3) * 32, 16, 1024);
-    uint64_t bd = smem_desc(b + (ks >> 2) * b_panel + (ks & 3) * 32, 16, 1024);
-    mma_f16(d, ad, bd, idesc, accumulate || ks > 0);
-  }
+                                           uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ks++)
+    mma_f16_lo(d, a + (((ks >> 2) * a_panel + (ks & 3) * 32) >> 4), b + (((ks >> 2) * b_panel + (ks & 3) * 32) >> 4), idesc,
+               accumulate || ks > 0);
+}
+// A K-major (rows = channel), B MN-major ([reduction row][n contiguous], one K=16 step = two 8-row atoms = 2048 B).
+__device__ __forceinline__ void mma_kmn4(uint32_t d, uint32_t a, uint32_t b, uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < 4; ks++) mma_f16_lo(d, a + ((ks * 32) >> 4), b + ((ks * 2048) >> 4), idesc, accumulate || ks > 0);
 }
 
 // Sum over the warp of x[lane & 15] for each of the 16 per-thread values (16 shuffles); every lane returns the
@@ -195,6 +206,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   float* sHd = reinterpret_cast<float*>(sm + Smem::HD);
   float* sEnd = reinterpret_cast<float*>(sm + Smem::END);
   float* sCarry = reinterpret_cast<float*>(sm + Smem::CARRY);
+  float* sDbP = reinterpret_cast<float*>(sm + Smem::DBP);
+  float* sDbW = reinterpret_cast<float*>(sm + Smem::DBW);
+  float* sDgW = reinterpret_cast<float*>(sm + Smem::DGW);
   float* sGl = reinterpret_cast<float*>(sm + Smem::GL);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + Smem::BARS);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + Smem::TMEM);
@@ -204,6 +218,11 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   const int T = p.T, H = p.H, NT = p.NT;
   const size_t ldt = (size_t)H * 128;
   const float scale = p.scale;
+#ifdef REWY_EXP_NOSTORE
+  const bool st_ok = p.scale < 0.f;
+#else
+  constexpr bool st_ok = true;
+#endif
 
   if (tid == 0) {
     for (int i = 0; i < NUM_BARS; i++) mbar_init(&bars[i], 1);
@@ -229,6 +248,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   constexpr uint32_t ID_KK_NEG = instr_desc(FMT_BF16, 128, 64, false, false, true, false);
   constexpr uint32_t ID_KMN = instr_desc(FMT_BF16, 128, 64, false, true);
 
+  // descriptor low word of the tile at byte offset `off` of the plan
+  const uint32_t sb4 = sb >> 4;  // the plan's base is 1024-byte aligned, so offsets add without carries
+  auto dl = [&](uint32_t off, uint32_t lbo) { return sb4 + (off >> 4) + ((lbo >> 4) << 16); };
   auto wait = [&](int b, int code) {
     if (alive) alive = mbar_wait(&bars[b], (ph >> b) & 1u, p.err, code);
   };
@@ -271,7 +293,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 
 #ifdef REWY_PHASE_PROF
   int prof_it = 0;
-#define STAMP(i) do { if (p.prof != nullptr && blockIdx.x == 0 && tid == 32 && prof_it < 64) p.prof[prof_it * 16 + (i)] = clock64(); } while (0)
+#define STAMP(i) do { if (p.prof != nullptr && blockIdx.x == 0 && tid == 32 && prof_it < 64) p.prof[prof_it * 32 + (i)] = clock64(); } while (0)
 #else
 #define STAMP(i) do {} while (0)
 #endif
@@ -284,21 +306,18 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     const int hrow0 = ((b * NT + n) * H + h) * 128;        // first row of this chunk's state in [B*NT*H*128]
     const int next_chunk = chunk + gridDim.x;
     uint32_t used = (1u << BAR_A) | (1u << BAR_B) | (1u << BAR_C) | (1u << BAR_G);
+    STAMP(28);
 
     if (tid < C) {
       sBeta[tid] = beta_pref;
-      sDb[tid] = 0.f;
-      sDgs[tid] = 0.f;
+      STAMP(29);
       if (GATE == GATE_SCALAR) sGs[tid] = gs_pref;
       if (next_chunk < p.total_chunks) {
         if (!VB) beta_pref = p.beta[row_base1(next_chunk) + (size_t)tid * H];
         if (GATE == GATE_SCALAR) gs_pref = p.g[row_base1(next_chunk) + (size_t)tid * H];
       }
     }
-    if (tid < 128) {
-      sHd[tid] = 0.f;
-      sEnd[tid] = 0.f;
-    }
+    STAMP(16);
     // ---- this thread's 32 tokens of its key channel: k and q (packed BF16 pair) and the gate row ------------
     uint32_t kq[HALF];
     float g[HALF];
@@ -363,12 +382,12 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       wait(BAR_A, 1);
       if (alive) {
         tc_fence_after_sync();
+#pragma unroll
         for (int ks = 0; ks < 4; ks++)
-          mma_f16(tb + TM_P, smem_desc(sb + Smem::AKK + ks * 2048, 8192, 1024),
-                  smem_desc(sb + Smem::DRHI + ks * 2048, 8192, 1024), ID_P, ks > 0);
+          mma_f16_lo(tb + TM_P, dl(Smem::AKK + ks * 2048, 0), dl(Smem::DRHI + ks * 2048, 8192), ID_P, ks > 0);
+#pragma unroll
         for (int ks = 0; ks < 4; ks++)
-          mma_f16(tb + TM_P, smem_desc(sb + Smem::AKK + ks * 2048, 8192, 1024),
-                  smem_desc(sb + Smem::DRLO + ks * 2048, 8192, 1024), ID_P, true);
+          mma_f16_lo(tb + TM_P, dl(Smem::AKK + ks * 2048, 0), dl(Smem::DRLO + ks * 2048, 8192), ID_P, true);
         mma_commit(&bars[BAR_P]);
       }
     }
@@ -401,15 +420,16 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::DHT + pn * 16384, &tmDH, 64 * pn, hrow0, &bars[BAR_D]);
     }
     used |= 1u << BAR_D;
-    if ((warp & 3) < 2 && alive) {
-      const int i = kch;                   // row (token) 0..63; this warpgroup handles value columns 32*wg ..
+    // The A operand's two 64-row panels are the same tile (leading offset 0), so TMEM lanes 64..127 repeat rows
+    // 0..63 and all sixteen warps take part: thread = (token i, 16 value columns).
+    if (alive) {
+      const int i = kch & 63, hs = kch >> 6;  // row (token) 0..63; value columns 32*wg + 16*hs ..
       const size_t go = base128 + (size_t)i * ldt;
       const float beta_i = sBeta[i];
       float dbv = 0.f;
-#pragma unroll 1
-      for (int c4 = 0; c4 < 2; c4++) {
+      {
         float x[16];
-        const int v0 = 32 * wg + 16 * c4;  // value column
+        const int v0 = 32 * wg + 16 * hs;  // value column
         const int vp = v0 >> 6, vc = (v0 & 63) >> 3;  // 64-wide panel, 16-byte chunk inside its rows
         tmem_ld16(tlane + TM_P + v0, x);
         tmem_ld_wait();
@@ -439,8 +459,10 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           dvp[j] = pack_bf16(w0 * x[2 * j], w1 * x[2 * j + 1]);
           pp[j] = pack_bf16(x[2 * j], x[2 * j + 1]);
         }
+        if (st_ok) {
         *reinterpret_cast<uint4*>(p.dv + go + v0) = make_uint4(dvp[0], dvp[1], dvp[2], dvp[3]);
         *reinterpret_cast<uint4*>(p.dv + go + v0 + 8) = make_uint4(dvp[4], dvp[5], dvp[6], dvp[7]);
+        }
         if (VB) {
           if (OUTF32) {
             float* o = reinterpret_cast<float*>(p.dwg) + go + v0;
@@ -460,8 +482,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         *reinterpret_cast<uint4*>(sm + ptile + swz(i, vc)) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
         *reinterpret_cast<uint4*>(sm + ptile + swz(i, vc + 1)) = make_uint4(pp[4], pp[5], pp[6], pp[7]);
       }
-      if (!VB) atomicAdd(&sDb[i], dbv);
+      if (!VB) sDbP[(wg * 2 + hs) * 64 + i] = dbv;
     }
+    STAMP(24);
     fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();
@@ -473,7 +496,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       wait(BAR_B, 3);
       if (alive) {
         tc_fence_after_sync();
-        mma_kmajor(tb + TM_HD, sb + Smem::DOP, 16384, sb + Smem::R, 8192, 8, ID_KK, false);
+        mma_kmajor<8>(tb + TM_HD, dl(Smem::DOP, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
         mma_commit(&bars[BAR_HD]);
       }
     }
@@ -493,6 +516,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       *reinterpret_cast<uint4*>(sm + Smem::EHI + swz(kch, wg * (HALF / 8) + t8)) = hi;
       *reinterpret_cast<uint4*>(sm + Smem::ELO + swz(kch, wg * (HALF / 8) + t8)) = lo;
     }
+    STAMP(25);
     // this thread's 32 values of its channel's h row, kept for the chunk-end gate term (the h tile is gone by
     // the time dh arrives)
     uint4 hrow[4];
@@ -504,6 +528,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     } else if (tid == 0) {
       wait(BAR_C, 6);
     }
+    STAMP(26);
     wait(BAR_HD, 4);
     tc_fence_after_sync();
     STAMP(5);  // HD ready
@@ -533,6 +558,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         }
       }
     }
+    STAMP(27);
     fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();
@@ -544,27 +570,25 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       tc_fence_after_sync();
       // the two products that read h go first and get a commit of their own: as soon as they are done the h
       // buffer can take the Qc tiles, while the matrix-intra products still run
-      mma_kmajor(tb + TM_X1, sb + Smem::HS, 16384, sb + Smem::DOP, 16384, 8, ID_KK, false);
-      mma_kmajor(tb + TM_X3, sb + Smem::HS, 16384, sb + Smem::DOP + 8192, 16384, 8, ID_KK_NEG, false);
+      mma_kmajor<8>(tb + TM_X1, dl(Smem::HS, 16), 16384, dl(Smem::DOP, 16), 16384, ID_KK, false);
+      mma_kmajor<8>(tb + TM_X3, dl(Smem::HS, 16), 16384, dl(Smem::DOP + 8192, 16), 16384, ID_KK_NEG, false);
       mma_commit(&bars[BAR_C12]);
-      mma_kmajor(tb + TM_X2, sb + Smem::YHI, 0, sb + Smem::HHI, 0, 4, ID_KK, false);
-      mma_kmajor(tb + TM_X2, sb + Smem::YLO, 0, sb + Smem::HHI, 0, 4, ID_KK, true);
-      mma_kmajor(tb + TM_X2, sb + Smem::YHI, 0, sb + Smem::HLO, 0, 4, ID_KK, true);
+      mma_kmajor<4>(tb + TM_X2, dl(Smem::YHI, 16), 0, dl(Smem::HHI, 16), 0, ID_KK, false);
+      mma_kmajor<4>(tb + TM_X2, dl(Smem::YLO, 16), 0, dl(Smem::HHI, 16), 0, ID_KK, true);
+      mma_kmajor<4>(tb + TM_X2, dl(Smem::YHI, 16), 0, dl(Smem::HLO, 16), 0, ID_KK, true);
       mma_commit(&bars[BAR_Q]);  // X1 and X2 complete: dq can be finished while the rest still runs
-      mma_kmajor(tb + TM_X4, sb + Smem::YHI, 0, sb + Smem::DHI, 0, 4, ID_KK, false);
-      mma_kmajor(tb + TM_X4, sb + Smem::YLO, 0, sb + Smem::DHI, 0, 4, ID_KK, true);
-      mma_kmajor(tb + TM_X4, sb + Smem::YHI, 0, sb + Smem::DLO, 0, 4, ID_KK, true);
-      // X6, Ec part: B stored [reduction row i][n = j contiguous] = MN-major, a K=16 step spans two 8-row atoms
-      const uint32_t amat[3] = {Smem::EHI, Smem::ELO, Smem::EHI};
-      const uint32_t bmat[3] = {Smem::DHI, Smem::DHI, Smem::DLO};
-      for (int m = 0; m < 3; m++)
-        for (int ks = 0; ks < 4; ks++)
-          mma_f16(tb + TM_X6, smem_desc(sb + amat[m] + ks * 32, 16, 1024),
-                  smem_desc(sb + bmat[m] + ks * 2048, 8192, 1024), ID_KMN, m > 0 || ks > 0);
+      mma_kmajor<4>(tb + TM_X4, dl(Smem::YHI, 16), 0, dl(Smem::DHI, 16), 0, ID_KK, false);
+      mma_kmajor<4>(tb + TM_X4, dl(Smem::YLO, 16), 0, dl(Smem::DHI, 16), 0, ID_KK, true);
+      mma_kmajor<4>(tb + TM_X4, dl(Smem::YHI, 16), 0, dl(Smem::DLO, 16), 0, ID_KK, true);
+      // X6, Ec part: B stored [reduction row i][n = j contiguous] = MN-major
+      mma_kmn4(tb + TM_X6, dl(Smem::EHI, 16), dl(Smem::DHI, 8192), ID_KMN, false);
+      mma_kmn4(tb + TM_X6, dl(Smem::ELO, 16), dl(Smem::DHI, 8192), ID_KMN, true);
+      mma_kmn4(tb + TM_X6, dl(Smem::EHI, 16), dl(Smem::DLO, 8192), ID_KMN, true);
     }
     used |= (1u << BAR_C12) | (1u << BAR_C3) | (1u << BAR_Q);
     // Qc^T tiles into the h buffer as soon as X1 and X3 are done with it
     wait(BAR_C12, 7);
+    STAMP(20);
 #pragma unroll
     for (int t8 = 0; t8 < HALF / 8; t8++) {
       float x[8];
@@ -579,7 +603,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       *reinterpret_cast<uint4*>(sm + Smem::QHI + swz(kch, wg * (HALF / 8) + t8)) = hi;
       *reinterpret_cast<uint4*>(sm + Smem::QLO + swz(kch, wg * (HALF / 8) + t8)) = lo;
     }
+    STAMP(21);
     wait(BAR_D, 8);
+    STAMP(22);
     // chunk-end gate term, part 1: sum_v h[k,v] dh[k,v] over this thread's 32 value columns (h from registers,
     // dh from the tile that just landed)
     if (GATE != GATE_NONE && alive) {
@@ -595,20 +621,18 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           hd += x.x * y.x + x.y * y.y;
         }
       }
-      atomicAdd(&sHd[kch], hd);
+      sHd[wg * 128 + kch] = hd;
     }
+    STAMP(23);
     fence_async_smem();
     __syncthreads();  // Qc tiles visible to the tensor core; every generic read of the dh tile is done
     STAMP(7);  // Qc tiles written, dh tile landed
     if (tid == 0 && alive) {
       tc_fence_after_sync();
-      mma_kmajor(tb + TM_X5, sb + Smem::DHT, 16384, sb + Smem::R, 8192, 8, ID_KK, false);
-      const uint32_t amat[3] = {Smem::QHI, Smem::QLO, Smem::QHI};
-      const uint32_t bmat[3] = {Smem::HHI, Smem::HHI, Smem::HLO};
-      for (int m = 0; m < 3; m++)
-        for (int ks = 0; ks < 4; ks++)
-          mma_f16(tb + TM_X6, smem_desc(sb + amat[m] + ks * 32, 16, 1024),
-                  smem_desc(sb + bmat[m] + ks * 2048, 8192, 1024), ID_KMN, true);
+      mma_kmajor<8>(tb + TM_X5, dl(Smem::DHT, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
+      mma_kmn4(tb + TM_X6, dl(Smem::QHI, 16), dl(Smem::HHI, 8192), ID_KMN, true);
+      mma_kmn4(tb + TM_X6, dl(Smem::QLO, 16), dl(Smem::HHI, 8192), ID_KMN, true);
+      mma_kmn4(tb + TM_X6, dl(Smem::QHI, 16), dl(Smem::HLO, 8192), ID_KMN, true);
       mma_commit(&bars[BAR_C3]);
     }
 
@@ -623,24 +647,28 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     // pass A (needs X1, X2 only): dq, and q*dq parked for the gate row
     wait(BAR_Q, 12);
     tc_fence_after_sync();
+    STAMP(17);
     if (alive) {
       const float ecs = ec * scale;
       float x1[16], x2[16];
       tmem_ld16(tlane + TM_X1 + t0, x1);
       tmem_ld16(tlane + TM_X2 + t0, x2);
       tmem_ld_wait();
+    STAMP(18);
 #pragma unroll
       for (int j = 0; j < HALF; j++) {
         const size_t go = go0 + (size_t)j * ldt;
         const float al = GATE == GATE_NONE ? 1.f : ex2(g[j] - cen);
         const float dq = al * fmaf(ecs, x1[j], x2[j]);
-        if (OUTF32)
+        if (!st_ok) {
+        } else if (OUTF32)
           reinterpret_cast<float*>(p.dq)[go] = dq;
         else
           reinterpret_cast<bf16*>(p.dq)[go] = f2bf(dq);
         if (GATE != GATE_NONE) sPark[(t0 + j) * 128 + kch] = qf(j) * dq;
       }
     }
+    STAMP(19);
     wait(BAR_C3, 10);
     tc_fence_after_sync();
     STAMP(8);  // all products done
@@ -676,7 +704,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           const float e = al * fmaf(ec, x3[j], x4[j]);   // gamma * eb
           const float y = ze * fmaf(en, x5[j], x6[j]);   // yb / gamma
           const float be = bb * e;
-          if (OUTF32) {
+          if (!st_ok) {
+          } else if (OUTF32) {
             reinterpret_cast<float*>(p.dk)[go] = be + y;
             if (VB) reinterpret_cast<float*>(p.dbg)[go] = kk * e;
           } else {
@@ -697,14 +726,14 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         }
         if (!VB) {
           float s = warp_sum8(dbp, lane);
-          if (lane < 8) atomicAdd(&sDb[col + lane], s);
+          if (lane < 8) sDbW[warp * 16 + 8 * c8 + lane] = s;
         }
         if (GATE == GATE_SCALAR) {
           float s = warp_sum8(dgp, lane);
-          if (lane < 8) atomicAdd(&sDgs[col + lane], s);
+          if (lane < 8) sDgW[warp * 16 + 8 * c8 + lane] = s;
         }
       }
-      if (GATE != GATE_NONE) atomicAdd(&sEnd[kch], colsum);
+      if (GATE != GATE_NONE) sEnd[wg * 128 + kch] = colsum;
       if (GATE == GATE_VECTOR) sCarry[wg * 128 + kch] = run;
     }
     STAMP(11);  // main epilogue loop done
@@ -713,26 +742,46 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     tc_fence_after_sync();
     STAMP(12);  // after its barrier
     if (alive) {
+      // chunk-end term of this channel: lambda * sum_v h dh + sum_t k 2^(g_last - g) (R dh^T)
+      float endk = 0.f;
+      if (GATE != GATE_NONE)
+        endk = ex2(gl) * (sHd[kch] + sHd[128 + kch] + sHd[256 + kch] + sHd[384 + kch]) +
+               (sEnd[kch] + sEnd[128 + kch] + sEnd[256 + kch] + sEnd[384 + kch]);
       if (GATE == GATE_VECTOR) {
-        float carry = ex2(gl) * sHd[kch] + sEnd[kch];  // the chunk-end term sits on token 63: part of every carry
+        float carry = endk;  // the chunk-end term sits on token 63: part of every carry
         for (int w2 = wg + 1; w2 < NWG; w2++) carry += sCarry[w2 * 128 + kch];
 #pragma unroll
         for (int jj = 0; jj < HALF; jj++)
-          p.dg[base128 + (size_t)(t0 + jj) * ldt + kch] = sPark[(t0 + jj) * 128 + kch] + carry;
+          if (st_ok) p.dg[base128 + (size_t)(t0 + jj) * ldt + kch] = sPark[(t0 + jj) * 128 + kch] + carry;
       }
-      if (!VB && tid < C) p.dbeta[base1 + (size_t)tid * H] = sDb[tid];
-      if (GATE == GATE_SCALAR && wg == 0) {
-        // scalar gate: the chunk-end term of every channel lands on the last token's sum
-        float se = ex2(gl) * sHd[kch] + sEnd[kch];
+      if (!VB && tid < C) {
+        float db = 0.f;
 #pragma unroll
-        for (int m = 16; m > 0; m >>= 1) se += __shfl_xor_sync(0xffffffffu, se, m);
-        if (lane == 0) atomicAdd(&sDgs[C - 1], se);
+        for (int m = 0; m < 8; m++) db += sDbP[m * 64 + tid];
+#pragma unroll
+        for (int m = 0; m < 4; m++) db += sDbW[((tid >> 4) * 4 + m) * 16 + (tid & 15)];
+        p.dbeta[base1 + (size_t)tid * H] = db;
+      }
+      if (GATE == GATE_SCALAR) {
+        if (tid < C) {
+          float dgt = 0.f;
+#pragma unroll
+          for (int m = 0; m < 4; m++) dgt += sDgW[((tid >> 4) * 4 + m) * 16 + (tid & 15)];
+          sDgs[tid] = dgt;
+        }
+        if (wg == 0) {
+          // scalar gate: the chunk-end term of every channel lands on the last token's sum
+          float se = endk;
+#pragma unroll
+          for (int m = 16; m > 0; m >>= 1) se += __shfl_xor_sync(0xffffffffu, se, m);
+          if (lane == 0) sDb[warp] = se;  // sDb is free for the scalar families' four partial sums
+        }
       }
     }
     if (GATE == GATE_SCALAR) {
       __syncthreads();
       if (tid == 0 && alive) {
-        float r = 0.f;
+        float r = sDb[0] + sDb[1] + sDb[2] + sDb[3];
         for (int t = C - 1; t >= 0; --t) {
           r += sDgs[t];
           p.dg[base1 + (size_t)t * H] = r;

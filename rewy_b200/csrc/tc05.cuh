@@ -40,7 +40,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0, t1;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+#pragma unroll 1
   for (;;) {
+#pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
@@ -147,6 +149,23 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"((uint32_t)accumulate)
+      : "memory");
+}
+// The same instruction with both descriptors given as (low, high) words.  For the fixed tile plan of a kernel the
+// high word is a constant and the low word is "tile base >> 4" plus a compile-time offset, so that issuing a
+// product costs the single thread that does it a couple of integer adds per instruction instead of rebuilding
+// two 64-bit descriptors.
+constexpr uint32_t DESC_HI_SW128 = ((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, SWIZZLE_128B
+// low word of the descriptor of a tile at shared address `saddr` (below 256 KB) with leading byte offset `lbo`
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) { return (saddr >> 4) | ((lbo_bytes >> 4) << 16); }
+__device__ __forceinline__ void mma_f16_lo(uint32_t d_tmem, uint32_t alo, uint32_t blo, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(alo), "r"(blo), "r"(idesc), "r"((uint32_t)accumulate), "r"(DESC_HI_SW128)
       : "memory");
 }
 // Arrive on an mbarrier when every MMA issued so far by this thread has completed (implies
