@@ -19,6 +19,12 @@ using namespace tc;
 
 constexpr float SPAN_LIMIT = 80.f;
 
+// Division of a non-negative int below 2^31 by a divisor fixed at launch: quotient = umulhi(x, mul) >> shift.
+struct FastDiv {
+  uint32_t mul, shift, div;
+  __device__ __forceinline__ int quot(int x) const { return div == 1 ? x : (int)(__umulhi((uint32_t)x, mul) >> shift); }
+};
+
 struct TcParams {
   const bf16 *q, *k, *v, *bg, *wg, *dh;
   const float *g, *beta;
@@ -28,6 +34,7 @@ struct TcParams {
   int* wide_list;   // [0] = count, [1..] = flattened chunk indices with a wide gate span
   int* err;         // device status word: non-zero if a bounded wait gave up
   int T, H, NT, total_chunks, out_f32;
+  FastDiv div_nt, div_h;
   float scale;
 #ifdef REWY_PHASE_PROF
   long long* prof;  // [CTA 0's chunk iteration][16] clock64 stamps (debug builds only)
@@ -44,9 +51,9 @@ struct Smem {
   static constexpr uint32_t R = DOP + 32768;           // 2 panels [64 j][64 v]                  16 KB
   static constexpr uint32_t HS = R + 16384;            // 2 panels [128 k][64 v]  h, later dh    32 KB
   static constexpr uint32_t HHI = HS + 32768;          // dAqk hi [64 i][64 j]                   8 KB
-  static constexpr uint32_t HLO = HHI + 8192;
-  static constexpr uint32_t DHI = HLO + 8192;          // dAkk hi
-  static constexpr uint32_t DLO = DHI + 8192;
+  static constexpr uint32_t DHI = HHI + 8192;          // dAkk hi; [dAqk hi ; dAkk hi] is one 128-row operand
+  static constexpr uint32_t HLO = DHI + 8192;          // dAqk lo
+  static constexpr uint32_t DLO = HLO + 8192;          // dAkk lo
   static constexpr uint32_t YHI = DLO + 8192;          // Yc^T hi [128 k][64 t]                  16 KB
   static constexpr uint32_t YLO = YHI + 16384;
   static constexpr uint32_t EHI = YLO + 16384;         // Ec^T hi
@@ -54,10 +61,10 @@ struct Smem {
   static constexpr uint32_t DHT = DRHI;                // dh tile (2 panels [128 k][64 v]) takes the dR tiles once P is done
   static constexpr uint32_t QHI = HS;                  // Qc^T hi/lo take the h buffer once the products that read h are done
   static constexpr uint32_t QLO = HS + 16384;
-  static constexpr uint32_t KT = DHI;                  // k tile of the NEXT chunk (2 panels [64 t][64 k]) lands in the dAkk
+  static constexpr uint32_t KT = HLO;                  // k tile of the NEXT chunk (2 panels [64 t][64 k]) lands in the two lo
                                                        // tiles once they are dead and is read into registers at chunk start
   static constexpr uint32_t GT = EHI;                  // g tile of the next chunk (4 panels [64 t][32 k] FP32) lands in the Ec tiles
-  static constexpr uint32_t VT = HHI;                  // v tile (2 panels [64 i][64 v]) aliases the dAqk tiles until P is done
+  static constexpr uint32_t VT = HHI;                  // v tile (2 panels [64 i][64 v]) aliases the two hi tiles until P is done
   static constexpr uint32_t TILES_END = ELO + 16384;   // 221184
   // Per-channel partial sums of the gate epilogue live in the first P tile: it is dead from the moment the
   // products that read P are complete until the next chunk's P epilogue.
@@ -82,7 +89,7 @@ static_assert(Smem::TOTAL + 1024 <= 232448, "shared memory plan exceeds the 227 
 enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C12, BAR_C3, BAR_G, BAR_Q, NUM_BARS };
 
 // TMEM column plan (512 columns allocated).
-constexpr uint32_t TM_P = 0, TM_HD = 128, TM_X1 = 192, TM_X2 = 256, TM_X3 = 320, TM_X4 = 384, TM_X5 = 0, TM_X6 = 64;
+constexpr uint32_t TM_P = 0, TM_HD = 128, TM_X1 = 192, TM_X3 = 256, TM_X2 = 320, TM_X4 = 384, TM_X5 = 0, TM_X6 = 64;
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&r)[16]) {
   uint32_t u[16];
@@ -171,7 +178,11 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-
+__device__ __forceinline__ float rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 // Same for 8 values: every lane returns the warp total of value index (lane & 7) (9 shuffles).
 __device__ __forceinline__ float warp_sum8(float (&x)[8], int lane) {
 #pragma unroll
@@ -245,7 +256,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 
   constexpr uint32_t ID_P = instr_desc(FMT_BF16, 128, 128, true, true);
   constexpr uint32_t ID_KK = instr_desc(FMT_BF16, 128, 64, false, false);
-  constexpr uint32_t ID_KK_NEG = instr_desc(FMT_BF16, 128, 64, false, false, true, false);
+  constexpr uint32_t ID_KK128 = instr_desc(FMT_BF16, 128, 128, false, false);
   constexpr uint32_t ID_KMN = instr_desc(FMT_BF16, 128, 64, false, true);
 
   // descriptor low word of the tile at byte offset `off` of the plan
@@ -256,34 +267,29 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   };
   // all tile loads of one chunk (issued by thread 0): A = {Akk, dR hi/lo, v}, B = {dO, R}, C = {h}
   auto issue_loads = [&](int chunk) {
-    const int bh = chunk / NT, n = chunk % NT, b = bh / H, h = bh % H;
+    const int bh = p.div_nt.quot(chunk), n = chunk - bh * NT, b = p.div_h.quot(bh), h = bh - b * H;
     const int row0 = b * T + n * C, hrow0 = ((b * NT + n) * H + h) * 128;
     // k (and the vector gate) of the chunk: read into registers at its start, so they get a barrier of their own
     mbar_expect_tx(&bars[BAR_G], 16384 + (GATE == GATE_VECTOR ? 32768 : 0));
-    for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::KT + pn * 8192, &tmK, h * 128 + 64 * pn, row0, &bars[BAR_G]);
-    if (GATE == GATE_VECTOR)
-      for (int pn = 0; pn < 4; pn++) tma_load_2d(sm + Smem::GT + pn * 8192, &tmG, h * 128 + 32 * pn, row0, &bars[BAR_G]);
+    tma_load_3d(sm + Smem::KT, &tmK, h * 128, row0, 0, &bars[BAR_G]);
+    if (GATE == GATE_VECTOR) tma_load_3d(sm + Smem::GT, &tmG, h * 128, row0, 0, &bars[BAR_G]);
     mbar_expect_tx(&bars[BAR_A], 8192 + 3 * 16384);
     tma_load_2d(sm + Smem::AKK, &tmAkk, h * 64, row0, &bars[BAR_A]);
-    for (int pn = 0; pn < 2; pn++) {
-      tma_load_2d(sm + Smem::DRHI + pn * 8192, &tmDRhi, h * 128 + 64 * pn, row0, &bars[BAR_A]);
-      tma_load_2d(sm + Smem::DRLO + pn * 8192, &tmDRlo, h * 128 + 64 * pn, row0, &bars[BAR_A]);
-      tma_load_2d(sm + Smem::VT + pn * 8192, &tmV, h * 128 + 64 * pn, row0, &bars[BAR_A]);
-    }
+    tma_load_3d(sm + Smem::DRHI, &tmDRhi, h * 128, row0, 0, &bars[BAR_A]);
+    tma_load_3d(sm + Smem::DRLO, &tmDRlo, h * 128, row0, 0, &bars[BAR_A]);
+    tma_load_3d(sm + Smem::VT, &tmV, h * 128, row0, 0, &bars[BAR_A]);
     mbar_expect_tx(&bars[BAR_B], 2 * 16384);
+    for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::DOP + pn * 16384, &tmDO, h * 128 + 64 * pn, row0, &bars[BAR_B]);
+    tma_load_3d(sm + Smem::R, &tmR, h * 128, row0, 0, &bars[BAR_B]);
     mbar_expect_tx(&bars[BAR_C], 32768);
-    for (int pn = 0; pn < 2; pn++) {
-      tma_load_2d(sm + Smem::DOP + pn * 16384, &tmDO, h * 128 + 64 * pn, row0, &bars[BAR_B]);
-      tma_load_2d(sm + Smem::R + pn * 8192, &tmR, h * 128 + 64 * pn, row0, &bars[BAR_B]);
-      tma_load_2d(sm + Smem::HS + pn * 16384, &tmH, 64 * pn, hrow0, &bars[BAR_C]);
-    }
+    tma_load_3d(sm + Smem::HS, &tmH, 0, hrow0, 0, &bars[BAR_C]);
   };
 
   if (tid == 0 && (int)blockIdx.x < p.total_chunks) issue_loads(blockIdx.x);
   // beta (and the scalar gate) of a chunk are fetched one chunk ahead into a register of threads 0..63
   auto row_base1 = [&](int chunk) -> size_t {
-    const int bh = chunk / NT, n = chunk % NT;
-    return ((size_t)(bh / H) * T + (size_t)n * C) * H + bh % H;
+    const int bh = p.div_nt.quot(chunk), n = chunk - bh * NT, b = p.div_h.quot(bh);
+    return ((size_t)b * T + (size_t)n * C) * H + (bh - b * H);
   };
   float beta_pref = 0.f, gs_pref = 0.f;
   if (tid < C && (int)blockIdx.x < p.total_chunks) {
@@ -294,12 +300,14 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 #ifdef REWY_PHASE_PROF
   int prof_it = 0;
 #define STAMP(i) do { if (p.prof != nullptr && blockIdx.x == 0 && tid == 32 && prof_it < 64) p.prof[prof_it * 32 + (i)] = clock64(); } while (0)
+#define STAMP0(i) do { if (p.prof != nullptr && blockIdx.x == 0 && tid == 0 && prof_it < 64) p.prof[2048 + prof_it * 32 + (i)] = clock64(); } while (0)
 #else
 #define STAMP(i) do {} while (0)
+#define STAMP0(i) do {} while (0)
 #endif
   for (int chunk = blockIdx.x; chunk < p.total_chunks && alive; chunk += gridDim.x) {
     STAMP(0);
-    const int bh = chunk / NT, n = chunk % NT, b = bh / H, h = bh % H;
+    const int bh = p.div_nt.quot(chunk), n = chunk - bh * NT, b = p.div_h.quot(bh), h = bh - b * H;
     const int row0 = b * T + n * C;                       // first token row in [B*T]
     const size_t base128 = ((size_t)row0 * H + h) * 128;
     const size_t base1 = (size_t)row0 * H + h;
@@ -374,14 +382,22 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       continue;
     }
     STAMP(1);  // operands in registers, centre known
+    // From here on g[] holds the centred factor alpha = 2^(g - c) of each token; zeta = 1 / alpha.
+    if (GATE != GATE_NONE) {
+#pragma unroll
+      for (int j = 0; j < HALF; j++) g[j] = ex2(g[j] - cen);
+    }
     auto kf = [&](int j) { return __uint_as_float(kq[j] << 16); };          // k of token t0 + j
     auto qf = [&](int j) { return __uint_as_float(kq[j] & 0xFFFF0000u); };  // q of token t0 + j
 
     // ---- P = Akk^T (dR_hi + dR_lo) ----------------------------------------------------------------
-    if (tid == 0) {
+    if (warp == 0) {
+      STAMP0(0);
       wait(BAR_A, 1);
+      STAMP0(1);
       if (alive) {
         tc_fence_after_sync();
+        if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < 4; ks++)
           mma_f16_lo(tb + TM_P, dl(Smem::AKK + ks * 2048, 0), dl(Smem::DRHI + ks * 2048, 8192), ID_P, ks > 0);
@@ -389,7 +405,10 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         for (int ks = 0; ks < 4; ks++)
           mma_f16_lo(tb + TM_P, dl(Smem::AKK + ks * 2048, 0), dl(Smem::DRLO + ks * 2048, 8192), ID_P, true);
         mma_commit(&bars[BAR_P]);
+        }
+        STAMP0(2);
       }
+      __syncwarp();
     }
     used |= 1u << BAR_P;
 
@@ -401,7 +420,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 #pragma unroll
       for (int j = 0; j < 8; j++) {
         const int jj = t8 * 8 + j;
-        y[j] = kf(jj) * (GATE == GATE_NONE ? 1.f : ex2(cen - g[jj]));
+        y[j] = kf(jj) * (GATE == GATE_NONE ? 1.f : rcp(g[jj]));
       }
       const int ch = wg * (HALF / 8) + t8;
       uint4 hi, lo;
@@ -415,9 +434,12 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     wait(BAR_P, 2);
     tc_fence_after_sync();
     STAMP(3);  // P ready
-    if (tid == 0 && alive) {
-      mbar_expect_tx(&bars[BAR_D], 32768);
-      for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::DHT + pn * 16384, &tmDH, 64 * pn, hrow0, &bars[BAR_D]);
+    if (warp == 0 && alive) {
+      if (elect_one()) {
+        mbar_expect_tx(&bars[BAR_D], 32768);
+        tma_load_3d(sm + Smem::DHT, &tmDH, 0, hrow0, 0, &bars[BAR_D]);
+      }
+      __syncwarp();
     }
     used |= 1u << BAR_D;
     // The A operand's two 64-row panels are the same tile (leading offset 0), so TMEM lanes 64..127 repeat rows
@@ -492,13 +514,18 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 
     STAMP(4);  // P epilogue + Qc done (after barrier)
     // ---- [dAqk/scale ; -dAkk] = [dO ; P] R^T ---------------------------------------------------------
-    if (tid == 0) {
+    if (warp == 0) {
+      STAMP0(3);
       wait(BAR_B, 3);
       if (alive) {
         tc_fence_after_sync();
-        mma_kmajor<8>(tb + TM_HD, dl(Smem::DOP, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
-        mma_commit(&bars[BAR_HD]);
+        if (elect_one()) {
+          mma_kmajor<8>(tb + TM_HD, dl(Smem::DOP, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
+          mma_commit(&bars[BAR_HD]);
+        }
+        STAMP0(4);
       }
+      __syncwarp();
     }
     used |= 1u << BAR_HD;
     // Ec^T tiles while the stacked product runs (first needed by the last product group)
@@ -509,7 +536,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       for (int j = 0; j < 8; j++) {
         const int jj = t8 * 8 + j;
         const float bb = VB ? bf2f(p.bg[base128 + (size_t)(t0 + jj) * ldt + kch]) : sBeta[t0 + jj];
-        e[j] = bb * kf(jj) * (GATE == GATE_NONE ? 1.f : ex2(g[jj] - cen));
+        e[j] = bb * kf(jj) * (GATE == GATE_NONE ? 1.f : g[jj]);
       }
       uint4 hi, lo;
       split8(e, hi, lo);
@@ -566,24 +593,29 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 
     STAMP(6);  // HD epilogue done (after barrier)
     // ---- products that read h: X1 = h dO^T, X2 = Yc^T dAqk^T, X3 = -(h P^T), X4 = Yc^T dAkk^T ---------------
-    if (tid == 0 && alive) {
+    if (warp == 0 && alive) {
+      STAMP0(5);
       tc_fence_after_sync();
-      // the two products that read h go first and get a commit of their own: as soon as they are done the h
-      // buffer can take the Qc tiles, while the matrix-intra products still run
-      mma_kmajor<8>(tb + TM_X1, dl(Smem::HS, 16), 16384, dl(Smem::DOP, 16), 16384, ID_KK, false);
-      mma_kmajor<8>(tb + TM_X3, dl(Smem::HS, 16), 16384, dl(Smem::DOP + 8192, 16), 16384, ID_KK_NEG, false);
-      mma_commit(&bars[BAR_C12]);
-      mma_kmajor<4>(tb + TM_X2, dl(Smem::YHI, 16), 0, dl(Smem::HHI, 16), 0, ID_KK, false);
-      mma_kmajor<4>(tb + TM_X2, dl(Smem::YLO, 16), 0, dl(Smem::HHI, 16), 0, ID_KK, true);
-      mma_kmajor<4>(tb + TM_X2, dl(Smem::YHI, 16), 0, dl(Smem::HLO, 16), 0, ID_KK, true);
-      mma_commit(&bars[BAR_Q]);  // X1 and X2 complete: dq can be finished while the rest still runs
-      mma_kmajor<4>(tb + TM_X4, dl(Smem::YHI, 16), 0, dl(Smem::DHI, 16), 0, ID_KK, false);
-      mma_kmajor<4>(tb + TM_X4, dl(Smem::YLO, 16), 0, dl(Smem::DHI, 16), 0, ID_KK, true);
-      mma_kmajor<4>(tb + TM_X4, dl(Smem::YHI, 16), 0, dl(Smem::DLO, 16), 0, ID_KK, true);
-      // X6, Ec part: B stored [reduction row i][n = j contiguous] = MN-major
-      mma_kmn4(tb + TM_X6, dl(Smem::EHI, 16), dl(Smem::DHI, 8192), ID_KMN, false);
-      mma_kmn4(tb + TM_X6, dl(Smem::ELO, 16), dl(Smem::DHI, 8192), ID_KMN, true);
-      mma_kmn4(tb + TM_X6, dl(Smem::EHI, 16), dl(Smem::DLO, 8192), ID_KMN, true);
+      if (elect_one()) {
+        // [X1 | X3] = h [dO ; P]^T as one N=128 product (the sign of X3 is applied in the epilogue).  It goes first
+        // and gets a commit of its own: as soon as it is done the h buffer can take the Qc tiles and the P tile the
+        // per-channel scratch, while the matrix-intra products still run
+        mma_kmajor<8>(tb + TM_X1, dl(Smem::HS, 16), 16384, dl(Smem::DOP, 16), 16384, ID_KK128, false);
+        mma_commit(&bars[BAR_C12]);
+        STAMP0(6);
+        // [X2 | X4] = Yc^T [dAqk ; dAkk]^T, hi/lo split in three passes
+        mma_kmajor<4>(tb + TM_X2, dl(Smem::YHI, 16), 0, dl(Smem::HHI, 16), 0, ID_KK128, false);
+        mma_kmajor<4>(tb + TM_X2, dl(Smem::YLO, 16), 0, dl(Smem::HHI, 16), 0, ID_KK128, true);
+        mma_kmajor<4>(tb + TM_X2, dl(Smem::YHI, 16), 0, dl(Smem::HLO, 16), 0, ID_KK128, true);
+        mma_commit(&bars[BAR_Q]);  // X1 and X2 complete: dq can be finished while the rest still runs
+        STAMP0(7);
+        // X6, Ec part: B stored [reduction row i][n = j contiguous] = MN-major
+        mma_kmn4(tb + TM_X6, dl(Smem::EHI, 16), dl(Smem::DHI, 8192), ID_KMN, false);
+        mma_kmn4(tb + TM_X6, dl(Smem::ELO, 16), dl(Smem::DHI, 8192), ID_KMN, true);
+        mma_kmn4(tb + TM_X6, dl(Smem::EHI, 16), dl(Smem::DLO, 8192), ID_KMN, true);
+      }
+      STAMP0(8);
+      __syncwarp();
     }
     used |= (1u << BAR_C12) | (1u << BAR_C3) | (1u << BAR_Q);
     // Qc^T tiles into the h buffer as soon as X1 and X3 are done with it
@@ -596,7 +628,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       for (int j = 0; j < 8; j++) {
         const int jj = t8 * 8 + j;
         kq[jj] |= qv[jj] << 16;
-        x[j] = qf(jj) * (GATE == GATE_NONE ? 1.f : ex2(g[jj] - cen));
+        x[j] = qf(jj) * (GATE == GATE_NONE ? 1.f : g[jj]);
       }
       uint4 hi, lo;
       split8(x, hi, lo);
@@ -627,13 +659,18 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     fence_async_smem();
     __syncthreads();  // Qc tiles visible to the tensor core; every generic read of the dh tile is done
     STAMP(7);  // Qc tiles written, dh tile landed
-    if (tid == 0 && alive) {
+    if (warp == 0 && alive) {
+      STAMP0(9);
       tc_fence_after_sync();
-      mma_kmajor<8>(tb + TM_X5, dl(Smem::DHT, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
-      mma_kmn4(tb + TM_X6, dl(Smem::QHI, 16), dl(Smem::HHI, 8192), ID_KMN, true);
-      mma_kmn4(tb + TM_X6, dl(Smem::QLO, 16), dl(Smem::HHI, 8192), ID_KMN, true);
-      mma_kmn4(tb + TM_X6, dl(Smem::QHI, 16), dl(Smem::HLO, 8192), ID_KMN, true);
-      mma_commit(&bars[BAR_C3]);
+      if (elect_one()) {
+        mma_kmajor<8>(tb + TM_X5, dl(Smem::DHT, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
+        mma_kmn4(tb + TM_X6, dl(Smem::QHI, 16), dl(Smem::HHI, 8192), ID_KMN, true);
+        mma_kmn4(tb + TM_X6, dl(Smem::QLO, 16), dl(Smem::HHI, 8192), ID_KMN, true);
+        mma_kmn4(tb + TM_X6, dl(Smem::QHI, 16), dl(Smem::HLO, 8192), ID_KMN, true);
+        mma_commit(&bars[BAR_C3]);
+      }
+      STAMP0(10);
+      __syncwarp();
     }
 
     // ---- epilogue, thread = (key channel, token quarter) ------------------------------------------------------
@@ -658,7 +695,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 #pragma unroll
       for (int j = 0; j < HALF; j++) {
         const size_t go = go0 + (size_t)j * ldt;
-        const float al = GATE == GATE_NONE ? 1.f : ex2(g[j] - cen);
+        const float al = GATE == GATE_NONE ? 1.f : g[j];
         const float dq = al * fmaf(ecs, x1[j], x2[j]);
         if (!st_ok) {
         } else if (OUTF32)
@@ -674,10 +711,16 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     STAMP(8);  // all products done
     // every tile of this chunk has been consumed by the tensor core and (barrier above) by the threads: start the
     // next chunk's loads under the rest of the epilogue
-    if (tid == 0 && alive && next_chunk < p.total_chunks) issue_loads(next_chunk);
+    STAMP0(11);
+    if (warp == 0 && alive && next_chunk < p.total_chunks) {
+      if (elect_one()) issue_loads(next_chunk);
+      __syncwarp();
+    }
+    STAMP0(12);
     STAMP(9);
     // pass B: dk, db, gate rows in reverse token order
     float run = 0.f;
+    const float nec = -ec;
     if (alive) {
       float colsum = 0.f;  // chunk-end term, part 2: sum_t k * exp2(g_last-g) * (R dh^T) over this thread's tokens
 #pragma unroll
@@ -696,12 +739,12 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           const size_t go = go0 + (size_t)jj * ldt;
           float al = 1.f, ze = 1.f;
           if (GATE != GATE_NONE) {
-            al = ex2(g[jj] - cen);
-            ze = ex2(cen - g[jj]);
+            al = g[jj];
+            ze = rcp(al);
           }
           const float kk = kf(jj);
           const float bb = VB ? bf2f(p.bg[go]) : sBeta[t];
-          const float e = al * fmaf(ec, x3[j], x4[j]);   // gamma * eb
+          const float e = al * fmaf(nec, x3[j], x4[j]);  // gamma * eb  (x3 = +h P^T)
           const float y = ze * fmaf(en, x5[j], x6[j]);   // yb / gamma
           const float be = bb * e;
           if (!st_ok) {
@@ -737,6 +780,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       if (GATE == GATE_VECTOR) sCarry[wg * 128 + kch] = run;
     }
     STAMP(11);  // main epilogue loop done
+    STAMP0(13);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -806,6 +850,18 @@ long long* g_prof = nullptr;
 #endif
 constexpr size_t TC_SMEM = Smem::TOTAL + 1024;
 
+// mul = ceil(2^(31 + ceil(log2 d)) / d), shift = ceil(log2 d) - 1: exact for every dividend below 2^31.
+FastDiv make_fastdiv(int d) {
+  FastDiv f;
+  f.div = (uint32_t)d;
+  int lg = 0;
+  while ((1ll << lg) < d) lg++;
+  const int pw = 31 + lg;
+  f.mul = (uint32_t)(((1ull << pw) + (uint64_t)d - 1) / (uint64_t)d);
+  f.shift = (uint32_t)(pw - 32);
+  return f;
+}
+
 int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -841,16 +897,16 @@ cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers
   const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
   CUtensorMap tm[10];
   bool ok = encode_tmap_2d(&tm[0], a.Akk, 2, (uint64_t)H * 64, rows, (uint64_t)H * 128, 64, 64) &&
-            encode_tmap_2d(&tm[1], s.dR, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
-            encode_tmap_2d(&tm[2], s.dR_lo, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+            encode_tmap_panels(&tm[1], s.dR, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
+            encode_tmap_panels(&tm[2], s.dR_lo, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
             encode_tmap_2d(&tm[3], a.d_o, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
-            encode_tmap_2d(&tm[4], s.v_new, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
-            encode_tmap_2d(&tm[5], s.h, 2, 128, srows, 256, 64, 128) &&
-            encode_tmap_2d(&tm[6], s.dh, 2, 128, srows, 256, 64, 128) &&
-            encode_tmap_2d(&tm[7], a.v, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
-            encode_tmap_2d(&tm[8], a.k, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64);
+            encode_tmap_panels(&tm[4], s.v_new, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
+            encode_tmap_panels(&tm[5], s.h, 2, 128, srows, 256, 128, 2) &&
+            encode_tmap_panels(&tm[6], s.dh, 2, 128, srows, 256, 128, 2) &&
+            encode_tmap_panels(&tm[7], a.v, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
+            encode_tmap_panels(&tm[8], a.k, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2);
   if (ok && gate_mode_of(a.family) == GATE_VECTOR)
-    ok = encode_tmap_2d(&tm[9], a.g, 4, (uint64_t)H * 128, rows, (uint64_t)H * 512, 32, 64);
+    ok = encode_tmap_panels(&tm[9], a.g, 4, (uint64_t)H * 128, rows, (uint64_t)H * 512, 64, 4);
   else
     tm[9] = tm[8];  // never dereferenced without a vector gate
   if (!ok) return cudaErrorInvalidValue;
@@ -866,6 +922,8 @@ cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers
 #endif
   p.T = T; p.H = H; p.NT = NT; p.total_chunks = B * H * NT; p.out_f32 = a.out_dtype == REWY_OUT_F32;
   p.scale = a.scale;
+  p.div_nt = make_fastdiv(NT);
+  p.div_h = make_fastdiv(H);
   switch (a.family) {
     case REWY_DELTA: e = run<GATE_NONE, false>(tm, p, st); break;
     case REWY_GDN: e = run<GATE_SCALAR, false>(tm, p, st); break;

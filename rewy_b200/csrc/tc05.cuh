@@ -52,6 +52,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
   return false;
 }
 
+// One lane of a fully active warp (used inside warp-uniform branches, so that the operands of the single-thread
+// instructions issued under it stay warp-uniform values).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- proxies and fences ------------------------------------------------------------------------
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -68,6 +80,15 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* m, int
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
           smem_u32(dst)),
       "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// 3-D tiled load (see encode_tmap_panels: the third coordinate walks over 128-byte column panels of the same rows).
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
 
@@ -192,5 +213,11 @@ __device__ __forceinline__ float round_tf32(float x) {
 // unavailable or the encode fails.
 bool encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
                     uint32_t box_cols, uint32_t box_rows);
+
+// Same tensor seen as `panels` column panels of 128 bytes each: one load of the box (128 bytes x box_rows x panels)
+// at coordinates (first column, first row, 0) writes the panels one after the other, each as box_rows rows of 128
+// swizzled bytes - the operand layout of a K extent (or an MN extent) wider than one swizzle atom.
+bool encode_tmap_panels(CUtensorMap* out, const void* base, int elem_bytes, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
+                        uint32_t box_rows, uint32_t panels);
 
 }  // namespace rewy
