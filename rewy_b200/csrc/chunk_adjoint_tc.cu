@@ -66,11 +66,9 @@ struct Smem {
   static constexpr uint32_t GT = EHI;                  // g tile of the next chunk (4 panels [64 t][32 k] FP32) lands in the Ec tiles
   static constexpr uint32_t VT = HHI;                  // v tile (2 panels [64 i][64 v]) aliases the two hi tiles until P is done
   static constexpr uint32_t TILES_END = ELO + 16384;   // 221184
-  // Per-channel partial sums of the gate epilogue live in the first P tile: it is dead from the moment the
-  // products that read P are complete until the next chunk's P epilogue.
-  static constexpr uint32_t HD = DOP + 8192;           // float[4][128] sum_v h*dh per channel, one row per value quarter
-  static constexpr uint32_t END = HD + 2048;           // float[4][128] chunk-end gate term per channel, per token quarter
-  static constexpr uint32_t CARRY = END + 2048;        // float[4][128] gate-gradient totals of each token quarter
+  static constexpr uint32_t QT = DOP + 8192;           // q tile of the NEXT chunk: its two panels [64 t][64 k] land in the two P
+                                                       // tiles (16384 apart) once the products that read P are complete, and
+                                                       // are read into registers at chunk start, before P is written again
   static constexpr uint32_t BETA = TILES_END;          // float[64]
   static constexpr uint32_t DBETA = BETA + 256;        // float[64]
   static constexpr uint32_t GS = DBETA + 256;          // float[64] scalar gate rows
@@ -90,6 +88,9 @@ enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C12, BAR_C3, BAR_G, BA
 
 // TMEM column plan (512 columns allocated).
 constexpr uint32_t TM_P = 0, TM_HD = 128, TM_X1 = 192, TM_X3 = 256, TM_X2 = 320, TM_X4 = 384, TM_X5 = 0, TM_X6 = 64;
+// Per-channel scratch of the gate epilogue in the last 64 columns (lane = key channel): column TM_SCR + wg holds
+// sum_v h*dh of value quarter wg, +4 the chunk-end sums and +8 the gate-gradient totals of token quarter wg.
+constexpr uint32_t TM_SCR = 448;
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&r)[16]) {
   uint32_t u[16];
@@ -102,6 +103,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&r)[16]) {
 #pragma unroll
   for (int i = 0; i < 16; i++) r[i] = __uint_as_float(u[i]);
 }
+
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, float x) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(__float_as_uint(x)) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&r)[8]) {
   uint32_t u[8];
@@ -206,6 +212,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
                         const __grid_constant__ CUtensorMap tmR, const __grid_constant__ CUtensorMap tmH,
                         const __grid_constant__ CUtensorMap tmDH, const __grid_constant__ CUtensorMap tmV,
                         const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmG,
+                        const __grid_constant__ CUtensorMap tmDG, const __grid_constant__ CUtensorMap tmQ,
                         const TcParams p) {
   extern __shared__ __align__(1024) unsigned char raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
@@ -214,9 +221,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   float* sGs = reinterpret_cast<float*>(sm + Smem::GS);
   float* sDgs = reinterpret_cast<float*>(sm + Smem::DGS);
   float* sMinMax = reinterpret_cast<float*>(sm + Smem::MINMAX);
-  float* sHd = reinterpret_cast<float*>(sm + Smem::HD);
-  float* sEnd = reinterpret_cast<float*>(sm + Smem::END);
-  float* sCarry = reinterpret_cast<float*>(sm + Smem::CARRY);
   float* sDbP = reinterpret_cast<float*>(sm + Smem::DBP);
   float* sDbW = reinterpret_cast<float*>(sm + Smem::DBW);
   float* sDgW = reinterpret_cast<float*>(sm + Smem::DGW);
@@ -241,6 +245,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     prefetch_tmap(&tmAkk); prefetch_tmap(&tmDRhi); prefetch_tmap(&tmDRlo); prefetch_tmap(&tmDO);
     prefetch_tmap(&tmR); prefetch_tmap(&tmH); prefetch_tmap(&tmDH); prefetch_tmap(&tmV);
     prefetch_tmap(&tmK); prefetch_tmap(&tmG);
+    if (GATE == GATE_VECTOR) prefetch_tmap(&tmDG);
+    prefetch_tmap(&tmQ);
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, 512);
@@ -267,11 +273,12 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   };
   // all tile loads of one chunk (issued by thread 0): A = {Akk, dR hi/lo, v}, B = {dO, R}, C = {h}
   auto issue_loads = [&](int chunk) {
-    const int bh = p.div_nt.quot(chunk), n = chunk - bh * NT, b = p.div_h.quot(bh), h = bh - b * H;
+    const int bn = p.div_h.quot(chunk), h = chunk - bn * H, b = p.div_nt.quot(bn), n = bn - b * NT;
     const int row0 = b * T + n * C, hrow0 = ((b * NT + n) * H + h) * 128;
     // k (and the vector gate) of the chunk: read into registers at its start, so they get a barrier of their own
-    mbar_expect_tx(&bars[BAR_G], 16384 + (GATE == GATE_VECTOR ? 32768 : 0));
+    mbar_expect_tx(&bars[BAR_G], 2 * 16384 + (GATE == GATE_VECTOR ? 32768 : 0));
     tma_load_3d(sm + Smem::KT, &tmK, h * 128, row0, 0, &bars[BAR_G]);
+    for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::QT + pn * 16384, &tmQ, h * 128 + 64 * pn, row0, &bars[BAR_G]);
     if (GATE == GATE_VECTOR) tma_load_3d(sm + Smem::GT, &tmG, h * 128, row0, 0, &bars[BAR_G]);
     mbar_expect_tx(&bars[BAR_A], 8192 + 3 * 16384);
     tma_load_2d(sm + Smem::AKK, &tmAkk, h * 64, row0, &bars[BAR_A]);
@@ -288,8 +295,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   if (tid == 0 && (int)blockIdx.x < p.total_chunks) issue_loads(blockIdx.x);
   // beta (and the scalar gate) of a chunk are fetched one chunk ahead into a register of threads 0..63
   auto row_base1 = [&](int chunk) -> size_t {
-    const int bh = p.div_nt.quot(chunk), n = chunk - bh * NT, b = p.div_h.quot(bh);
-    return ((size_t)b * T + (size_t)n * C) * H + (bh - b * H);
+    const int bn = p.div_h.quot(chunk), h = chunk - bn * H, b = p.div_nt.quot(bn), n = bn - b * NT;
+    return ((size_t)b * T + (size_t)n * C) * H + h;
   };
   float beta_pref = 0.f, gs_pref = 0.f;
   if (tid < C && (int)blockIdx.x < p.total_chunks) {
@@ -307,7 +314,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 #endif
   for (int chunk = blockIdx.x; chunk < p.total_chunks && alive; chunk += gridDim.x) {
     STAMP(0);
-    const int bh = p.div_nt.quot(chunk), n = chunk - bh * NT, b = p.div_h.quot(bh), h = bh - b * H;
+    // Work order: head fastest, then chunk, then batch.  CTAs that run at the same time then read the same token rows
+    // (the heads of a row are contiguous in memory) and neighbouring state tiles.
+    const int bn = p.div_h.quot(chunk), h = chunk - bn * H, b = p.div_nt.quot(bn), n = bn - b * NT;
     const int row0 = b * T + n * C;                       // first token row in [B*T]
     const size_t base128 = ((size_t)row0 * H + h) * 128;
     const size_t base1 = (size_t)row0 * H + h;
@@ -329,18 +338,16 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     // ---- this thread's 32 tokens of its key channel: k and q (packed BF16 pair) and the gate row ------------
     uint32_t kq[HALF];
     float g[HALF];
-    // q straight from global memory (first needed after P, so its latency hides behind the tile building);
-    // k and g from the tiles TMA brought in while the previous chunk's epilogue ran
-    uint32_t qv[HALF];  // merged into kq only when q is first needed, so nothing waits on these loads early
-#pragma unroll
-    for (int j = 0; j < HALF; j++) qv[j] = *reinterpret_cast<const uint16_t*>(p.q + base128 + (size_t)(t0 + j) * ldt + kch);
+    // k, q and g from the tiles TMA brought in while the previous chunk's epilogue ran
     STAMP(13);
     wait(BAR_G, 11);
     STAMP(14);
 #pragma unroll
     for (int j = 0; j < HALF; j++) {
       const int t = t0 + j;
-      kq[j] = *reinterpret_cast<const uint16_t*>(sm + Smem::KT + (kch >> 6) * 8192 + swz(t, (kch & 63) >> 3) + (kch & 7) * 2);
+      const uint32_t off = swz(t, (kch & 63) >> 3) + (kch & 7) * 2;
+      kq[j] = (uint32_t) * reinterpret_cast<const uint16_t*>(sm + Smem::KT + (kch >> 6) * 8192 + off) |
+              ((uint32_t) * reinterpret_cast<const uint16_t*>(sm + Smem::QT + (kch >> 6) * 16384 + off) << 16);
       g[j] = GATE == GATE_VECTOR
                  ? *reinterpret_cast<const float*>(sm + Smem::GT + (kch >> 5) * 8192 + swz(t, (kch & 31) >> 2) + (kch & 3) * 4)
                  : 0.f;
@@ -369,12 +376,14 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       cen = 0.5f * (lo + hi);
       wide = !(hi - lo < SPAN_LIMIT);
     }
+    // the previous chunk's gate-gradient tile (in the Yc tiles) must have left shared memory before they are rebuilt
+    if (GATE == GATE_VECTOR && tid == 0) tma_store_wait_read();
     if (__syncthreads_or(wide ? 1 : 0)) {
       // wide gate span: leave the chunk to the exact pairwise kernel; drain the loads already in flight
       if (tid == 0) {
         wait(BAR_A, 101); wait(BAR_B, 102); wait(BAR_C, 103);
         int idx = atomicAdd(&p.wide_list[0], 1);
-        p.wide_list[1 + idx] = chunk;
+        p.wide_list[1 + idx] = (b * H + h) * NT + n;  // the pairwise kernel's chunk numbering: (batch, head) major
       }
       ph ^= used;
       alive = __syncthreads_and(alive ? 1 : 0) != 0;
@@ -627,7 +636,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 #pragma unroll
       for (int j = 0; j < 8; j++) {
         const int jj = t8 * 8 + j;
-        kq[jj] |= qv[jj] << 16;
         x[j] = qf(jj) * (GATE == GATE_NONE ? 1.f : g[jj]);
       }
       uint4 hi, lo;
@@ -653,7 +661,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           hd += x.x * y.x + x.y * y.y;
         }
       }
-      sHd[wg * 128 + kch] = hd;
+      tmem_st1(tlane + TM_SCR + wg, hd);
+      tmem_st_wait();
     }
     STAMP(23);
     fence_async_smem();
@@ -712,10 +721,12 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     // every tile of this chunk has been consumed by the tensor core and (barrier above) by the threads: start the
     // next chunk's loads under the rest of the epilogue
     STAMP0(11);
+#ifndef REWY_EXP_LATE_LOADS
     if (warp == 0 && alive && next_chunk < p.total_chunks) {
       if (elect_one()) issue_loads(next_chunk);
       __syncwarp();
     }
+#endif
     STAMP0(12);
     STAMP(9);
     // pass B: dk, db, gate rows in reverse token order
@@ -776,9 +787,16 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           if (lane < 8) sDgW[warp * 16 + 8 * c8 + lane] = s;
         }
       }
-      if (GATE != GATE_NONE) sEnd[wg * 128 + kch] = colsum;
-      if (GATE == GATE_VECTOR) sCarry[wg * 128 + kch] = run;
+      if (GATE != GATE_NONE) tmem_st1(tlane + TM_SCR + 4 + wg, colsum);
+      if (GATE == GATE_VECTOR) tmem_st1(tlane + TM_SCR + 8 + wg, run);
+      if (GATE != GATE_NONE) tmem_st_wait();
     }
+#ifdef REWY_EXP_LATE_LOADS
+    if (warp == 0 && alive && next_chunk < p.total_chunks) {
+      if (elect_one()) issue_loads(next_chunk);
+      __syncwarp();
+    }
+#endif
     STAMP(11);  // main epilogue loop done
     STAMP0(13);
     tc_fence_before_sync();
@@ -788,15 +806,20 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     if (alive) {
       // chunk-end term of this channel: lambda * sum_v h dh + sum_t k 2^(g_last - g) (R dh^T)
       float endk = 0.f;
-      if (GATE != GATE_NONE)
-        endk = ex2(gl) * (sHd[kch] + sHd[128 + kch] + sHd[256 + kch] + sHd[384 + kch]) +
-               (sEnd[kch] + sEnd[128 + kch] + sEnd[256 + kch] + sEnd[384 + kch]);
+      float scr[16];
+      if (GATE != GATE_NONE) {
+        tmem_ld16(tlane + TM_SCR, scr);
+        tmem_ld_wait();
+        endk = ex2(gl) * (scr[0] + scr[1] + scr[2] + scr[3]) + (scr[4] + scr[5] + scr[6] + scr[7]);
+      }
       if (GATE == GATE_VECTOR) {
         float carry = endk;  // the chunk-end term sits on token 63: part of every carry
-        for (int w2 = wg + 1; w2 < NWG; w2++) carry += sCarry[w2 * 128 + kch];
 #pragma unroll
-        for (int jj = 0; jj < HALF; jj++)
-          if (st_ok) p.dg[base128 + (size_t)(t0 + jj) * ldt + kch] = sPark[(t0 + jj) * 128 + kch] + carry;
+        for (int w2 = 1; w2 < NWG; w2++) carry += w2 > wg ? scr[8 + w2] : 0.f;
+        // the finished [64 tokens][128 channels] tile leaves as one bulk store after the barrier below
+#pragma unroll
+        for (int jj = 0; jj < HALF; jj++) sPark[(t0 + jj) * 128 + kch] += carry;
+        fence_async_smem();
       }
       if (!VB && tid < C) {
         float db = 0.f;
@@ -835,11 +858,16 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     STAMP(10);  // epilogue done
     ph ^= used;
     alive = __syncthreads_and(alive ? 1 : 0) != 0;
+    if (GATE == GATE_VECTOR && tid == 0 && alive && st_ok) {
+      tma_store_2d(&tmDG, sPark, h * 128, row0);
+      tma_store_commit();
+    }
 #ifdef REWY_PHASE_PROF
     prof_it++;
 #endif
   }
 
+  if (GATE == GATE_VECTOR && tid == 0) tma_store_wait_read();  // shared memory stays valid until the last store has read it
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tb, 512);
@@ -878,7 +906,7 @@ cudaError_t run1(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
   if (e != cudaSuccess) return e;
   const int grid = p.total_chunks < sm_count() ? p.total_chunks : sm_count();
-  kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9], p);
+  kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9], tm[10], tm[11], p);
   count_launch();
   return cudaGetLastError();
 }
@@ -895,7 +923,7 @@ cudaError_t run(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
 cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* ctrl, cudaStream_t st) {
   const int B = a.B, T = a.T, H = a.H, NT = T / C;
   const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
-  CUtensorMap tm[10];
+  CUtensorMap tm[12];
   bool ok = encode_tmap_2d(&tm[0], a.Akk, 2, (uint64_t)H * 64, rows, (uint64_t)H * 128, 64, 64) &&
             encode_tmap_panels(&tm[1], s.dR, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
             encode_tmap_panels(&tm[2], s.dR_lo, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
@@ -904,11 +932,13 @@ cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers
             encode_tmap_panels(&tm[5], s.h, 2, 128, srows, 256, 128, 2) &&
             encode_tmap_panels(&tm[6], s.dh, 2, 128, srows, 256, 128, 2) &&
             encode_tmap_panels(&tm[7], a.v, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
-            encode_tmap_panels(&tm[8], a.k, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2);
+            encode_tmap_panels(&tm[8], a.k, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
+            encode_tmap_2d(&tm[11], a.q, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64);
   if (ok && gate_mode_of(a.family) == GATE_VECTOR)
-    ok = encode_tmap_panels(&tm[9], a.g, 4, (uint64_t)H * 128, rows, (uint64_t)H * 512, 64, 4);
+    ok = encode_tmap_panels(&tm[9], a.g, 4, (uint64_t)H * 128, rows, (uint64_t)H * 512, 64, 4) &&
+         encode_tmap_2d(&tm[10], a.dg, 4, (uint64_t)H * 128, rows, (uint64_t)H * 512, 128, 64, false);
   else
-    tm[9] = tm[8];  // never dereferenced without a vector gate
+    tm[9] = tm[10] = tm[8];  // never dereferenced without a vector gate
   if (!ok) return cudaErrorInvalidValue;
   cudaError_t e = cudaMemsetAsync(ctrl + 1, 0, sizeof(int), st);  // wide-chunk count; the status word is kept
   if (e != cudaSuccess) return e;

@@ -83,6 +83,18 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* m, int
       : "memory");
 }
 
+// 2-D tiled store shared -> global (bulk async group of the issuing thread).  The shared tile must have been
+// written (generic proxy), fenced with fence_async_smem() and made visible by a barrier before this is issued.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until every committed store group of this thread has finished READING shared memory.
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
 // 3-D tiled load (see encode_tmap_panels: the third coordinate walks over 128-byte column panels of the same rows).
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, int c0, int c1, int c2, uint64_t* bar) {
   asm volatile(
@@ -209,10 +221,11 @@ __device__ __forceinline__ float round_tf32(float x) {
 }  // namespace tc
 
 // Host side: encode a 2-D tiled tensor map (row-major tensor of `rows` x `cols` elements, `pitch_bytes` between
-// rows) whose box is box_cols x box_rows with 128-byte swizzle.  Returns false if the driver entry point is
+// rows) whose box is box_cols x box_rows with 128-byte swizzle (or, with swizzle128 = false, dense rows of box_cols
+// elements).  Returns false if the driver entry point is
 // unavailable or the encode fails.
 bool encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
-                    uint32_t box_cols, uint32_t box_rows);
+                    uint32_t box_cols, uint32_t box_rows, bool swizzle128 = true);
 
 // Same tensor seen as `panels` column panels of 128 bytes each: one load of the box (128 bytes x box_rows x panels)
 // at coordinates (first column, first row, 0) writes the panels one after the other, each as box_rows rows of 128
