@@ -271,28 +271,38 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   auto wait = [&](int b, int code) {
     if (alive) alive = mbar_wait(&bars[b], (ph >> b) & 1u, p.err, code);
   };
-  // all tile loads of one chunk (issued by thread 0): A = {Akk, dR hi/lo, v}, B = {dO, R}, C = {h}
-  auto issue_loads = [&](int chunk) {
+  // Tile loads of one chunk, issued by one thread, in three instalments so that the SM's memory port is never
+  // saturated for long while the epilogue's global stores need it:
+  //   LOAD_G  {k, q, g}            needed at the start of the chunk     -> issued before the previous chunk's pass B
+  //   LOAD_A  {Akk, dR hi/lo, v}   needed by the first product          -> issued after the previous chunk's pass B
+  //   LOAD_BC {dO, R} and {h}      needed by the second product group   -> issued at the start of the chunk itself
+  constexpr int LOAD_G = 1, LOAD_A = 2, LOAD_BC = 4;
+  auto issue_loads = [&](int chunk, int parts) {
     const int bn = p.div_h.quot(chunk), h = chunk - bn * H, b = p.div_nt.quot(bn), n = bn - b * NT;
     const int row0 = b * T + n * C, hrow0 = ((b * NT + n) * H + h) * 128;
-    // k (and the vector gate) of the chunk: read into registers at its start, so they get a barrier of their own
-    mbar_expect_tx(&bars[BAR_G], 2 * 16384 + (GATE == GATE_VECTOR ? 32768 : 0));
-    tma_load_3d(sm + Smem::KT, &tmK, h * 128, row0, 0, &bars[BAR_G]);
-    for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::QT + pn * 16384, &tmQ, h * 128 + 64 * pn, row0, &bars[BAR_G]);
-    if (GATE == GATE_VECTOR) tma_load_3d(sm + Smem::GT, &tmG, h * 128, row0, 0, &bars[BAR_G]);
-    mbar_expect_tx(&bars[BAR_A], 8192 + 3 * 16384);
-    tma_load_2d(sm + Smem::AKK, &tmAkk, h * 64, row0, &bars[BAR_A]);
-    tma_load_3d(sm + Smem::DRHI, &tmDRhi, h * 128, row0, 0, &bars[BAR_A]);
-    tma_load_3d(sm + Smem::DRLO, &tmDRlo, h * 128, row0, 0, &bars[BAR_A]);
-    tma_load_3d(sm + Smem::VT, &tmV, h * 128, row0, 0, &bars[BAR_A]);
-    mbar_expect_tx(&bars[BAR_B], 2 * 16384);
-    for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::DOP + pn * 16384, &tmDO, h * 128 + 64 * pn, row0, &bars[BAR_B]);
-    tma_load_3d(sm + Smem::R, &tmR, h * 128, row0, 0, &bars[BAR_B]);
-    mbar_expect_tx(&bars[BAR_C], 32768);
-    tma_load_3d(sm + Smem::HS, &tmH, 0, hrow0, 0, &bars[BAR_C]);
+    if (parts & LOAD_G) {
+      mbar_expect_tx(&bars[BAR_G], 2 * 16384 + (GATE == GATE_VECTOR ? 32768 : 0));
+      tma_load_3d(sm + Smem::KT, &tmK, h * 128, row0, 0, &bars[BAR_G]);
+      for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::QT + pn * 16384, &tmQ, h * 128 + 64 * pn, row0, &bars[BAR_G]);
+      if (GATE == GATE_VECTOR) tma_load_3d(sm + Smem::GT, &tmG, h * 128, row0, 0, &bars[BAR_G]);
+    }
+    if (parts & LOAD_A) {
+      mbar_expect_tx(&bars[BAR_A], 8192 + 3 * 16384);
+      tma_load_2d(sm + Smem::AKK, &tmAkk, h * 64, row0, &bars[BAR_A]);
+      tma_load_3d(sm + Smem::DRHI, &tmDRhi, h * 128, row0, 0, &bars[BAR_A]);
+      tma_load_3d(sm + Smem::DRLO, &tmDRlo, h * 128, row0, 0, &bars[BAR_A]);
+      tma_load_3d(sm + Smem::VT, &tmV, h * 128, row0, 0, &bars[BAR_A]);
+    }
+    if (parts & LOAD_BC) {
+      mbar_expect_tx(&bars[BAR_B], 2 * 16384);
+      for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::DOP + pn * 16384, &tmDO, h * 128 + 64 * pn, row0, &bars[BAR_B]);
+      tma_load_3d(sm + Smem::R, &tmR, h * 128, row0, 0, &bars[BAR_B]);
+      mbar_expect_tx(&bars[BAR_C], 32768);
+      tma_load_3d(sm + Smem::HS, &tmH, 0, hrow0, 0, &bars[BAR_C]);
+    }
   };
 
-  if (tid == 0 && (int)blockIdx.x < p.total_chunks) issue_loads(blockIdx.x);
+  if (tid == 0 && (int)blockIdx.x < p.total_chunks) issue_loads(blockIdx.x, LOAD_G | LOAD_A);
   // beta (and the scalar gate) of a chunk are fetched one chunk ahead into a register of threads 0..63
   auto row_base1 = [&](int chunk) -> size_t {
     const int bn = p.div_h.quot(chunk), h = chunk - bn * H, b = p.div_nt.quot(bn), n = bn - b * NT;
@@ -323,6 +333,10 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     const int hrow0 = ((b * NT + n) * H + h) * 128;        // first row of this chunk's state in [B*NT*H*128]
     const int next_chunk = chunk + gridDim.x;
     uint32_t used = (1u << BAR_A) | (1u << BAR_B) | (1u << BAR_C) | (1u << BAR_G);
+    if (warp == 0) {
+      if (elect_one()) issue_loads(chunk, LOAD_BC);
+      __syncwarp();
+    }
     STAMP(28);
 
     if (tid < C) {
@@ -387,7 +401,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       }
       ph ^= used;
       alive = __syncthreads_and(alive ? 1 : 0) != 0;
-      if (tid == 0 && alive && next_chunk < p.total_chunks) issue_loads(next_chunk);
+      if (tid == 0 && alive && next_chunk < p.total_chunks) issue_loads(next_chunk, LOAD_G | LOAD_A);
       continue;
     }
     STAMP(1);  // operands in registers, centre known
@@ -721,12 +735,10 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     // every tile of this chunk has been consumed by the tensor core and (barrier above) by the threads: start the
     // next chunk's loads under the rest of the epilogue
     STAMP0(11);
-#ifndef REWY_EXP_LATE_LOADS
     if (warp == 0 && alive && next_chunk < p.total_chunks) {
-      if (elect_one()) issue_loads(next_chunk);
+      if (elect_one()) issue_loads(next_chunk, LOAD_G);
       __syncwarp();
     }
-#endif
     STAMP0(12);
     STAMP(9);
     // pass B: dk, db, gate rows in reverse token order
@@ -791,12 +803,10 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       if (GATE == GATE_VECTOR) tmem_st1(tlane + TM_SCR + 8 + wg, run);
       if (GATE != GATE_NONE) tmem_st_wait();
     }
-#ifdef REWY_EXP_LATE_LOADS
     if (warp == 0 && alive && next_chunk < p.total_chunks) {
-      if (elect_one()) issue_loads(next_chunk);
+      if (elect_one()) issue_loads(next_chunk, LOAD_A);
       __syncwarp();
     }
-#endif
     STAMP(11);  // main epilogue loop done
     STAMP0(13);
     tc_fence_before_sync();
