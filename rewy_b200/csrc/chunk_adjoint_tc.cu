@@ -64,6 +64,8 @@ struct Smem {
   static constexpr uint32_t KT = HLO;                  // k tile of the NEXT chunk (2 panels [64 t][64 k]) lands in the two lo
                                                        // tiles once they are dead and is read into registers at chunk start
   static constexpr uint32_t GT = EHI;                  // g tile of the next chunk (4 panels [64 t][32 k] FP32) lands in the Ec tiles
+  static constexpr uint32_t DVT = HLO;                 // dv tile (2 panels [64 i][64 v]) between the P epilogue and its bulk store,
+                                                       // which has read it before the lo tiles are written
   static constexpr uint32_t VT = HHI;                  // v tile (2 panels [64 i][64 v]) aliases the two hi tiles until P is done
   static constexpr uint32_t TILES_END = ELO + 16384;   // 221184
   static constexpr uint32_t QT = DOP + 8192;           // q tile of the NEXT chunk: its two panels [64 t][64 k] land in the two P
@@ -213,7 +215,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
                         const __grid_constant__ CUtensorMap tmDH, const __grid_constant__ CUtensorMap tmV,
                         const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmG,
                         const __grid_constant__ CUtensorMap tmDG, const __grid_constant__ CUtensorMap tmQ,
-                        const TcParams p) {
+                        const __grid_constant__ CUtensorMap tmDV, const TcParams p) {
   extern __shared__ __align__(1024) unsigned char raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   float* sBeta = reinterpret_cast<float*>(sm + Smem::BETA);
@@ -233,11 +235,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   const int T = p.T, H = p.H, NT = p.NT;
   const size_t ldt = (size_t)H * 128;
   const float scale = p.scale;
-#ifdef REWY_EXP_NOSTORE
-  const bool st_ok = p.scale < 0.f;
-#else
-  constexpr bool st_ok = true;
-#endif
 
   if (tid == 0) {
     for (int i = 0; i < NUM_BARS; i++) mbar_init(&bars[i], 1);
@@ -246,7 +243,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     prefetch_tmap(&tmR); prefetch_tmap(&tmH); prefetch_tmap(&tmDH); prefetch_tmap(&tmV);
     prefetch_tmap(&tmK); prefetch_tmap(&tmG);
     if (GATE == GATE_VECTOR) prefetch_tmap(&tmDG);
-    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmDV);
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, 512);
@@ -257,6 +254,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   tc_fence_after_sync();
   const uint32_t tb = *tmem_slot;
   const uint32_t tlane = tb + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's TMEM lanes
+  // the one thread that issues every TMA copy, tensor-core product and commit (bulk store groups are per thread)
+  const bool leader = warp == 0 && elect_one();
   uint32_t ph = 0;                                                  // phase bit per barrier
   bool alive = true;                                                // false once a bounded wait gave up
 
@@ -334,7 +333,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     const int next_chunk = chunk + gridDim.x;
     uint32_t used = (1u << BAR_A) | (1u << BAR_B) | (1u << BAR_C) | (1u << BAR_G);
     if (warp == 0) {
-      if (elect_one()) issue_loads(chunk, LOAD_BC);
+      if (leader) issue_loads(chunk, LOAD_BC);
       __syncwarp();
     }
     STAMP(28);
@@ -391,7 +390,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       wide = !(hi - lo < SPAN_LIMIT);
     }
     // the previous chunk's gate-gradient tile (in the Yc tiles) must have left shared memory before they are rebuilt
-    if (GATE == GATE_VECTOR && tid == 0) tma_store_wait_read();
+    if (GATE == GATE_VECTOR && leader) tma_store_wait_read();
     if (__syncthreads_or(wide ? 1 : 0)) {
       // wide gate span: leave the chunk to the exact pairwise kernel; drain the loads already in flight
       if (tid == 0) {
@@ -420,7 +419,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       STAMP0(1);
       if (alive) {
         tc_fence_after_sync();
-        if (elect_one()) {
+        if (leader) {
 #pragma unroll
         for (int ks = 0; ks < 4; ks++)
           mma_f16_lo(tb + TM_P, dl(Smem::AKK + ks * 2048, 0), dl(Smem::DRHI + ks * 2048, 8192), ID_P, ks > 0);
@@ -458,7 +457,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     tc_fence_after_sync();
     STAMP(3);  // P ready
     if (warp == 0 && alive) {
-      if (elect_one()) {
+      if (leader) {
         mbar_expect_tx(&bars[BAR_D], 32768);
         tma_load_3d(sm + Smem::DHT, &tmDH, 0, hrow0, 0, &bars[BAR_D]);
       }
@@ -504,10 +503,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           dvp[j] = pack_bf16(w0 * x[2 * j], w1 * x[2 * j + 1]);
           pp[j] = pack_bf16(x[2 * j], x[2 * j + 1]);
         }
-        if (st_ok) {
-        *reinterpret_cast<uint4*>(p.dv + go + v0) = make_uint4(dvp[0], dvp[1], dvp[2], dvp[3]);
-        *reinterpret_cast<uint4*>(p.dv + go + v0 + 8) = make_uint4(dvp[4], dvp[5], dvp[6], dvp[7]);
-        }
+        // dv tile (same panel layout as the v tile) in the dead k tile; it leaves by one bulk store after the barrier
+        *reinterpret_cast<uint4*>(sm + Smem::DVT + vp * 8192 + swz(i, vc)) = make_uint4(dvp[0], dvp[1], dvp[2], dvp[3]);
+        *reinterpret_cast<uint4*>(sm + Smem::DVT + vp * 8192 + swz(i, vc + 1)) = make_uint4(dvp[4], dvp[5], dvp[6], dvp[7]);
         if (VB) {
           if (OUTF32) {
             float* o = reinterpret_cast<float*>(p.dwg) + go + v0;
@@ -542,8 +540,13 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       wait(BAR_B, 3);
       if (alive) {
         tc_fence_after_sync();
-        if (elect_one()) {
+        if (leader) {
+          tma_store_3d(&tmDV, sm + Smem::DVT, h * 128, row0, 0);
+          tma_store_commit();
           mma_kmajor<8>(tb + TM_HD, dl(Smem::DOP, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
+          // the dv tile sits where the epilogue of this product writes: everyone waits for this commit first, and
+          // it is only issued once the store has read the tile
+          tma_store_wait_read();
           mma_commit(&bars[BAR_HD]);
         }
         STAMP0(4);
@@ -619,7 +622,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     if (warp == 0 && alive) {
       STAMP0(5);
       tc_fence_after_sync();
-      if (elect_one()) {
+      if (leader) {
         // [X1 | X3] = h [dO ; P]^T as one N=128 product (the sign of X3 is applied in the epilogue).  It goes first
         // and gets a commit of its own: as soon as it is done the h buffer can take the Qc tiles and the P tile the
         // per-channel scratch, while the matrix-intra products still run
@@ -685,7 +688,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     if (warp == 0 && alive) {
       STAMP0(9);
       tc_fence_after_sync();
-      if (elect_one()) {
+      if (leader) {
         mma_kmajor<8>(tb + TM_X5, dl(Smem::DHT, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
         mma_kmn4(tb + TM_X6, dl(Smem::QHI, 16), dl(Smem::HHI, 8192), ID_KMN, true);
         mma_kmn4(tb + TM_X6, dl(Smem::QLO, 16), dl(Smem::HHI, 8192), ID_KMN, true);
@@ -720,8 +723,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         const size_t go = go0 + (size_t)j * ldt;
         const float al = GATE == GATE_NONE ? 1.f : g[j];
         const float dq = al * fmaf(ecs, x1[j], x2[j]);
-        if (!st_ok) {
-        } else if (OUTF32)
+        if (OUTF32)
           reinterpret_cast<float*>(p.dq)[go] = dq;
         else
           reinterpret_cast<bf16*>(p.dq)[go] = f2bf(dq);
@@ -736,7 +738,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     // next chunk's loads under the rest of the epilogue
     STAMP0(11);
     if (warp == 0 && alive && next_chunk < p.total_chunks) {
-      if (elect_one()) issue_loads(next_chunk, LOAD_G);
+      if (leader) issue_loads(next_chunk, LOAD_G);
       __syncwarp();
     }
     STAMP0(12);
@@ -770,8 +772,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           const float e = al * fmaf(nec, x3[j], x4[j]);  // gamma * eb  (x3 = +h P^T)
           const float y = ze * fmaf(en, x5[j], x6[j]);   // yb / gamma
           const float be = bb * e;
-          if (!st_ok) {
-          } else if (OUTF32) {
+          if (OUTF32) {
             reinterpret_cast<float*>(p.dk)[go] = be + y;
             if (VB) reinterpret_cast<float*>(p.dbg)[go] = kk * e;
           } else {
@@ -804,7 +805,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       if (GATE != GATE_NONE) tmem_st_wait();
     }
     if (warp == 0 && alive && next_chunk < p.total_chunks) {
-      if (elect_one()) issue_loads(next_chunk, LOAD_A);
+      if (leader) issue_loads(next_chunk, LOAD_A);
       __syncwarp();
     }
     STAMP(11);  // main epilogue loop done
@@ -868,7 +869,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     STAMP(10);  // epilogue done
     ph ^= used;
     alive = __syncthreads_and(alive ? 1 : 0) != 0;
-    if (GATE == GATE_VECTOR && tid == 0 && alive && st_ok) {
+    if (GATE == GATE_VECTOR && leader && alive) {
       tma_store_2d(&tmDG, sPark, h * 128, row0);
       tma_store_commit();
     }
@@ -877,7 +878,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 #endif
   }
 
-  if (GATE == GATE_VECTOR && tid == 0) tma_store_wait_read();  // shared memory stays valid until the last store has read it
+  if (leader) tma_store_wait_read();  // shared memory stays valid until the last store has read it
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tb, 512);
@@ -916,7 +917,7 @@ cudaError_t run1(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
   if (e != cudaSuccess) return e;
   const int grid = p.total_chunks < sm_count() ? p.total_chunks : sm_count();
-  kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9], tm[10], tm[11], p);
+  kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9], tm[10], tm[11], tm[12], p);
   count_launch();
   return cudaGetLastError();
 }
@@ -933,7 +934,7 @@ cudaError_t run(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
 cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* ctrl, cudaStream_t st) {
   const int B = a.B, T = a.T, H = a.H, NT = T / C;
   const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
-  CUtensorMap tm[12];
+  CUtensorMap tm[13];
   bool ok = encode_tmap_2d(&tm[0], a.Akk, 2, (uint64_t)H * 64, rows, (uint64_t)H * 128, 64, 64) &&
             encode_tmap_panels(&tm[1], s.dR, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
             encode_tmap_panels(&tm[2], s.dR_lo, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
@@ -943,7 +944,8 @@ cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers
             encode_tmap_panels(&tm[6], s.dh, 2, 128, srows, 256, 128, 2) &&
             encode_tmap_panels(&tm[7], a.v, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
             encode_tmap_panels(&tm[8], a.k, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
-            encode_tmap_2d(&tm[11], a.q, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64);
+            encode_tmap_2d(&tm[11], a.q, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+            encode_tmap_panels(&tm[12], a.dv, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2);
   if (ok && gate_mode_of(a.family) == GATE_VECTOR)
     ok = encode_tmap_panels(&tm[9], a.g, 4, (uint64_t)H * 128, rows, (uint64_t)H * 512, 64, 4) &&
          encode_tmap_2d(&tm[10], a.dg, 4, (uint64_t)H * 128, rows, (uint64_t)H * 512, 128, 64, false);
