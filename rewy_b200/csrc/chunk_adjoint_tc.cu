@@ -54,20 +54,15 @@ struct Smem {
   static constexpr uint32_t DHI = HHI + 8192;          // dAkk hi; [dAqk hi ; dAkk hi] is one 128-row operand
   static constexpr uint32_t HLO = DHI + 8192;          // dAqk lo
   static constexpr uint32_t DLO = HLO + 8192;          // dAkk lo
-  static constexpr uint32_t YHI = DLO + 8192;          // Yc^T hi [128 k][64 t]                  16 KB
-  static constexpr uint32_t YLO = YHI + 16384;
-  static constexpr uint32_t EHI = YLO + 16384;         // Ec^T hi
-  static constexpr uint32_t ELO = EHI + 16384;
+  static constexpr uint32_t PARK = DLO + 8192;         // float [64 t][128 k]: parked gate-gradient rows, then the dg tile   32 KB
+  static constexpr uint32_t GT = PARK + 32768;         // g tile of the NEXT chunk (4 panels [64 t][32 k] FP32)                32 KB
   static constexpr uint32_t DHT = DRHI;                // dh tile (2 panels [128 k][64 v]) takes the dR tiles once P is done
-  static constexpr uint32_t QHI = HS;                  // Qc^T hi/lo take the h buffer once the products that read h are done
-  static constexpr uint32_t QLO = HS + 16384;
   static constexpr uint32_t KT = HLO;                  // k tile of the NEXT chunk (2 panels [64 t][64 k]) lands in the two lo
                                                        // tiles once they are dead and is read into registers at chunk start
-  static constexpr uint32_t GT = EHI;                  // g tile of the next chunk (4 panels [64 t][32 k] FP32) lands in the Ec tiles
   static constexpr uint32_t DVT = HLO;                 // dv tile (2 panels [64 i][64 v]) between the P epilogue and its bulk store,
                                                        // which has read it before the lo tiles are written
   static constexpr uint32_t VT = HHI;                  // v tile (2 panels [64 i][64 v]) aliases the two hi tiles until P is done
-  static constexpr uint32_t TILES_END = ELO + 16384;   // 221184
+  static constexpr uint32_t TILES_END = GT + 32768;    // 221184
   static constexpr uint32_t QT = DOP + 8192;           // q tile of the NEXT chunk: its two panels [64 t][64 k] land in the two P
                                                        // tiles (16384 apart) once the products that read P are complete, and
                                                        // are read into registers at chunk start, before P is written again
@@ -86,13 +81,17 @@ struct Smem {
 };
 static_assert(Smem::TOTAL + 1024 <= 232448, "shared memory plan exceeds the 227 KB per-CTA limit");
 
-enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C12, BAR_C3, BAR_G, BAR_Q, NUM_BARS };
+enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C3, BAR_G, BAR_Q, NUM_BARS };
 
 // TMEM column plan (512 columns allocated).
 constexpr uint32_t TM_P = 0, TM_HD = 128, TM_X1 = 192, TM_X3 = 256, TM_X2 = 320, TM_X4 = 384, TM_X5 = 0, TM_X6 = 64;
 // Per-channel scratch of the gate epilogue in the last 64 columns (lane = key channel): column TM_SCR + wg holds
 // sum_v h*dh of value quarter wg, +4 the chunk-end sums and +8 the gate-gradient totals of token quarter wg.
 constexpr uint32_t TM_SCR = 448;
+// Operand tiles of the matrix-intra products, written by their owner threads (lane = key channel; 16 tokens = 8
+// packed columns per thread; hi block then lo block, 32 columns each): Yc^T in the last 64 columns until [X2 | X4]
+// is complete (the scratch above comes after), Ec^T where P was, Qc^T where the stacked product was.
+constexpr uint32_t TM_Y = 448, TM_E = 0, TM_QC = 128;
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&r)[16]) {
   uint32_t u[16];
@@ -108,6 +107,10 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&r)[16]) {
 
 __device__ __forceinline__ void tmem_st1(uint32_t taddr, float x) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(__float_as_uint(x)) : "memory");
+}
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, const uint4& v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -152,10 +155,11 @@ __device__ __forceinline__ void mma_kmajor(uint32_t d, uint32_t a, uint32_t a_pa
     mma_f16_lo(d, a + (((ks >> 2) * a_panel + (ks & 3) * 32) >> 4), b + (((ks >> 2) * b_panel + (ks & 3) * 32) >> 4), idesc,
                accumulate || ks > 0);
 }
-// A K-major (rows = channel), B MN-major ([reduction row][n contiguous], one K=16 step = two 8-row atoms = 2048 B).
-__device__ __forceinline__ void mma_kmn4(uint32_t d, uint32_t a, uint32_t b, uint32_t idesc, bool accumulate) {
+// Four K=16 steps with A in tensor memory (8 columns per step) and B in shared memory, K-major (step 32 B) or
+// MN-major (step 2048 B).
+__device__ __forceinline__ void mma_ts4(uint32_t d, uint32_t a_tmem, uint32_t b, uint32_t b_step, uint32_t idesc, bool accumulate) {
 #pragma unroll
-  for (int ks = 0; ks < 4; ks++) mma_f16_lo(d, a + ((ks * 32) >> 4), b + ((ks * 2048) >> 4), idesc, accumulate || ks > 0);
+  for (int ks = 0; ks < 4; ks++) mma_f16_ts(d, a_tmem + ks * 8, b + ((ks * b_step) >> 4), idesc, accumulate || ks > 0);
 }
 
 // Sum over the warp of x[lane & 15] for each of the 16 per-thread values (16 shuffles); every lane returns the
@@ -447,9 +451,10 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       const int ch = wg * (HALF / 8) + t8;
       uint4 hi, lo;
       split8(y, hi, lo);
-      *reinterpret_cast<uint4*>(sm + Smem::YHI + swz(kch, ch)) = hi;
-      *reinterpret_cast<uint4*>(sm + Smem::YLO + swz(kch, ch)) = lo;
+      tmem_st4(tlane + TM_Y + ch * 4, hi);
+      tmem_st4(tlane + TM_Y + 32 + ch * 4, lo);
     }
+    tmem_st_wait();
 
     STAMP(2);  // Yc tiles built
     // ---- after P: dh takes the place of the dR tiles; P epilogue (rows 0..63 live in TMEM lanes 0..63) ---------
@@ -566,9 +571,10 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       }
       uint4 hi, lo;
       split8(e, hi, lo);
-      *reinterpret_cast<uint4*>(sm + Smem::EHI + swz(kch, wg * (HALF / 8) + t8)) = hi;
-      *reinterpret_cast<uint4*>(sm + Smem::ELO + swz(kch, wg * (HALF / 8) + t8)) = lo;
+      tmem_st4(tlane + TM_E + (wg * (HALF / 8) + t8) * 4, hi);
+      tmem_st4(tlane + TM_E + 32 + (wg * (HALF / 8) + t8) * 4, lo);
     }
+    tmem_st_wait();
     STAMP(25);
     // this thread's 32 values of its channel's h row, kept for the chunk-end gate term (the h tile is gone by
     // the time dh arrives)
@@ -623,29 +629,25 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       STAMP0(5);
       tc_fence_after_sync();
       if (leader) {
-        // [X1 | X3] = h [dO ; P]^T as one N=128 product (the sign of X3 is applied in the epilogue).  It goes first
-        // and gets a commit of its own: as soon as it is done the h buffer can take the Qc tiles and the P tile the
-        // per-channel scratch, while the matrix-intra products still run
+        // [X1 | X3] = h [dO ; P]^T as one N=128 product (the sign of X3 is applied in the epilogue)
         mma_kmajor<8>(tb + TM_X1, dl(Smem::HS, 16), 16384, dl(Smem::DOP, 16), 16384, ID_KK128, false);
-        mma_commit(&bars[BAR_C12]);
         STAMP0(6);
-        // [X2 | X4] = Yc^T [dAqk ; dAkk]^T, hi/lo split in three passes
-        mma_kmajor<4>(tb + TM_X2, dl(Smem::YHI, 16), 0, dl(Smem::HHI, 16), 0, ID_KK128, false);
-        mma_kmajor<4>(tb + TM_X2, dl(Smem::YLO, 16), 0, dl(Smem::HHI, 16), 0, ID_KK128, true);
-        mma_kmajor<4>(tb + TM_X2, dl(Smem::YHI, 16), 0, dl(Smem::HLO, 16), 0, ID_KK128, true);
+        // [X2 | X4] = Yc^T [dAqk ; dAkk]^T, hi/lo split in three passes, Yc^T from tensor memory
+        mma_ts4(tb + TM_X2, tb + TM_Y, dl(Smem::HHI, 16), 32, ID_KK128, false);
+        mma_ts4(tb + TM_X2, tb + TM_Y + 32, dl(Smem::HHI, 16), 32, ID_KK128, true);
+        mma_ts4(tb + TM_X2, tb + TM_Y, dl(Smem::HLO, 16), 32, ID_KK128, true);
         mma_commit(&bars[BAR_Q]);  // X1 and X2 complete: dq can be finished while the rest still runs
         STAMP0(7);
         // X6, Ec part: B stored [reduction row i][n = j contiguous] = MN-major
-        mma_kmn4(tb + TM_X6, dl(Smem::EHI, 16), dl(Smem::DHI, 8192), ID_KMN, false);
-        mma_kmn4(tb + TM_X6, dl(Smem::ELO, 16), dl(Smem::DHI, 8192), ID_KMN, true);
-        mma_kmn4(tb + TM_X6, dl(Smem::EHI, 16), dl(Smem::DLO, 8192), ID_KMN, true);
+        mma_ts4(tb + TM_X6, tb + TM_E, dl(Smem::DHI, 8192), 2048, ID_KMN, false);
+        mma_ts4(tb + TM_X6, tb + TM_E + 32, dl(Smem::DHI, 8192), 2048, ID_KMN, true);
+        mma_ts4(tb + TM_X6, tb + TM_E, dl(Smem::DLO, 8192), 2048, ID_KMN, true);
       }
       STAMP0(8);
       __syncwarp();
     }
-    used |= (1u << BAR_C12) | (1u << BAR_C3) | (1u << BAR_Q);
-    // Qc^T tiles into the h buffer as soon as X1 and X3 are done with it
-    wait(BAR_C12, 7);
+    used |= (1u << BAR_C3) | (1u << BAR_Q);
+    // Qc^T into the columns the stacked product has left
     STAMP(20);
 #pragma unroll
     for (int t8 = 0; t8 < HALF / 8; t8++) {
@@ -657,16 +659,17 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       }
       uint4 hi, lo;
       split8(x, hi, lo);
-      *reinterpret_cast<uint4*>(sm + Smem::QHI + swz(kch, wg * (HALF / 8) + t8)) = hi;
-      *reinterpret_cast<uint4*>(sm + Smem::QLO + swz(kch, wg * (HALF / 8) + t8)) = lo;
+      tmem_st4(tlane + TM_QC + (wg * (HALF / 8) + t8) * 4, hi);
+      tmem_st4(tlane + TM_QC + 32 + (wg * (HALF / 8) + t8) * 4, lo);
     }
+    tmem_st_wait();
     STAMP(21);
     wait(BAR_D, 8);
     STAMP(22);
     // chunk-end gate term, part 1: sum_v h[k,v] dh[k,v] over this thread's 32 value columns (h from registers,
     // dh from the tile that just landed)
+    float hd = 0.f;  // written to the scratch columns once Yc^T, which they overlap, has been consumed
     if (GATE != GATE_NONE && alive) {
-      float hd = 0.f;
 #pragma unroll
       for (int ch = 0; ch < 4; ch++) {
         uint4 d = *reinterpret_cast<const uint4*>(sm + Smem::DHT + (wg >> 1) * 16384 + swz(kch, (wg & 1) * 4 + ch));
@@ -678,21 +681,19 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           hd += x.x * y.x + x.y * y.y;
         }
       }
-      tmem_st1(tlane + TM_SCR + wg, hd);
-      tmem_st_wait();
     }
     STAMP(23);
-    fence_async_smem();
-    __syncthreads();  // Qc tiles visible to the tensor core; every generic read of the dh tile is done
+    tc_fence_before_sync();
+    __syncthreads();  // Qc^T complete in tensor memory; every generic read of the dh tile is done
     STAMP(7);  // Qc tiles written, dh tile landed
     if (warp == 0 && alive) {
       STAMP0(9);
       tc_fence_after_sync();
       if (leader) {
         mma_kmajor<8>(tb + TM_X5, dl(Smem::DHT, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
-        mma_kmn4(tb + TM_X6, dl(Smem::QHI, 16), dl(Smem::HHI, 8192), ID_KMN, true);
-        mma_kmn4(tb + TM_X6, dl(Smem::QLO, 16), dl(Smem::HHI, 8192), ID_KMN, true);
-        mma_kmn4(tb + TM_X6, dl(Smem::QHI, 16), dl(Smem::HLO, 8192), ID_KMN, true);
+        mma_ts4(tb + TM_X6, tb + TM_QC, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
+        mma_ts4(tb + TM_X6, tb + TM_QC + 32, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
+        mma_ts4(tb + TM_X6, tb + TM_QC, dl(Smem::HLO, 8192), 2048, ID_KMN, true);
         mma_commit(&bars[BAR_C3]);
       }
       STAMP0(10);
@@ -705,12 +706,13 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     // tiles and the carry (plus the chunk-end term) is added after the barrier.
     const float gl = GATE == GATE_VECTOR ? sGl[kch] : (GATE == GATE_SCALAR ? sGs[C - 1] : 0.f);
     const float en = GATE == GATE_NONE ? 1.f : ex2(gl - cen);  // exp2(g_last - g) = zeta * en
-    float* sPark = reinterpret_cast<float*>(sm + Smem::YHI);  // [64 tokens][128 channels] over YHI + YLO
+    float* sPark = reinterpret_cast<float*>(sm + Smem::PARK);  // [64 tokens][128 channels]
     const size_t go0 = base128 + (size_t)t0 * ldt + kch;
     // pass A (needs X1, X2 only): dq, and q*dq parked for the gate row
     wait(BAR_Q, 12);
     tc_fence_after_sync();
     STAMP(17);
+    if (GATE != GATE_NONE && alive) tmem_st1(tlane + TM_SCR + wg, hd);
     if (alive) {
       const float ecs = ec * scale;
       float x1[16], x2[16];

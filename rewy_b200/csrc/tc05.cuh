@@ -207,6 +207,17 @@ __device__ __forceinline__ void mma_f16_lo(uint32_t d_tmem, uint32_t alo, uint32
       "r"(alo), "r"(blo), "r"(idesc), "r"((uint32_t)accumulate), "r"(DESC_HI_SW128)
       : "memory");
 }
+// A operand in tensor memory: row m of A is TMEM lane m, element k sits in column a_tmem + k / 2 (two BF16 per 32-bit
+// column, even k in the low half), exactly as a thread that owns lane m writes it with tcgen05.st; B from shared memory.
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t blo, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(blo), "r"(idesc), "r"((uint32_t)accumulate), "r"(DESC_HI_SW128)
+      : "memory");
+}
 // Arrive on an mbarrier when every MMA issued so far by this thread has completed (implies
 // tcgen05.fence::before_thread_sync).
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
