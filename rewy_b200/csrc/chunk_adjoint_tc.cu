@@ -66,10 +66,10 @@ struct Smem {
   static constexpr uint32_t QT = DOP + 8192;           // q tile of the NEXT chunk: its two panels [64 t][64 k] land in the two P
                                                        // tiles (16384 apart) once the products that read P are complete, and
                                                        // are read into registers at chunk start, before P is written again
-  static constexpr uint32_t BETA = TILES_END;          // float[64]
-  static constexpr uint32_t DBETA = BETA + 256;        // float[64]
-  static constexpr uint32_t GS = DBETA + 256;          // float[64] scalar gate rows
-  static constexpr uint32_t DGS = GS + 256;            // float[64] per-token gate sums (scalar gate)
+  static constexpr uint32_t BETA = TILES_END;          // float[2][64] beta of this chunk and of the next one
+  static constexpr uint32_t DBETA = BETA + 512;        // float[64]
+  static constexpr uint32_t GS = DBETA + 256;          // float[2][64] scalar gate rows, this chunk and the next
+  static constexpr uint32_t DGS = GS + 512;            // float[64] per-token gate sums (scalar gate)
   static constexpr uint32_t MINMAX = DGS + 256;        // float[4][2][128] per-quarter min / max of the gate rows (chunk start)
   static constexpr uint32_t DBP = MINMAX;              // float[8][64] sum_v v*P per token, one row per 16 value columns
   static constexpr uint32_t DBW = DBP + 2048;          // float[16 warps][16 tokens] sum_k k*(gamma eb) of the warp's channels
@@ -222,9 +222,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
                         const __grid_constant__ CUtensorMap tmDV, const TcParams p) {
   extern __shared__ __align__(1024) unsigned char raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
-  float* sBeta = reinterpret_cast<float*>(sm + Smem::BETA);
+  float* sBeta2 = reinterpret_cast<float*>(sm + Smem::BETA);
   float* sDb = reinterpret_cast<float*>(sm + Smem::DBETA);
-  float* sGs = reinterpret_cast<float*>(sm + Smem::GS);
+  float* sGs2 = reinterpret_cast<float*>(sm + Smem::GS);
   float* sDgs = reinterpret_cast<float*>(sm + Smem::DGS);
   float* sMinMax = reinterpret_cast<float*>(sm + Smem::MINMAX);
   float* sDbP = reinterpret_cast<float*>(sm + Smem::DBP);
@@ -306,16 +306,21 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   };
 
   if (tid == 0 && (int)blockIdx.x < p.total_chunks) issue_loads(blockIdx.x, LOAD_G | LOAD_A);
-  // beta (and the scalar gate) of a chunk are fetched one chunk ahead into a register of threads 0..63
   auto row_base1 = [&](int chunk) -> size_t {
     const int bn = p.div_h.quot(chunk), h = chunk - bn * H, b = p.div_nt.quot(bn), n = bn - b * NT;
     return ((size_t)b * T + (size_t)n * C) * H + h;
   };
-  float beta_pref = 0.f, gs_pref = 0.f;
-  if (tid < C && (int)blockIdx.x < p.total_chunks) {
-    if (!VB) beta_pref = p.beta[row_base1(blockIdx.x) + (size_t)tid * H];
-    if (GATE == GATE_SCALAR) gs_pref = p.g[row_base1(blockIdx.x) + (size_t)tid * H];
-  }
+  // beta (and the scalar gate) of a chunk are fetched one chunk ahead, by threads 64..127 at a point of the chunk
+  // where they would wait for the tensor core anyway, into the other half of a double buffer
+  int buf = 0;
+  auto fetch_rows = [&](int chunk, int into) {
+    if (tid >= C && tid < 2 * C && chunk < p.total_chunks) {
+      const size_t at = row_base1(chunk) + (size_t)(tid - C) * H;
+      if (!VB) sBeta2[into * C + tid - C] = p.beta[at];
+      if (GATE == GATE_SCALAR) sGs2[into * C + tid - C] = p.g[at];
+    }
+  };
+  fetch_rows(blockIdx.x, 0);
 
 #ifdef REWY_PHASE_PROF
   int prof_it = 0;
@@ -335,22 +340,11 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     const size_t base1 = (size_t)row0 * H + h;
     const int hrow0 = ((b * NT + n) * H + h) * 128;        // first row of this chunk's state in [B*NT*H*128]
     const int next_chunk = chunk + gridDim.x;
-    uint32_t used = (1u << BAR_A) | (1u << BAR_B) | (1u << BAR_C) | (1u << BAR_G);
-    if (warp == 0) {
-      if (leader) issue_loads(chunk, LOAD_BC);
-      __syncwarp();
-    }
+    uint32_t used = (1u << BAR_A) | (1u << BAR_G);
     STAMP(28);
 
-    if (tid < C) {
-      sBeta[tid] = beta_pref;
-      STAMP(29);
-      if (GATE == GATE_SCALAR) sGs[tid] = gs_pref;
-      if (next_chunk < p.total_chunks) {
-        if (!VB) beta_pref = p.beta[row_base1(next_chunk) + (size_t)tid * H];
-        if (GATE == GATE_SCALAR) gs_pref = p.g[row_base1(next_chunk) + (size_t)tid * H];
-      }
-    }
+    const float* sBeta = sBeta2 + buf * C;
+    const float* sGs = sGs2 + buf * C;
     STAMP(16);
     // ---- this thread's 32 tokens of its key channel: k and q (packed BF16 pair) and the gate row ------------
     uint32_t kq[HALF];
@@ -398,15 +392,22 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     if (__syncthreads_or(wide ? 1 : 0)) {
       // wide gate span: leave the chunk to the exact pairwise kernel; drain the loads already in flight
       if (tid == 0) {
-        wait(BAR_A, 101); wait(BAR_B, 102); wait(BAR_C, 103);
+        wait(BAR_A, 101);
         int idx = atomicAdd(&p.wide_list[0], 1);
         p.wide_list[1 + idx] = (b * H + h) * NT + n;  // the pairwise kernel's chunk numbering: (batch, head) major
       }
       ph ^= used;
+      fetch_rows(next_chunk, buf ^ 1);
+      buf ^= 1;
       alive = __syncthreads_and(alive ? 1 : 0) != 0;
       if (tid == 0 && alive && next_chunk < p.total_chunks) issue_loads(next_chunk, LOAD_G | LOAD_A);
       continue;
     }
+    if (warp == 0) {
+      if (leader) issue_loads(chunk, LOAD_BC);
+      __syncwarp();
+    }
+    used |= (1u << BAR_B) | (1u << BAR_C);
     STAMP(1);  // operands in registers, centre known
     // From here on g[] holds the centred factor alpha = 2^(g - c) of each token; zeta = 1 / alpha.
     if (GATE != GATE_NONE) {
@@ -708,6 +709,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     const float en = GATE == GATE_NONE ? 1.f : ex2(gl - cen);  // exp2(g_last - g) = zeta * en
     float* sPark = reinterpret_cast<float*>(sm + Smem::PARK);  // [64 tokens][128 channels]
     const size_t go0 = base128 + (size_t)t0 * ldt + kch;
+    fetch_rows(next_chunk, buf ^ 1);
     // pass A (needs X1, X2 only): dq, and q*dq parked for the gate row
     wait(BAR_Q, 12);
     tc_fence_after_sync();
@@ -870,6 +872,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     }
     STAMP(10);  // epilogue done
     ph ^= used;
+    buf ^= 1;
     alive = __syncthreads_and(alive ? 1 : 0) != 0;
     if (GATE == GATE_VECTOR && leader && alive) {
       tma_store_2d(&tmDG, sPark, h * 128, row0);
