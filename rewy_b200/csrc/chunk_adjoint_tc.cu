@@ -1,15 +1,28 @@
-// Stage "chunk adjoint" on the Blackwell tensor cores (tcgen05 + TMEM accumulators, TMA tile loads).
+// Stage "chunk adjoint" on the Blackwell tensor cores (tcgen05 + TMEM accumulators, TMA tile loads and stores).
 //
 // Same mathematics as chunk_adjoint.cu (the reference functions it replaces are listed there); this file is
-// the production path.  One persistent CTA per SM walks over chunks; per chunk:
-//   P      = Akk^T (dR_hi + dR_lo)                 M=128 (64 valid rows) N=128 K=64   both operands MN-major
-//   [H;-D] = [dO;P] R^T                            M=128 N=64 K=128                  one stacked product
-//   X1 = h dO^T, X3 = -(h P^T), X5 = dh R^T        M=128 (key channel) N=64 (token) K=128
-//   X2 = Yc^T H^T, X4 = Yc^T D^T, X6 = Qc^T H + Ec^T D   K=64, BF16 hi/lo split operands (3 passes each)
-// The accumulators of the last six products are [key channel x token]: epilogue thread k owns channel k and
-// all 64 tokens, so gate factors are per-thread scalars per token and the reverse gate cumsum is a running sum
-// inside the thread.  Chunks whose cumulative gate spans 80 or more log2 units are not processed here: their
-// indices are appended to a list that the warp-MMA kernel (exact pairwise path) works off afterwards.
+// the production path.  One persistent CTA per SM walks over chunks (head fastest, so CTAs that run together
+// read the same token rows); per chunk:
+//   P        = Akk^T (dR_hi + dR_lo)               M=128 N=128 K=64  both operands MN-major; the A tile is used for
+//                                                  both 64-row halves, so lanes 64..127 repeat rows 0..63
+//   [H;-D]   = [dO;P] R^T                          M=128 N=64  K=128 one stacked product
+//   [X1|X3]  = h [dO;P]^T                          M=128 (key channel) N=128 (token | token) K=128
+//   [X2|X4]  = Yc^T [H;D]^T                        N=128 K=64, BF16 hi/lo split operands, three passes
+//   X5       = dh R^T                              N=64 K=128
+//   X6       = Ec^T D + Qc^T H                     N=64 K=64+64, three passes each
+// Yc^T, Ec^T and Qc^T are written by their owner threads straight into tensor memory (A operand from TMEM); every
+// other operand is a tile exactly as TMA lands it.  The accumulators of the last products are [key channel x
+// token]: epilogue thread (k, token quarter) sees per-channel gate factors as scalars and runs the reverse gate
+// cumsum as a running sum.  What keeps the kernel fed:
+//   * one elected thread issues every TMA copy, product and commit, from warp-uniform code with descriptor words
+//     precomputed (a product costs it two integer adds);
+//   * the next chunk's tiles are requested in three instalments (k,q,g / Akk,dR,v / dO,R,h) so that the SM's
+//     memory port is never saturated while the epilogue stores need it; k, q, g arrive as tiles and are read
+//     into registers once; beta rows are double-buffered and fetched under a tensor-core wait;
+//   * dv and dg leave as tiles by bulk stores; per-token sums go through small per-warp arrays, per-channel
+//     sums through spare TMEM columns (no shared-memory atomics).
+// Chunks whose cumulative gate spans 80 or more log2 units are not processed here: their indices are appended
+// to a list that the warp-MMA kernel (exact pairwise path) works off afterwards.
 #include <cstdio>
 #include "tc05.cuh"
 
@@ -41,21 +54,23 @@ struct TcParams {
 #endif
 };
 
-// Shared-memory plan (byte offsets from a 1024-byte aligned base).  "t0" tiles are dead once P is computed and
-// are then overwritten by the Qc tiles; dh is loaded into the h buffer after the products that read h are done.
+// Shared-memory plan (byte offsets from a 1024-byte aligned base).  Regions are reused as soon as the product that
+// read them is complete; the aliases are listed after the tiles.
 struct Smem {
   static constexpr uint32_t AKK = 0;                   // [64 j][64 i] BF16                      8 KB
-  static constexpr uint32_t DRHI = AKK + 8192;         // 2 panels [64 j][64 v]                  16 KB   (later Qc hi)
-  static constexpr uint32_t DRLO = DRHI + 16384;       //                                        16 KB   (later Qc lo)
+  static constexpr uint32_t DRHI = AKK + 8192;         // 2 panels [64 j][64 v]                  16 KB
+  static constexpr uint32_t DRLO = DRHI + 16384;       //                                        16 KB
   static constexpr uint32_t DOP = DRLO + 16384;        // per v-panel: dO [64][64] then P [64][64] 32 KB
   static constexpr uint32_t R = DOP + 32768;           // 2 panels [64 j][64 v]                  16 KB
-  static constexpr uint32_t HS = R + 16384;            // 2 panels [128 k][64 v]  h, later dh    32 KB
+  static constexpr uint32_t HS = R + 16384;            // 2 panels [128 k][64 v]  h              32 KB
   static constexpr uint32_t HHI = HS + 32768;          // dAqk hi [64 i][64 j]                   8 KB
   static constexpr uint32_t DHI = HHI + 8192;          // dAkk hi; [dAqk hi ; dAkk hi] is one 128-row operand
   static constexpr uint32_t HLO = DHI + 8192;          // dAqk lo
   static constexpr uint32_t DLO = HLO + 8192;          // dAkk lo
   static constexpr uint32_t PARK = DLO + 8192;         // float [64 t][128 k]: parked gate-gradient rows, then the dg tile   32 KB
   static constexpr uint32_t GT = PARK + 32768;         // g tile of the NEXT chunk (4 panels [64 t][32 k] FP32)                32 KB
+  static constexpr uint32_t DQT = HS;                  // dq and dk tiles (dense [64 t][128 k] BF16, 16 KB each) take the h buffer
+  static constexpr uint32_t DKT = HS + 16384;          // once [X1|X3] is complete; they leave by bulk stores before h is reloaded
   static constexpr uint32_t DHT = DRHI;                // dh tile (2 panels [128 k][64 v]) takes the dR tiles once P is done
   static constexpr uint32_t KT = HLO;                  // k tile of the NEXT chunk (2 panels [64 t][64 k]) lands in the two lo
                                                        // tiles once they are dead and is read into registers at chunk start
@@ -219,7 +234,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
                         const __grid_constant__ CUtensorMap tmDH, const __grid_constant__ CUtensorMap tmV,
                         const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmG,
                         const __grid_constant__ CUtensorMap tmDG, const __grid_constant__ CUtensorMap tmQ,
-                        const __grid_constant__ CUtensorMap tmDV, const TcParams p) {
+                        const __grid_constant__ CUtensorMap tmDV, const __grid_constant__ CUtensorMap tmDQ,
+                        const __grid_constant__ CUtensorMap tmDK, const TcParams p) {
   extern __shared__ __align__(1024) unsigned char raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   float* sBeta2 = reinterpret_cast<float*>(sm + Smem::BETA);
@@ -248,6 +264,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     prefetch_tmap(&tmK); prefetch_tmap(&tmG);
     if (GATE == GATE_VECTOR) prefetch_tmap(&tmDG);
     prefetch_tmap(&tmQ); prefetch_tmap(&tmDV);
+    if (!OUTF32) { prefetch_tmap(&tmDQ); prefetch_tmap(&tmDK); }
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, 512);
@@ -388,7 +405,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       wide = !(hi - lo < SPAN_LIMIT);
     }
     // the previous chunk's gate-gradient tile (in the Yc tiles) must have left shared memory before they are rebuilt
-    if (GATE == GATE_VECTOR && leader) tma_store_wait_read();
+    if (leader) tma_store_wait_read();
     if (__syncthreads_or(wide ? 1 : 0)) {
       // wide gate span: leave the chunk to the exact pairwise kernel; drain the loads already in flight
       if (tid == 0) {
@@ -625,7 +642,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     tc_fence_after_sync();
 
     STAMP(6);  // HD epilogue done (after barrier)
-    // ---- products that read h: X1 = h dO^T, X2 = Yc^T dAqk^T, X3 = -(h P^T), X4 = Yc^T dAkk^T ---------------
+    // ---- second product group: [X1|X3], [X2|X4] and the Ec part of X6 ----------------------------------------
     if (warp == 0 && alive) {
       STAMP0(5);
       tc_fence_after_sync();
@@ -730,7 +747,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         if (OUTF32)
           reinterpret_cast<float*>(p.dq)[go] = dq;
         else
-          reinterpret_cast<bf16*>(p.dq)[go] = f2bf(dq);
+          *reinterpret_cast<bf16*>(sm + Smem::DQT + (t0 + j) * 256 + kch * 2) = f2bf(dq);
         if (GATE != GATE_NONE) sPark[(t0 + j) * 128 + kch] = qf(j) * dq;
       }
     }
@@ -780,7 +797,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
             reinterpret_cast<float*>(p.dk)[go] = be + y;
             if (VB) reinterpret_cast<float*>(p.dbg)[go] = kk * e;
           } else {
-            reinterpret_cast<bf16*>(p.dk)[go] = f2bf(be + y);
+            *reinterpret_cast<bf16*>(sm + Smem::DKT + t * 256 + kch * 2) = f2bf(be + y);
             if (VB) reinterpret_cast<bf16*>(p.dbg)[go] = f2bf(kk * e);
           }
           if (!VB) dbp[j] = kk * e;
@@ -814,9 +831,15 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     }
     STAMP(11);  // main epilogue loop done
     STAMP0(13);
+    if (!OUTF32) fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    if (!OUTF32 && leader && alive) {
+      tma_store_2d(&tmDQ, sm + Smem::DQT, h * 128, row0);
+      tma_store_2d(&tmDK, sm + Smem::DKT, h * 128, row0);
+      tma_store_commit();
+    }
     STAMP(12);  // after its barrier
     if (alive) {
       // chunk-end term of this channel: lambda * sum_v h dh + sum_t k 2^(g_last - g) (R dh^T)
@@ -922,7 +945,7 @@ cudaError_t run1(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
   if (e != cudaSuccess) return e;
   const int grid = p.total_chunks < sm_count() ? p.total_chunks : sm_count();
-  kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9], tm[10], tm[11], tm[12], p);
+  kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9], tm[10], tm[11], tm[12], tm[13], tm[14], p);
   count_launch();
   return cudaGetLastError();
 }
@@ -939,7 +962,7 @@ cudaError_t run(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
 cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* ctrl, cudaStream_t st) {
   const int B = a.B, T = a.T, H = a.H, NT = T / C;
   const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
-  CUtensorMap tm[13];
+  CUtensorMap tm[15];
   bool ok = encode_tmap_2d(&tm[0], a.Akk, 2, (uint64_t)H * 64, rows, (uint64_t)H * 128, 64, 64) &&
             encode_tmap_panels(&tm[1], s.dR, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
             encode_tmap_panels(&tm[2], s.dR_lo, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
@@ -956,6 +979,11 @@ cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers
          encode_tmap_2d(&tm[10], a.dg, 4, (uint64_t)H * 128, rows, (uint64_t)H * 512, 128, 64, false);
   else
     tm[9] = tm[10] = tm[8];  // never dereferenced without a vector gate
+  if (ok && a.out_dtype != REWY_OUT_F32)
+    ok = encode_tmap_2d(&tm[13], a.dq, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 128, 64, false) &&
+         encode_tmap_2d(&tm[14], a.dk, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 128, 64, false);
+  else
+    tm[13] = tm[14] = tm[8];  // FP32 dq / dk are stored directly
   if (!ok) return cudaErrorInvalidValue;
   cudaError_t e = cudaMemsetAsync(ctrl + 1, 0, sizeof(int), st);  // wide-chunk count; the status word is kept
   if (e != cudaSuccess) return e;
