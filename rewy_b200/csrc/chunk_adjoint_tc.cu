@@ -96,7 +96,7 @@ struct Smem {
 };
 static_assert(Smem::TOTAL + 1024 <= 232448, "shared memory plan exceeds the 227 KB per-CTA limit");
 
-enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C3, BAR_G, BAR_Q, NUM_BARS };
+enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C3, BAR_G, BAR_Q, BAR_QR, NUM_BARS };
 
 // TMEM column plan (512 columns allocated).
 constexpr uint32_t TM_P = 0, TM_HD = 128, TM_X1 = 192, TM_X3 = 256, TM_X2 = 320, TM_X4 = 384, TM_X5 = 0, TM_X6 = 64;
@@ -257,7 +257,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   const float scale = p.scale;
 
   if (tid == 0) {
-    for (int i = 0; i < NUM_BARS; i++) mbar_init(&bars[i], 1);
+    for (int i = 0; i < NUM_BARS; i++) mbar_init(&bars[i], i == BAR_QR ? TPB / 32 : 1);  // BAR_QR: one arrival per warp
     fence_barrier_init();
     prefetch_tmap(&tmAkk); prefetch_tmap(&tmDRhi); prefetch_tmap(&tmDRlo); prefetch_tmap(&tmDO);
     prefetch_tmap(&tmR); prefetch_tmap(&tmH); prefetch_tmap(&tmDH); prefetch_tmap(&tmV);
@@ -277,6 +277,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   const uint32_t tlane = tb + ((uint32_t)((warp & 3) * 32) << 16);  // this warp's TMEM lanes
   // the one thread that issues every TMA copy, tensor-core product and commit (bulk store groups are per thread)
   const bool leader = warp == 0 && elect_one();
+  // The last product group is issued from another warp: the leader's warp is still busy with its own share of the
+  // operand tiles when the others have finished theirs, and whoever issues is late for the epilogue by that much.
+  const bool leader2 = warp == 1 && elect_one();
   uint32_t ph = 0;                                                  // phase bit per barrier
   bool alive = true;                                                // false once a bounded wait gave up
 
@@ -404,7 +407,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       cen = 0.5f * (lo + hi);
       wide = !(hi - lo < SPAN_LIMIT);
     }
-    // the previous chunk's gate-gradient tile (in the Yc tiles) must have left shared memory before they are rebuilt
+    // the previous chunk's output tiles must have left shared memory before their regions are written again
     if (leader) tma_store_wait_read();
     if (__syncthreads_or(wide ? 1 : 0)) {
       // wide gate span: leave the chunk to the exact pairwise kernel; drain the loads already in flight
@@ -664,7 +667,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       STAMP0(8);
       __syncwarp();
     }
-    used |= (1u << BAR_C3) | (1u << BAR_Q);
+    used |= (1u << BAR_C3) | (1u << BAR_Q) | (1u << BAR_QR);
     // Qc^T into the columns the stacked product has left
     STAMP(20);
 #pragma unroll
@@ -681,6 +684,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       tmem_st4(tlane + TM_QC + 32 + (wg * (HALF / 8) + t8) * 4, lo);
     }
     tmem_st_wait();
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&bars[BAR_QR]);  // this warp's part of Qc^T is complete in tensor memory
     STAMP(21);
     wait(BAR_D, 8);
     STAMP(22);
@@ -701,20 +707,21 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       }
     }
     STAMP(23);
-    tc_fence_before_sync();
-    __syncthreads();  // Qc^T complete in tensor memory; every generic read of the dh tile is done
-    STAMP(7);  // Qc tiles written, dh tile landed
-    if (warp == 0 && alive) {
-      STAMP0(9);
-      tc_fence_after_sync();
-      if (leader) {
-        mma_kmajor<8>(tb + TM_X5, dl(Smem::DHT, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
-        mma_ts4(tb + TM_X6, tb + TM_QC, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
-        mma_ts4(tb + TM_X6, tb + TM_QC + 32, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
-        mma_ts4(tb + TM_X6, tb + TM_QC, dl(Smem::HLO, 8192), 2048, ID_KMN, true);
-        mma_commit(&bars[BAR_C3]);
+    STAMP(7);
+    if (warp == 1) {
+      wait(BAR_QR, 13);  // Qc^T complete (all sixteen warps), and the leader has issued everything before it
+      STAMP(30);
+      if (alive) {
+        tc_fence_after_sync();
+        if (leader2) {
+          mma_kmajor<8>(tb + TM_X5, dl(Smem::DHT, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
+          mma_ts4(tb + TM_X6, tb + TM_QC, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
+          mma_ts4(tb + TM_X6, tb + TM_QC + 32, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
+          mma_ts4(tb + TM_X6, tb + TM_QC, dl(Smem::HLO, 8192), 2048, ID_KMN, true);
+          mma_commit(&bars[BAR_C3]);
+        }
       }
-      STAMP0(10);
+      STAMP(31);
       __syncwarp();
     }
 
