@@ -659,10 +659,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         mma_ts4(tb + TM_X2, tb + TM_Y, dl(Smem::HLO, 16), 32, ID_KK128, true);
         mma_commit(&bars[BAR_Q]);  // X1 and X2 complete: dq can be finished while the rest still runs
         STAMP0(7);
-        // X6, Ec part: B stored [reduction row i][n = j contiguous] = MN-major
-        mma_ts4(tb + TM_X6, tb + TM_E, dl(Smem::DHI, 8192), 2048, ID_KMN, false);
-        mma_ts4(tb + TM_X6, tb + TM_E + 32, dl(Smem::DHI, 8192), 2048, ID_KMN, true);
-        mma_ts4(tb + TM_X6, tb + TM_E, dl(Smem::DLO, 8192), 2048, ID_KMN, true);
       }
       STAMP0(8);
       __syncwarp();
@@ -714,6 +710,10 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       if (alive) {
         tc_fence_after_sync();
         if (leader2) {
+          // X6, Ec part: B stored [reduction row i][n = j contiguous] = MN-major
+          mma_ts4(tb + TM_X6, tb + TM_E, dl(Smem::DHI, 8192), 2048, ID_KMN, false);
+          mma_ts4(tb + TM_X6, tb + TM_E + 32, dl(Smem::DHI, 8192), 2048, ID_KMN, true);
+          mma_ts4(tb + TM_X6, tb + TM_E, dl(Smem::DLO, 8192), 2048, ID_KMN, true);
           mma_kmajor<8>(tb + TM_X5, dl(Smem::DHT, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
           mma_ts4(tb + TM_X6, tb + TM_QC, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
           mma_ts4(tb + TM_X6, tb + TM_QC + 32, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
