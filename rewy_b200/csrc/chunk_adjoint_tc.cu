@@ -99,13 +99,15 @@ static_assert(Smem::TOTAL + 1024 <= 232448, "shared memory plan exceeds the 227 
 enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C3, BAR_G, BAR_Q, BAR_QR, NUM_BARS };
 
 // TMEM column plan (512 columns allocated).
-constexpr uint32_t TM_P = 0, TM_HD = 128, TM_X1 = 192, TM_X3 = 256, TM_X2 = 320, TM_X4 = 384, TM_X5 = 0, TM_X6 = 64;
-// Per-channel scratch of the gate epilogue in the last 64 columns (lane = key channel): column TM_SCR + wg holds
-// sum_v h*dh of value quarter wg, +4 the chunk-end sums and +8 the gate-gradient totals of token quarter wg.
-constexpr uint32_t TM_SCR = 448;
+constexpr uint32_t TM_P = 0, TM_HD = 128, TM_X1 = 192, TM_X3 = 256, TM_X2 = 320, TM_X4 = 384, TM_X5 = 448, TM_X6 = 64;
 // Operand tiles of the matrix-intra products, written by their owner threads (lane = key channel; 16 tokens = 8
 // packed columns per thread; hi block then lo block, 32 columns each): Yc^T in the last 64 columns until [X2 | X4]
-// is complete (the scratch above comes after), Ec^T where P was, Qc^T where the stacked product was.
+// is complete (X5, issued after it by the same thread, accumulates there), Ec^T where P was, Qc^T where the
+// stacked product was.
+// Per-channel scratch of the gate epilogue (lane = key channel) takes the first columns of Ec^T once X6 is complete:
+// column TM_SCR + wg holds sum_v h*dh of value quarter wg, +4 the chunk-end sums and +8 the gate-gradient totals
+// of token quarter wg.
+constexpr uint32_t TM_SCR = 0;
 constexpr uint32_t TM_Y = 448, TM_E = 0, TM_QC = 128;
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&r)[16]) {
@@ -257,7 +259,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   const float scale = p.scale;
 
   if (tid == 0) {
-    for (int i = 0; i < NUM_BARS; i++) mbar_init(&bars[i], i == BAR_QR ? TPB / 32 : 1);  // BAR_QR: one arrival per warp
+    for (int i = 0; i < NUM_BARS; i++) mbar_init(&bars[i], i == BAR_QR ? TPB / 32 : (i == BAR_C3 ? 2 : 1));  // BAR_QR: one arrival per warp; BAR_C3: one per issuer
     fence_barrier_init();
     prefetch_tmap(&tmAkk); prefetch_tmap(&tmDRhi); prefetch_tmap(&tmDRlo); prefetch_tmap(&tmDO);
     prefetch_tmap(&tmR); prefetch_tmap(&tmH); prefetch_tmap(&tmDH); prefetch_tmap(&tmV);
@@ -344,7 +346,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 
 #ifdef REWY_PHASE_PROF
   int prof_it = 0;
-#define STAMP(i) do { if (p.prof != nullptr && blockIdx.x == 0 && tid == 32 && prof_it < 64) p.prof[prof_it * 32 + (i)] = clock64(); } while (0)
+#define STAMP(i) do { if (p.prof != nullptr && blockIdx.x == 0 && tid == 64 && prof_it < 64) p.prof[prof_it * 32 + (i)] = clock64(); } while (0)
 #define STAMP0(i) do { if (p.prof != nullptr && blockIdx.x == 0 && tid == 0 && prof_it < 64) p.prof[2048 + prof_it * 32 + (i)] = clock64(); } while (0)
 #else
 #define STAMP(i) do {} while (0)
@@ -663,6 +665,16 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       STAMP0(8);
       __syncwarp();
     }
+    if (warp == 1 && alive) {
+      tc_fence_after_sync();
+      if (leader2) {
+        // X6, Ec part, from the second issuer at the same time: B stored [reduction row i][n = j contiguous] = MN-major
+        mma_ts4(tb + TM_X6, tb + TM_E, dl(Smem::DHI, 8192), 2048, ID_KMN, false);
+        mma_ts4(tb + TM_X6, tb + TM_E + 32, dl(Smem::DHI, 8192), 2048, ID_KMN, true);
+        mma_ts4(tb + TM_X6, tb + TM_E, dl(Smem::DLO, 8192), 2048, ID_KMN, true);
+      }
+      __syncwarp();
+    }
     used |= (1u << BAR_C3) | (1u << BAR_Q) | (1u << BAR_QR);
     // Qc^T into the columns the stacked product has left
     STAMP(20);
@@ -685,10 +697,18 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     if (lane == 0) mbar_arrive(&bars[BAR_QR]);  // this warp's part of Qc^T is complete in tensor memory
     STAMP(21);
     wait(BAR_D, 8);
+    if (warp == 0 && alive) {
+      if (leader) {
+        // X5 = dh R^T into the columns Yc^T leaves: issued after [X2 | X4] by the same thread, so it runs after it
+        mma_kmajor<8>(tb + TM_X5, dl(Smem::DHT, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
+        mma_commit(&bars[BAR_C3]);
+      }
+      __syncwarp();
+    }
     STAMP(22);
     // chunk-end gate term, part 1: sum_v h[k,v] dh[k,v] over this thread's 32 value columns (h from registers,
     // dh from the tile that just landed)
-    float hd = 0.f;  // written to the scratch columns once Yc^T, which they overlap, has been consumed
+    float hd = 0.f;  // written to the scratch columns once every product is complete
     if (GATE != GATE_NONE && alive) {
 #pragma unroll
       for (int ch = 0; ch < 4; ch++) {
@@ -710,11 +730,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       if (alive) {
         tc_fence_after_sync();
         if (leader2) {
-          // X6, Ec part: B stored [reduction row i][n = j contiguous] = MN-major
-          mma_ts4(tb + TM_X6, tb + TM_E, dl(Smem::DHI, 8192), 2048, ID_KMN, false);
-          mma_ts4(tb + TM_X6, tb + TM_E + 32, dl(Smem::DHI, 8192), 2048, ID_KMN, true);
-          mma_ts4(tb + TM_X6, tb + TM_E, dl(Smem::DLO, 8192), 2048, ID_KMN, true);
-          mma_kmajor<8>(tb + TM_X5, dl(Smem::DHT, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
           mma_ts4(tb + TM_X6, tb + TM_QC, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
           mma_ts4(tb + TM_X6, tb + TM_QC + 32, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
           mma_ts4(tb + TM_X6, tb + TM_QC, dl(Smem::HLO, 8192), 2048, ID_KMN, true);
@@ -738,7 +753,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     wait(BAR_Q, 12);
     tc_fence_after_sync();
     STAMP(17);
-    if (GATE != GATE_NONE && alive) tmem_st1(tlane + TM_SCR + wg, hd);
     if (alive) {
       const float ecs = ec * scale;
       float x1[16], x2[16];
@@ -761,6 +775,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     STAMP(19);
     wait(BAR_C3, 10);
     tc_fence_after_sync();
+    if (GATE != GATE_NONE && alive) tmem_st1(tlane + TM_SCR + wg, hd);
     STAMP(8);  // all products done
     // every tile of this chunk has been consumed by the tensor core and (barrier above) by the threads: start the
     // next chunk's loads under the rest of the epilogue
