@@ -406,8 +406,19 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         lo = fminf(lo, sMinMax[(w2 * 2 + 0) * 128 + kch]);
         hi = fmaxf(hi, sMinMax[(w2 * 2 + 1) * 128 + kch]);
       }
-      cen = 0.5f * (lo + hi);
-      wide = !(hi - lo < SPAN_LIMIT);
+      if (GATE == GATE_VECTOR) {
+        cen = 0.5f * (lo + hi);
+        wide = !(hi - lo < SPAN_LIMIT);
+      } else {
+        // A scalar gate is the same for every channel, so its pairwise factor 2^(G_i - G_j), i >= j, is applied to the
+        // 64x64 matrices themselves and no operand is scaled by a centred factor.  With a non-increasing cumulative
+        // gate (every per-token gate <= 0) that factor is at most 1 whatever the span; only a chunk that both spans
+        // 80 log2 units and rises somewhere goes to the pairwise kernel.
+        bool rises = t0 > 0 && g[0] > sGs[t0 - 1];
+#pragma unroll
+        for (int j = 1; j < HALF; j++) rises = rises || g[j] > g[j - 1];
+        wide = rises && !(hi - lo < SPAN_LIMIT);
+      }
     }
     // the previous chunk's output tiles must have left shared memory before their regions are written again
     if (leader) tma_store_wait_read();
@@ -431,7 +442,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     }
     used |= (1u << BAR_B) | (1u << BAR_C);
     STAMP(1);  // operands in registers, centre known
-    // From here on g[] holds the centred factor alpha = 2^(g - c) of each token; zeta = 1 / alpha.
+    // From here on g[] holds the centred factor alpha = 2^(g - c) of each token; zeta = 1 / alpha (vector gate), or
+    // gamma = 2^g (scalar gate, c = 0).
     if (GATE != GATE_NONE) {
 #pragma unroll
       for (int j = 0; j < HALF; j++) g[j] = ex2(g[j] - cen);
@@ -469,7 +481,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 #pragma unroll
       for (int j = 0; j < 8; j++) {
         const int jj = t8 * 8 + j;
-        y[j] = kf(jj) * (GATE == GATE_NONE ? 1.f : rcp(g[jj]));
+        y[j] = kf(jj) * (GATE == GATE_VECTOR ? rcp(g[jj]) : 1.f);
       }
       const int ch = wg * (HALF / 8) + t8;
       uint4 hi, lo;
@@ -590,7 +602,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       for (int j = 0; j < 8; j++) {
         const int jj = t8 * 8 + j;
         const float bb = VB ? bf2f(p.bg[base128 + (size_t)(t0 + jj) * ldt + kch]) : sBeta[t0 + jj];
-        e[j] = bb * kf(jj) * (GATE == GATE_NONE ? 1.f : g[jj]);
+        e[j] = bb * kf(jj) * (GATE == GATE_VECTOR ? g[jj] : 1.f);
       }
       uint4 hi, lo;
       split8(e, hi, lo);
@@ -631,7 +643,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           for (int j = 0; j < 8; j++) {
             const int col = col0 + 8 * half + j;
             const bool keep = lower_incl ? (col <= i) : (col < i);
-            y[j] = keep ? mul * x[8 * half + j] : 0.f;
+            float f = mul;
+            if (GATE == GATE_SCALAR) f *= ex2(fminf(sGs[i] - sGs[col], 126.f));  // pairwise gate factor (kept entries: i >= col)
+            y[j] = keep ? f * x[8 * half + j] : 0.f;
           }
           uint4 hi, lo;
           split8(y, hi, lo);
@@ -684,7 +698,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 #pragma unroll
       for (int j = 0; j < 8; j++) {
         const int jj = t8 * 8 + j;
-        x[j] = qf(jj) * (GATE == GATE_NONE ? 1.f : g[jj]);
+        x[j] = qf(jj) * (GATE == GATE_VECTOR ? g[jj] : 1.f);
       }
       uint4 hi, lo;
       split8(x, hi, lo);
@@ -764,7 +778,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       for (int j = 0; j < HALF; j++) {
         const size_t go = go0 + (size_t)j * ldt;
         const float al = GATE == GATE_NONE ? 1.f : g[j];
-        const float dq = al * fmaf(ecs, x1[j], x2[j]);
+        const float dq = GATE == GATE_SCALAR ? fmaf(al * ecs, x1[j], x2[j]) : al * fmaf(ecs, x1[j], x2[j]);
         if (OUTF32)
           reinterpret_cast<float*>(p.dq)[go] = dq;
         else
@@ -808,12 +822,20 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           float al = 1.f, ze = 1.f;
           if (GATE != GATE_NONE) {
             al = g[jj];
-            ze = rcp(al);
+            if (GATE == GATE_VECTOR) ze = rcp(al);
           }
           const float kk = kf(jj);
           const float bb = VB ? bf2f(p.bg[go]) : sBeta[t];
-          const float e = al * fmaf(nec, x3[j], x4[j]);  // gamma * eb  (x3 = +h P^T)
-          const float y = ze * fmaf(en, x5[j], x6[j]);   // yb / gamma
+          float e, y, tail_f;  // gamma * eb (x3 = +h P^T), yb / gamma, 2^(g_last - g)
+          if (GATE == GATE_SCALAR) {
+            tail_f = ex2(gl - sGs[t]);
+            e = fmaf(al * nec, x3[j], x4[j]);
+            y = fmaf(tail_f, x5[j], x6[j]);
+          } else {
+            tail_f = ze * en;
+            e = al * fmaf(nec, x3[j], x4[j]);
+            y = ze * fmaf(en, x5[j], x6[j]);
+          }
           const float be = bb * e;
           if (OUTF32) {
             reinterpret_cast<float*>(p.dk)[go] = be + y;
@@ -824,7 +846,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           }
           if (!VB) dbp[j] = kk * e;
           if (GATE != GATE_NONE) {
-            colsum = fmaf(kk * ze * en, x5[j], colsum);
+            colsum = fmaf(kk * tail_f, x5[j], colsum);
             const float row = fmaf(kk, be - y, sPark[t * 128 + kch]);
             if (GATE == GATE_VECTOR) {
               run += row;

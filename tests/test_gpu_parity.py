@@ -236,6 +236,30 @@ def test_strong_gate_pairwise_path(op):
     _report(errs, 4e-3)
 
 
+@pytest.mark.parametrize("rising", (False, True))
+def test_scalar_gate_strong_decay_keeps_the_tensor_core_path(rising):
+    """Gated DeltaNet with a decay of far more than 80 log2 units per chunk: the pairwise factor is applied to the
+    64x64 matrices, so a monotone gate needs no pairwise kernel; one rising step in such a chunk sends it there."""
+    from rewy_b200 import backward as bw
+    lib = _capi.load()
+    xs = _inputs("gdn", T=128, H=2, seed=5)
+    xs["g"] = xs["g"] * 3
+    if rising:
+        xs["g"][:, 70, 0] = 4.0
+    saved = forward_saved("gdn", xs)
+    span = (saved["g_cumsum"][:, 64:128].amax(1) - saved["g_cumsum"][:, 64:128].amin(1)).min().item()
+    assert span > 80, span
+    ref = oracle_backward("gdn", xs, saved)
+    ws = torch.empty(_capi.workspace_bytes(_capi.GDN, _capi.RECOMPUTE, 1, 128, 2), dtype=torch.uint8, device=DEV)
+    r = bw.gdn_backward(q=xs["q"], k=xs["k"], v=xs["v"], g=saved["g_cumsum"], beta=xs["beta"], A=saved["Akk"],
+                        scale=128 ** -0.5, initial_state=xs["initial_state"], do=xs["do"], dht=xs["dht"],
+                        out_dtype=torch.float32, workspace=ws, check_status=True)
+    out = dict(dq=r[0], dk=r[1], dv=r[2], dbeta=r[3], dg=r[4], dh0=r[5])
+    count = lib.rewy_wide_chunk_count(_capi.ptr(ws), _capi.current_stream(torch.device(DEV)))
+    assert count == (1 if rising else 0), count
+    _report(_grad_errs("gdn", ref, out), 4e-3)
+
+
 @pytest.mark.parametrize("op", OPS)
 def test_tensor_core_and_warp_mma_kernels_agree(op):
     """The production (tcgen05) scan and chunk kernels against the warp-MMA kernels on the same inputs."""
