@@ -71,6 +71,9 @@ struct Smem {
   static constexpr uint32_t GT = PARK + 32768;         // g tile of the NEXT chunk (4 panels [64 t][32 k] FP32)                32 KB
   static constexpr uint32_t DQT = HS;                  // dq and dk tiles (dense [64 t][128 k] BF16, 16 KB each) take the h buffer
   static constexpr uint32_t DKT = HS + 16384;          // once [X1|X3] is complete; they leave by bulk stores before h is reloaded
+  static constexpr uint32_t BT = DOP;                  // GDN2: key-gate tile of the NEXT chunk, its two panels in the two dO tiles
+                                                       // (16384 apart) once [X1|X3] is complete; read into registers at chunk start
+  static constexpr uint32_t DBT = R;                   // GDN2: key-gate gradient tile (dense [64 t][128 k] BF16) during pass B
   static constexpr uint32_t DHT = DRHI;                // dh tile (2 panels [128 k][64 v]) takes the dR tiles once P is done
   static constexpr uint32_t KT = HLO;                  // k tile of the NEXT chunk (2 panels [64 t][64 k]) lands in the two lo
                                                        // tiles once they are dead and is read into registers at chunk start
@@ -237,7 +240,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
                         const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmG,
                         const __grid_constant__ CUtensorMap tmDG, const __grid_constant__ CUtensorMap tmQ,
                         const __grid_constant__ CUtensorMap tmDV, const __grid_constant__ CUtensorMap tmDQ,
-                        const __grid_constant__ CUtensorMap tmDK, const TcParams p) {
+                        const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmBG,
+                        const __grid_constant__ CUtensorMap tmDBG, const TcParams p) {
   extern __shared__ __align__(1024) unsigned char raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   float* sBeta2 = reinterpret_cast<float*>(sm + Smem::BETA);
@@ -267,6 +271,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     if (GATE == GATE_VECTOR) prefetch_tmap(&tmDG);
     prefetch_tmap(&tmQ); prefetch_tmap(&tmDV);
     if (!OUTF32) { prefetch_tmap(&tmDQ); prefetch_tmap(&tmDK); }
+    if (VB) { prefetch_tmap(&tmBG); if (!OUTF32) prefetch_tmap(&tmDBG); }
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, 512);
@@ -306,7 +311,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     const int bn = p.div_h.quot(chunk), h = chunk - bn * H, b = p.div_nt.quot(bn), n = bn - b * NT;
     const int row0 = b * T + n * C, hrow0 = ((b * NT + n) * H + h) * 128;
     if (parts & LOAD_G) {
-      mbar_expect_tx(&bars[BAR_G], 2 * 16384 + (GATE == GATE_VECTOR ? 32768 : 0));
+      mbar_expect_tx(&bars[BAR_G], 2 * 16384 + (GATE == GATE_VECTOR ? 32768 : 0) + (VB ? 16384 : 0));
+      if (VB)
+        for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::BT + pn * 16384, &tmBG, h * 128 + 64 * pn, row0, &bars[BAR_G]);
       tma_load_3d(sm + Smem::KT, &tmK, h * 128, row0, 0, &bars[BAR_G]);
       for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + Smem::QT + pn * 16384, &tmQ, h * 128 + 64 * pn, row0, &bars[BAR_G]);
       if (GATE == GATE_VECTOR) tma_load_3d(sm + Smem::GT, &tmG, h * 128, row0, 0, &bars[BAR_G]);
@@ -370,6 +377,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     STAMP(16);
     // ---- this thread's 32 tokens of its key channel: k and q (packed BF16 pair) and the gate row ------------
     uint32_t kq[HALF];
+    uint32_t bgp[VB ? HALF / 2 : 1];  // GDN2: key gate of the thread's tokens, two BF16 per register
     float g[HALF];
     // k, q and g from the tiles TMA brought in while the previous chunk's epilogue ran
     STAMP(13);
@@ -381,6 +389,10 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       const uint32_t off = swz(t, (kch & 63) >> 3) + (kch & 7) * 2;
       kq[j] = (uint32_t) * reinterpret_cast<const uint16_t*>(sm + Smem::KT + (kch >> 6) * 8192 + off) |
               ((uint32_t) * reinterpret_cast<const uint16_t*>(sm + Smem::QT + (kch >> 6) * 16384 + off) << 16);
+      if (VB) {
+        const uint32_t bv = *reinterpret_cast<const uint16_t*>(sm + Smem::BT + (kch >> 6) * 16384 + off);
+        bgp[j >> 1] = (j & 1) ? (bgp[j >> 1] | (bv << 16)) : bv;
+      }
       g[j] = GATE == GATE_VECTOR
                  ? *reinterpret_cast<const float*>(sm + Smem::GT + (kch >> 5) * 8192 + swz(t, (kch & 31) >> 2) + (kch & 3) * 4)
                  : 0.f;
@@ -450,6 +462,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     }
     auto kf = [&](int j) { return __uint_as_float(kq[j] << 16); };          // k of token t0 + j
     auto qf = [&](int j) { return __uint_as_float(kq[j] & 0xFFFF0000u); };  // q of token t0 + j
+    auto bgf = [&](int j) {                                                  // key gate of token t0 + j (GDN2)
+      return __uint_as_float((j & 1) ? (bgp[VB ? j >> 1 : 0] & 0xFFFF0000u) : (bgp[VB ? j >> 1 : 0] << 16));
+    };
 
     // ---- P = Akk^T (dR_hi + dR_lo) ----------------------------------------------------------------
     if (warp == 0) {
@@ -601,7 +616,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 #pragma unroll
       for (int j = 0; j < 8; j++) {
         const int jj = t8 * 8 + j;
-        const float bb = VB ? bf2f(p.bg[base128 + (size_t)(t0 + jj) * ldt + kch]) : sBeta[t0 + jj];
+        const float bb = VB ? bgf(jj) : sBeta[t0 + jj];
         e[j] = bb * kf(jj) * (GATE == GATE_VECTOR ? g[jj] : 1.f);
       }
       uint4 hi, lo;
@@ -825,7 +840,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
             if (GATE == GATE_VECTOR) ze = rcp(al);
           }
           const float kk = kf(jj);
-          const float bb = VB ? bf2f(p.bg[go]) : sBeta[t];
+          const float bb = VB ? bgf(jj) : sBeta[t];
           float e, y, tail_f;  // gamma * eb (x3 = +h P^T), yb / gamma, 2^(g_last - g)
           if (GATE == GATE_SCALAR) {
             tail_f = ex2(gl - sGs[t]);
@@ -842,7 +857,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
             if (VB) reinterpret_cast<float*>(p.dbg)[go] = kk * e;
           } else {
             *reinterpret_cast<bf16*>(sm + Smem::DKT + t * 256 + kch * 2) = f2bf(be + y);
-            if (VB) reinterpret_cast<bf16*>(p.dbg)[go] = f2bf(kk * e);
+            if (VB) *reinterpret_cast<bf16*>(sm + Smem::DBT + t * 256 + kch * 2) = f2bf(kk * e);
           }
           if (!VB) dbp[j] = kk * e;
           if (GATE != GATE_NONE) {
@@ -882,6 +897,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     if (!OUTF32 && leader && alive) {
       tma_store_2d(&tmDQ, sm + Smem::DQT, h * 128, row0);
       tma_store_2d(&tmDK, sm + Smem::DKT, h * 128, row0);
+      if (VB) tma_store_2d(&tmDBG, sm + Smem::DBT, h * 128, row0);
       tma_store_commit();
     }
     STAMP(12);  // after its barrier
@@ -989,7 +1005,7 @@ cudaError_t run1(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
   if (e != cudaSuccess) return e;
   const int grid = p.total_chunks < sm_count() ? p.total_chunks : sm_count();
-  kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9], tm[10], tm[11], tm[12], tm[13], tm[14], p);
+  kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9], tm[10], tm[11], tm[12], tm[13], tm[14], tm[15], tm[16], p);
   count_launch();
   return cudaGetLastError();
 }
@@ -1006,7 +1022,7 @@ cudaError_t run(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
 cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* ctrl, cudaStream_t st) {
   const int B = a.B, T = a.T, H = a.H, NT = T / C;
   const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
-  CUtensorMap tm[15];
+  CUtensorMap tm[17];
   bool ok = encode_tmap_2d(&tm[0], a.Akk, 2, (uint64_t)H * 64, rows, (uint64_t)H * 128, 64, 64) &&
             encode_tmap_panels(&tm[1], s.dR, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
             encode_tmap_panels(&tm[2], s.dR_lo, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
@@ -1028,6 +1044,12 @@ cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers
          encode_tmap_2d(&tm[14], a.dk, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 128, 64, false);
   else
     tm[13] = tm[14] = tm[8];  // FP32 dq / dk are stored directly
+  tm[15] = tm[16] = tm[8];
+  if (ok && a.family == REWY_GDN2) {
+    ok = encode_tmap_2d(&tm[15], a.b_gate, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64);
+    if (ok && a.out_dtype != REWY_OUT_F32)
+      ok = encode_tmap_2d(&tm[16], a.db_gate, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 128, 64, false);
+  }
   if (!ok) return cudaErrorInvalidValue;
   cudaError_t e = cudaMemsetAsync(ctrl + 1, 0, sizeof(int), st);  // wide-chunk count; the status word is kept
   if (e != cudaSuccess) return e;
