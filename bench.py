@@ -258,37 +258,64 @@ def main():
     }
 
     # end to end through the family function with HOST buffers (pinned), copies inside the timed region
-    e2e = None
-    if not args.no_e2e:
+    def measure_e2e(pol_saved):
         names_in = ["q", "k", "v", "do"]
         host_in = {n: xs[n] for n in names_in}
         host_in.update(beta=beta32, g=saved["g_cumsum"], Aqk=saved["Aqk"], Akk=saved["Akk"])
-        if head_saved:
+        if pol_saved:
             host_in.update({n: saved[n] for n in ("w", "qg", "kg", "v_new", "h")})
         if xs["initial_state"] is not None:
             host_in.update(h0=xs["initial_state"], dht=xs["dht"])
         pinned = {n: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for n, t in host_in.items()}
-        devbuf = {n: torch.empty_like(t) for n, t in host_in.items()}
         h2d = sum(t.numel() * t.element_size() for t in pinned.values())
-        fam, pol = _capi.KDA, (_capi.SAVED if head_saved else _capi.RECOMPUTE)
-        ws = torch.empty(_capi.workspace_bytes(fam, pol, B, T, H), dtype=torch.uint8, device=dev)
+        fam, pol = _capi.KDA, (_capi.SAVED if pol_saved else _capi.RECOMPUTE)
+        # The path is independent per batch element, so the host-facing call streams it: one batch element per call,
+        # two sets of device buffers, and three streams so that the copy in, the backward and the copy out overlap.
+        slots = [{n: torch.empty((1,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev) for n, t in host_in.items()}
+                 for _ in range(2)]
+        ws_slot = [torch.empty(_capi.workspace_bytes(fam, pol, 1, T, H), dtype=torch.uint8, device=dev) for _ in range(2)]
+        s_in, s_comp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
         out_host = None
 
         def e2e_step():
             nonlocal out_host
-            for n, t in pinned.items():
-                devbuf[n].copy_(t, non_blocking=True)
-            r = bw.kda_backward(
-                q=devbuf["q"], k=devbuf["k"], v=devbuf["v"], beta=devbuf["beta"], Aqk=devbuf["Aqk"], Akk=devbuf["Akk"],
-                scale=128 ** -0.5, initial_state=devbuf.get("h0"), do=devbuf["do"], dht=devbuf.get("dht"), g=devbuf["g"],
-                disable_recompute=head_saved, w=devbuf.get("w"), qg=devbuf.get("qg"), kg=devbuf.get("kg"),
-                v_new=devbuf.get("v_new"), h=devbuf.get("h"), out_dtype=torch.bfloat16, workspace=ws)
-            outs = [t for t in r if t is not None]
-            if out_host is None:
-                out_host = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in outs]
-            for hb, t in zip(out_host, outs):
-                hb.copy_(t, non_blocking=True)
-            return sum(t.numel() * t.element_size() for t in outs)
+            cur = torch.cuda.current_stream()
+            for st in (s_in, s_comp, s_out):
+                st.wait_stream(cur)
+            computed = [None, None]
+            keep, nbytes = [], 0
+            for ib in range(B):
+                slot = ib % 2
+                d = slots[slot]
+                with torch.cuda.stream(s_in):
+                    if computed[slot] is not None:
+                        s_in.wait_event(computed[slot])  # the slot's previous batch element has been consumed
+                    for n, t in pinned.items():
+                        d[n].copy_(t[ib:ib + 1], non_blocking=True)
+                    arrived = torch.cuda.Event()
+                    arrived.record(s_in)
+                with torch.cuda.stream(s_comp):
+                    s_comp.wait_event(arrived)
+                    r = bw.kda_backward(
+                        q=d["q"], k=d["k"], v=d["v"], beta=d["beta"], Aqk=d["Aqk"], Akk=d["Akk"], scale=128 ** -0.5,
+                        initial_state=d.get("h0"), do=d["do"], dht=d.get("dht"), g=d["g"], disable_recompute=pol_saved,
+                        w=d.get("w"), qg=d.get("qg"), kg=d.get("kg"), v_new=d.get("v_new"), h=d.get("h"),
+                        out_dtype=torch.bfloat16, workspace=ws_slot[slot])
+                    computed[slot] = torch.cuda.Event()
+                    computed[slot].record(s_comp)
+                outs = [t for t in r if t is not None]
+                if out_host is None:
+                    out_host = [torch.empty((B,) + tuple(t.shape[1:]), dtype=t.dtype, pin_memory=True) for t in outs]
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(computed[slot])
+                    for hb, t in zip(out_host, outs):
+                        hb[ib:ib + 1].copy_(t, non_blocking=True)
+                        t.record_stream(s_out)
+                keep.append(outs)
+                nbytes += sum(t.numel() * t.element_size() for t in outs)
+            for st in (s_in, s_comp, s_out):
+                cur.wait_stream(st)
+            return nbytes
 
         e_steps = max(1, min(K, 3))
         d2h = e2e_step()
@@ -304,11 +331,17 @@ def main():
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
-        e2e = {"value": tokens / (ms / e_steps * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+        return {"value": tokens / (ms / e_steps * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "steps": e_steps, "ms_per_step": ms / e_steps,
-               "api": "rewy_b200.backward.kda_backward (the function the autograd backward calls) with pinned host "
-                      "inputs copied H2D and gradients copied D2H every step"}
-        del pinned, devbuf, ws
+               "api": "rewy_b200.backward.kda_backward (the function the autograd backward calls), one batch element per "
+                      "call, pinned host inputs copied H2D and gradients copied D2H every step on three streams "
+                      "(copy in, backward, copy out overlap)"}
+
+    e2e = e2e_other = None
+    if not args.no_e2e:
+        e2e = measure_e2e(head_saved)
+        e2e_other = measure_e2e(not head_saved)
+        e2e_other["policy"] = "recompute" if head_saved else "full saving"
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -329,7 +362,7 @@ def main():
                          ("recompute" if head_saved else "saved"): {"tokens_per_s": tokens / (ms_other * 1e-3),
                                                                      "ms_per_step": ms_other, "stage_ms": stages_other}},
             "token_heads_per_s": value * H,
-            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "e2e_other_policy": e2e_other, "clocks": clocks,
             "gpu_launches": launches,
         }
         print(json.dumps(line), flush=True)
