@@ -105,7 +105,7 @@ enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C3, BAR_G, BAR_Q, BAR_
 constexpr uint32_t TM_P = 0, TM_HD = 128, TM_X1 = 192, TM_X3 = 256, TM_X2 = 320, TM_X4 = 384, TM_X5 = 448, TM_X6 = 64;
 // Operand tiles of the matrix-intra products, written by their owner threads (lane = key channel; 16 tokens = 8
 // packed columns per thread; hi block then lo block, 32 columns each): Yc^T in the last 64 columns until [X2 | X4]
-// is complete (X5, issued after it by the same thread, accumulates there), Ec^T where P was, Qc^T where the
+// is complete (X5, issued after it, accumulates there), Ec^T where P was, Qc^T where the
 // stacked product was.
 // Per-channel scratch of the gate epilogue (lane = key channel) takes the first columns of Ec^T once X6 is complete:
 // column TM_SCR + wg holds sum_v h*dh of value quarter wg, +4 the chunk-end sums and +8 the gate-gradient totals
@@ -263,7 +263,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   const float scale = p.scale;
 
   if (tid == 0) {
-    for (int i = 0; i < NUM_BARS; i++) mbar_init(&bars[i], i == BAR_QR ? TPB / 32 : (i == BAR_C3 ? 2 : 1));  // BAR_QR: one arrival per warp; BAR_C3: one per issuer
+    for (int i = 0; i < NUM_BARS; i++) mbar_init(&bars[i], i == BAR_QR ? TPB / 32 : 1);  // BAR_QR: one arrival per warp
     fence_barrier_init();
     prefetch_tmap(&tmAkk); prefetch_tmap(&tmDRhi); prefetch_tmap(&tmDRlo); prefetch_tmap(&tmDO);
     prefetch_tmap(&tmR); prefetch_tmap(&tmH); prefetch_tmap(&tmDH); prefetch_tmap(&tmV);
@@ -726,14 +726,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     if (lane == 0) mbar_arrive(&bars[BAR_QR]);  // this warp's part of Qc^T is complete in tensor memory
     STAMP(21);
     wait(BAR_D, 8);
-    if (warp == 0 && alive) {
-      if (leader) {
-        // X5 = dh R^T into the columns Yc^T leaves: issued after [X2 | X4] by the same thread, so it runs after it
-        mma_kmajor<8>(tb + TM_X5, dl(Smem::DHT, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
-        mma_commit(&bars[BAR_C3]);
-      }
-      __syncwarp();
-    }
     STAMP(22);
     // chunk-end gate term, part 1: sum_v h[k,v] dh[k,v] over this thread's 32 value columns (h from registers,
     // dh from the tile that just landed)
@@ -759,6 +751,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       if (alive) {
         tc_fence_after_sync();
         if (leader2) {
+          // X5 = dh R^T into the columns Yc^T leaves: the leader issued [X2 | X4] before its warp arrived on BAR_QR, so
+          // this runs after it
+          mma_kmajor<8>(tb + TM_X5, dl(Smem::DHT, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
           mma_ts4(tb + TM_X6, tb + TM_QC, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
           mma_ts4(tb + TM_X6, tb + TM_QC + 32, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
           mma_ts4(tb + TM_X6, tb + TM_QC, dl(Smem::HLO, 8192), 2048, ID_KMN, true);
