@@ -651,6 +651,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         const int col0 = 16 * wg;
         tmem_ld16(tlane + TM_HD + col0, x);
         tmem_ld_wait();
+        STAMP(29);
 #pragma unroll
         for (int half = 0; half < 2; half++) {
           float y[8];
