@@ -74,6 +74,8 @@ struct Smem {
   static constexpr uint32_t BT = DOP;                  // GDN2: key-gate tile of the NEXT chunk, its two panels in the two dO tiles
                                                        // (16384 apart) once [X1|X3] is complete; read into registers at chunk start
   static constexpr uint32_t DBT = R;                   // GDN2: key-gate gradient tile (dense [64 t][128 k] BF16) during pass B
+  static constexpr uint32_t DWT = PARK;                // GDN2: value-gate gradient tile (2 panels [64 i][64 v]) and, behind it,
+  static constexpr uint32_t WT = PARK + 16384;         // the value-gate tile of this chunk: PARK is free until pass A
   static constexpr uint32_t DHT = DRHI;                // dh tile (2 panels [128 k][64 v]) takes the dR tiles once P is done
   static constexpr uint32_t KT = HLO;                  // k tile of the NEXT chunk (2 panels [64 t][64 k]) lands in the two lo
                                                        // tiles once they are dead and is read into registers at chunk start
@@ -99,7 +101,7 @@ struct Smem {
 };
 static_assert(Smem::TOTAL + 1024 <= 232448, "shared memory plan exceeds the 227 KB per-CTA limit");
 
-enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C3, BAR_G, BAR_Q, BAR_QR, NUM_BARS };
+enum { BAR_A = 0, BAR_B, BAR_C, BAR_D, BAR_P, BAR_HD, BAR_C3, BAR_G, BAR_Q, BAR_QR, BAR_W, NUM_BARS };
 
 // TMEM column plan (512 columns allocated).
 constexpr uint32_t TM_P = 0, TM_HD = 128, TM_X1 = 192, TM_X3 = 256, TM_X2 = 320, TM_X4 = 384, TM_X5 = 448, TM_X6 = 64;
@@ -241,7 +243,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
                         const __grid_constant__ CUtensorMap tmDG, const __grid_constant__ CUtensorMap tmQ,
                         const __grid_constant__ CUtensorMap tmDV, const __grid_constant__ CUtensorMap tmDQ,
                         const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmBG,
-                        const __grid_constant__ CUtensorMap tmDBG, const TcParams p) {
+                        const __grid_constant__ CUtensorMap tmDBG, const __grid_constant__ CUtensorMap tmWG,
+                        const __grid_constant__ CUtensorMap tmDW, const TcParams p) {
   extern __shared__ __align__(1024) unsigned char raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   float* sBeta2 = reinterpret_cast<float*>(sm + Smem::BETA);
@@ -271,7 +274,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     if (GATE == GATE_VECTOR) prefetch_tmap(&tmDG);
     prefetch_tmap(&tmQ); prefetch_tmap(&tmDV);
     if (!OUTF32) { prefetch_tmap(&tmDQ); prefetch_tmap(&tmDK); }
-    if (VB) { prefetch_tmap(&tmBG); if (!OUTF32) prefetch_tmap(&tmDBG); }
+    if (VB) { prefetch_tmap(&tmBG); prefetch_tmap(&tmWG); if (!OUTF32) { prefetch_tmap(&tmDBG); prefetch_tmap(&tmDW); } }
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, 512);
@@ -331,6 +334,10 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       tma_load_3d(sm + Smem::R, &tmR, h * 128, row0, 0, &bars[BAR_B]);
       mbar_expect_tx(&bars[BAR_C], 32768);
       tma_load_3d(sm + Smem::HS, &tmH, 0, hrow0, 0, &bars[BAR_C]);
+      if (VB) {
+        mbar_expect_tx(&bars[BAR_W], 16384);
+        tma_load_3d(sm + Smem::WT, &tmWG, h * 128, row0, 0, &bars[BAR_W]);
+      }
     }
   };
 
@@ -452,7 +459,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       if (leader) issue_loads(chunk, LOAD_BC);
       __syncwarp();
     }
-    used |= (1u << BAR_B) | (1u << BAR_C);
+    used |= (1u << BAR_B) | (1u << BAR_C) | (VB ? 1u << BAR_W : 0u);
     STAMP(1);  // operands in registers, centre known
     // From here on g[] holds the centred factor alpha = 2^(g - c) of each token; zeta = 1 / alpha (vector gate), or
     // gamma = 2^g (scalar gate, c = 0).
@@ -510,6 +517,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     // ---- after P: dh takes the place of the dR tiles; P epilogue (rows 0..63 live in TMEM lanes 0..63) ---------
     wait(BAR_P, 2);
     tc_fence_after_sync();
+    if (VB) wait(BAR_W, 15);
     STAMP(3);  // P ready
     if (warp == 0 && alive) {
       if (leader) {
@@ -539,8 +547,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         float dwv[16];
         uint4 wraw[2];
         if (VB) {
-          wraw[0] = *reinterpret_cast<const uint4*>(p.wg + go + v0);
-          wraw[1] = *reinterpret_cast<const uint4*>(p.wg + go + v0 + 8);
+          wraw[0] = *reinterpret_cast<const uint4*>(sm + Smem::WT + vp * 8192 + swz(i, vc));
+          wraw[1] = *reinterpret_cast<const uint4*>(sm + Smem::WT + vp * 8192 + swz(i, vc + 1));
         }
         const uint32_t* wu = reinterpret_cast<const uint32_t*>(wraw);
 #pragma unroll
@@ -571,9 +579,9 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
             uint32_t dwp[8];
 #pragma unroll
             for (int j = 0; j < 8; j++) dwp[j] = pack_bf16(dwv[2 * j], dwv[2 * j + 1]);
-            bf16* o = reinterpret_cast<bf16*>(p.dwg) + go + v0;
-            *reinterpret_cast<uint4*>(o) = make_uint4(dwp[0], dwp[1], dwp[2], dwp[3]);
-            *reinterpret_cast<uint4*>(o + 8) = make_uint4(dwp[4], dwp[5], dwp[6], dwp[7]);
+            // tile in the parking area (free until pass A); it leaves with the dv tile
+            *reinterpret_cast<uint4*>(sm + Smem::DWT + vp * 8192 + swz(i, vc)) = make_uint4(dwp[0], dwp[1], dwp[2], dwp[3]);
+            *reinterpret_cast<uint4*>(sm + Smem::DWT + vp * 8192 + swz(i, vc + 1)) = make_uint4(dwp[4], dwp[5], dwp[6], dwp[7]);
           }
         }
         const uint32_t ptile = Smem::DOP + vp * 16384 + 8192;
@@ -597,6 +605,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         tc_fence_after_sync();
         if (leader) {
           tma_store_3d(&tmDV, sm + Smem::DVT, h * 128, row0, 0);
+          if (VB && !OUTF32) tma_store_3d(&tmDW, sm + Smem::DWT, h * 128, row0, 0);
           tma_store_commit();
           mma_kmajor<8>(tb + TM_HD, dl(Smem::DOP, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
           // the dv tile sits where the epilogue of this product writes: everyone waits for this commit first, and
@@ -1001,7 +1010,7 @@ cudaError_t run1(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
   if (e != cudaSuccess) return e;
   const int grid = p.total_chunks < sm_count() ? p.total_chunks : sm_count();
-  kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9], tm[10], tm[11], tm[12], tm[13], tm[14], tm[15], tm[16], p);
+  kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9], tm[10], tm[11], tm[12], tm[13], tm[14], tm[15], tm[16], tm[17], tm[18], p);
   count_launch();
   return cudaGetLastError();
 }
@@ -1018,7 +1027,7 @@ cudaError_t run(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
 cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* ctrl, cudaStream_t st) {
   const int B = a.B, T = a.T, H = a.H, NT = T / C;
   const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
-  CUtensorMap tm[17];
+  CUtensorMap tm[19];
   bool ok = encode_tmap_2d(&tm[0], a.Akk, 2, (uint64_t)H * 64, rows, (uint64_t)H * 128, 64, 64) &&
             encode_tmap_panels(&tm[1], s.dR, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
             encode_tmap_panels(&tm[2], s.dR_lo, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
@@ -1040,11 +1049,13 @@ cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers
          encode_tmap_2d(&tm[14], a.dk, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 128, 64, false);
   else
     tm[13] = tm[14] = tm[8];  // FP32 dq / dk are stored directly
-  tm[15] = tm[16] = tm[8];
+  tm[15] = tm[16] = tm[17] = tm[18] = tm[8];
   if (ok && a.family == REWY_GDN2) {
-    ok = encode_tmap_2d(&tm[15], a.b_gate, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64);
+    ok = encode_tmap_2d(&tm[15], a.b_gate, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
+         encode_tmap_panels(&tm[17], a.w_gate, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2);
     if (ok && a.out_dtype != REWY_OUT_F32)
-      ok = encode_tmap_2d(&tm[16], a.db_gate, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 128, 64, false);
+      ok = encode_tmap_2d(&tm[16], a.db_gate, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 128, 64, false) &&
+           encode_tmap_panels(&tm[18], a.dw_gate, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2);
   }
   if (!ok) return cudaErrorInvalidValue;
   cudaError_t e = cudaMemsetAsync(ctrl + 1, 0, sizeof(int), st);  // wide-chunk count; the status word is kept
