@@ -2,13 +2,18 @@
 """Benchmark of the chunked delta-rule backward (headline: KDA B=8, T=8192, H=32, K=V=128, BF16).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload cfg2_kda]
+                    [--scaling weak|strong] [--policy saved|recompute]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-A "step" is one complete backward (saved tensors + dO -> dq, dk, dv, dbeta, dg) of the workload on each rank.
-Ranks own disjoint batch slices of a global batch of N x B sequences (weak scaling, no collective on the data
-path); NCCL is used only for the barriers and the max-reduce of the elapsed time.  Rank 0 prints ONE JSON line.
-Inputs are synthetic (seeded, distributions of the benchmark configuration) and far larger than L2 (126 MB),
-so every step reads its inputs from HBM.
+A "step" is one complete backward (saved tensors + dO -> every gradient) of the workload on each rank, called through
+the whole-family function the autograd backward calls.  Ranks own disjoint (batch, head) shards and there is no
+collective on the data path; NCCL carries only the barriers and the max-reduce of the elapsed time.
+  --scaling weak    (default) every rank holds the workload's full batch: global batch = N x B
+  --scaling strong  the workload's batch is fixed and split by (batch, head): batches first, then heads
+Rank 0 prints ONE JSON line.  Inputs are synthetic (seeded, distributions of the benchmark configuration) and far
+larger than L2 (126 MB), so every step reads its inputs from HBM.  At N=1 the line also carries the other benchmark
+configurations ("families"), the reference's Triton backward on the same GPU ("triton_baseline", timed in a child
+process) and the CPU arm ("cpu_baseline").
 """
 import argparse
 import json
@@ -23,8 +28,16 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-METRIC = "delta-rule bwd tokens/s (KDA T=8192 H=32 K=V=128)"
 UNIT = "tokens/s"
+SCALE = 128 ** -0.5
+
+
+def metric_name(workload, policy_saved):
+    from rewy_b200.synthetic import CONFIGS
+    c = CONFIGS[workload]
+    fam = {"kda": "KDA", "gdn": "GDN", "gdn2": "GDN2", "delta": "DeltaNet"}[c["op"]]
+    pol = ("full-saving policy" if policy_saved else "recompute policy") if c["op"] in ("kda", "gdn2") else "recompute policy"
+    return f"delta-rule bwd tokens/s ({fam} T={c['T']} H={c['H']} K=V=128, {pol})"
 
 
 def parse():
@@ -33,13 +46,16 @@ def parse():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="rewy_b200", choices=("rewy_b200", "reference"))
-    ap.add_argument("--workload", default="cfg2_kda")
+    ap.add_argument("--workload", default="cfg2_kda", choices=("cfg1_gdn", "cfg2_kda", "cfg3_delta", "cfg4_gdn2"))
+    ap.add_argument("--scaling", default="weak", choices=("weak", "strong"))
     ap.add_argument("--policy", default="saved", choices=("saved", "recompute"),
                     help="activation policy of the headline value (both are timed and reported)")
-    ap.add_argument("--batch", type=int, default=None, help="override the per-rank batch size (smaller captures)")
+    ap.add_argument("--batch", type=int, default=None, help="override the workload's batch size (smaller captures)")
     ap.add_argument("--seq", type=int, default=None, help="override the sequence length")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-families", action="store_true")
+    ap.add_argument("--no-triton", action="store_true")
     return ap.parse_args()
 
 
@@ -98,6 +114,8 @@ def cpu_sample(steps, warmup, T=2048, H=32, heads_of_workload=32):
     import torch
     from oracle import naive_chunk_backward_fp32
     from rewy_b200.synthetic import make_inputs, operator_inputs
+    # every logical CPU of the host, whatever the launcher exported (torch.distributed.run sets OMP_NUM_THREADS=1)
+    torch.set_num_threads(os.cpu_count() or 1)
     xs = make_inputs("kda", 1, T, H, seed=42, gate_scale=0.1, state=False)
     ins = operator_inputs("kda", xs)
     times = []
@@ -110,19 +128,20 @@ def cpu_sample(steps, warmup, T=2048, H=32, heads_of_workload=32):
     return dict(value=token_heads_per_s / heads_of_workload, unit=UNIT, cores=torch.get_num_threads(), kind="port",
                 sample=f"KDA B=1 T={T} H={H} FP32 autograd backward through the naive chunked forward (oracle port of "
                        f"fla naive_chunk_kda); token-heads/s divided by {heads_of_workload} heads; "
-                       f"{steps} timed passes of {t * 1e3:.0f} ms; host has {os.cpu_count()} logical CPUs"), t
+                       f"{steps} timed passes of {t * 1e3:.0f} ms; {torch.get_num_threads()} threads on "
+                       f"{os.cpu_count()} logical CPUs"), t
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import torch
     steps, warmup = max(1, min(args.steps, 12)), max(1, min(args.warmup, 2))
     base, t = cpu_sample(steps, warmup)
     line = {
-        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
-        "steps": steps, "warmup": warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
+        "impl": "reference", "metric": metric_name("cfg2_kda", args.policy == "saved"), "value": base["value"],
+        "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": args.scaling,
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "KDA backward B=8 T=8192 H=32 K=V=128 chunk=64 (cfg2); CPU arm: each step is a bounded "
                                "sample (B=1, T=2048, all 32 heads) of it"},
@@ -134,6 +153,79 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------------------------
+# boundary bytes per token-head: every input of the family function read once, every gradient written once, public
+# dtypes (BF16 q,k,v,dO,dq,dk,dv and saved tensors; FP32 gates, beta and their gradients); states amortised over T
+def boundary_bytes(op, policy_saved, T, state):
+    base = {"kda": (3080, 4616), "gdn2": (4096, 5632), "gdn": (1936, 1936), "delta": (1928, 1928)}[op][1 if policy_saved else 0]
+    return base + (3 * 65536 / T if state else 0.0)
+
+
+class Problem:
+    """One rank's shard of a benchmark configuration, resident on the device, with its saved forward tensors."""
+
+    def __init__(self, name, dev, world=1, rank=0, scaling="weak", batch=None, seq=None):
+        import torch
+        from rewy_b200.forward import chunk_forward
+        from rewy_b200.sharding import shard
+        from rewy_b200.synthetic import CONFIGS, make_inputs
+        cfg = dict(CONFIGS[name])
+        self.name, self.op = name, cfg.pop("op")
+        B, self.T, self.H = batch or cfg["B"], seq or cfg["T"], cfg["H"]
+        self.state = cfg["state"]
+        if scaling == "weak":   # rank r owns batches [r*B, (r+1)*B) of a global batch of world*B sequences
+            self.global_B = world * B
+            batches, heads = shard(world * B, self.H, world, rank)
+        else:                   # the configuration's batch is fixed and split by (batch, head)
+            self.global_B = B
+            batches, heads = shard(B, self.H, world, rank)
+        self.B, self.nh = len(batches), len(heads)
+        self.shard = f"batches {batches[0]}..{batches[-1]}, heads {heads[0]}..{heads[-1]}"
+        xs = make_inputs(self.op, self.global_B, self.T, self.H, seed=42, device=dev, gate=cfg["gate"],
+                         gate_scale=cfg["gate_scale"], state=cfg["state"], batches=batches, heads=heads)
+        self.xs = xs
+        self.sv = chunk_forward(self.op, xs["q"], xs["k"], xs["v"], g=xs.get("g"), beta=xs.get("beta"), b=xs.get("b"),
+                                w=xs.get("w"), initial_state=xs.get("initial_state"), output_final_state=False)
+        self.sv.pop("o", None)
+        self.beta32 = xs["beta"].float() if "beta" in xs else None
+        self.dev = dev
+        self.policies = (True, False) if self.op in ("kda", "gdn2") else (False,)
+        torch.cuda.synchronize()
+
+    @property
+    def token_heads(self):
+        return self.B * self.T * self.nh
+
+    def family_policy(self, policy_saved):
+        from rewy_b200 import _capi
+        return _capi.FAMILY_ID[self.op], (_capi.SAVED if policy_saved else _capi.RECOMPUTE)
+
+    def workspace(self, policy_saved):
+        import torch
+        from rewy_b200 import _capi
+        fam, pol = self.family_policy(policy_saved)
+        return torch.empty(_capi.workspace_bytes(fam, pol, self.B, self.T, self.nh), dtype=torch.uint8, device=self.dev)
+
+    def call(self, policy_saved, workspace, xs=None, sv=None, beta32=None):
+        import torch
+        from rewy_b200 import backward as bw
+        xs, sv = xs or self.xs, sv or self.sv
+        beta32 = self.beta32 if beta32 is None else beta32
+        common = dict(q=xs["q"], k=xs["k"], v=xs["v"], scale=SCALE, initial_state=xs.get("initial_state"), do=xs["do"],
+                      dht=xs.get("dht"), out_dtype=torch.bfloat16, workspace=workspace)
+        keep = (lambda n: sv.get(n)) if policy_saved else (lambda n: None)
+        if self.op == "kda":
+            return bw.kda_backward(beta=beta32, Aqk=sv["Aqk"], Akk=sv["Akk"], g=sv["g_cumsum"],
+                                   disable_recompute=policy_saved, w=keep("w"), u=keep("u"), qg=keep("qg"), kg=keep("kg"),
+                                   v_new=keep("v_new"), h=keep("h"), **common)
+        if self.op == "gdn2":
+            return bw.gdn2_backward(b=xs["b"], w_gate=xs["w"], Aqk=sv["Aqk"], Akk=sv["Akk"], g=sv["g_cumsum"],
+                                    disable_recompute=policy_saved, w_wy=keep("w"), u_wy=keep("u"), qg=keep("qg"),
+                                    kg=keep("kg"), v_new=keep("v_new"), h=keep("h"), **common)
+        if self.op == "gdn":
+            return bw.gdn_backward(g=sv["g_cumsum"], beta=beta32, A=sv["Akk"], **common)
+        return bw.delta_backward(beta=beta32, A=sv["Akk"], **common)
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -141,10 +233,7 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from rewy_b200 import _capi, backward as bw
-    from rewy_b200.forward import chunk_forward
-    from rewy_b200.sharding import shard
-    from rewy_b200.synthetic import CONFIGS, make_inputs
+    from rewy_b200 import _capi
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -154,42 +243,25 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        os.environ["NCCL_DEBUG"] = os.environ.get("REWY_NCCL_DEBUG", "WARN")  # keep stdout to the one JSON line
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev)   # NCCL logs to stderr; stdout stays the one JSON line
     _capi.load()
-
-    cfg = dict(CONFIGS[args.workload])
-    op = cfg.pop("op")
-    if op != "kda":
-        raise SystemExit("bench.py measures the KDA headline workload")
-    B = args.batch or cfg["B"]
-    T = args.seq or cfg["T"]
-    H = cfg["H"]
-    # weak scaling: rank r owns batches [r*B, (r+1)*B) of a global batch of world*B sequences
-    xs = make_inputs(op, world * B, T, H, seed=42, device=dev, gate=cfg["gate"], gate_scale=cfg["gate_scale"],
-                     state=cfg["state"], batches=shard(world * B, H, world, rank)[0])
-    saved = chunk_forward(op, xs["q"], xs["k"], xs["v"], g=xs["g"], beta=xs["beta"], initial_state=xs["initial_state"],
-                          output_final_state=False)
-    beta32 = xs["beta"].float()
-    torch.cuda.synchronize()
-
-    def call(policy_saved, workspace):
-        return bw.kda_backward(
-            q=xs["q"], k=xs["k"], v=xs["v"], beta=beta32, Aqk=saved["Aqk"], Akk=saved["Akk"], scale=128 ** -0.5,
-            initial_state=xs["initial_state"], do=xs["do"], dht=xs["dht"], g=saved["g_cumsum"],
-            disable_recompute=policy_saved, w=saved["w"], u=saved["u"], qg=saved["qg"], kg=saved["kg"],
-            v_new=saved["v_new"], h=saved["h"], out_dtype=torch.bfloat16, workspace=workspace)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(policy_saved, steps, warmup, sample_clocks=False):
-        fam, pol = _capi.KDA, (_capi.SAVED if policy_saved else _capi.RECOMPUTE)
-        ws = torch.empty(_capi.workspace_bytes(fam, pol, B, T, H), dtype=torch.uint8, device=dev)
+    def max_over_ranks(ms):
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    def timed(prob, policy_saved, steps, warmup, sample_clocks=False):
+        ws = prob.workspace(policy_saved)
         for _ in range(warmup):
-            call(policy_saved, ws)
+            prob.call(policy_saved, ws)
         barrier()
         sampler = ClockSampler(local) if sample_clocks else None
         if sampler:
@@ -202,7 +274,7 @@ def main():
         t0 = time.perf_counter()
         ev0.record()
         for _ in range(steps):
-            call(policy_saved, ws)
+            prob.call(policy_saved, ws)
         ev1.record()
         barrier()
         t1 = time.perf_counter()
@@ -211,18 +283,21 @@ def main():
         _capi.stage_timing_enable(False)
         launches = _capi.launch_count() - launches0
         clocks = sampler.stop(t0, t1) if sampler else None
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+        ms = max_over_ranks(ms)
         del ws
         return ms / steps, {k: v / max(calls, 1) for k, v in stage_ms.items()}, launches, clocks
 
     K, W = args.steps, max(args.warmup, 3)
-    head_saved = args.policy == "saved"
-    ms_head, stages_head, launches, clocks = timed(head_saved, K, W, sample_clocks=True)
-    ms_other, stages_other, _, _ = timed(not head_saved, K, W)
-    tokens = world * B * T
+    prob = Problem(args.workload, dev, world, rank, args.scaling, args.batch, args.seq)
+    head_saved = args.policy == "saved" and True in prob.policies
+    ms_head, stages_head, launches, clocks = timed(prob, head_saved, K, W, sample_clocks=True)
+    policies = {("saved" if head_saved else "recompute"): {"ms_per_step": ms_head, "stage_ms": stages_head}}
+    if len(prob.policies) > 1:
+        ms_other, stages_other, _, _ = timed(prob, not head_saved, K, W)
+        policies["recompute" if head_saved else "saved"] = {"ms_per_step": ms_other, "stage_ms": stages_other}
+    tokens = prob.global_B * prob.T
+    for p in policies.values():
+        p["tokens_per_s"] = tokens / (p["ms_per_step"] * 1e-3)
     value = tokens / (ms_head * 1e-3)
 
     # roofline of the dominant kernel of the headline policy
@@ -231,49 +306,56 @@ def main():
         peak, peak_src = json.loads(peaks_file.read_text())["hbm_gbs"], "measured (MEASURED_PEAKS.json hbm_gbs)"
     else:
         peak, peak_src = 6650.0, "fallback 6.65 TB/s"
-    n_th = B * T * H                      # token-heads one launch processes on one rank
-    state_bytes = 2 * 65536 * B * H if cfg["state"] else 0
-    alg = {  # algorithmic bytes per token-head of each kernel (inputs read once + outputs written once)
-        "prepare": 4 * 256 + 512 + 4 + 128 + 4 * 256,
-        "fwd_scan": 3 * 256 + 8 + 512 + 256,
-        "bwd_scan": 4 * 256 + 128 + 8 + 512 + 2 * 256,
-        "chunk_adjoint": 5 * 256 + 512 + 4 + 128 + 2 * 512 + 2 * 256 + 3 * 256 + 512 + 4,
+    n_th = prob.token_heads               # token-heads one launch processes on this rank
+    vec = prob.op in ("kda", "gdn2")
+    gate_b = 512 if vec else (4 if prob.op == "gdn" else 0)
+    extra_gates = 2 * 256 if prob.op == "gdn2" else 4             # GDN2: b and w gates; others: beta
+    alg = {  # algorithmic bytes per token-head of each kernel (its operands read once + its results written once)
+        "prepare": 3 * 256 + gate_b + extra_gates + 128 + 4 * 256 + (0 if vec else 128),
+        "fwd_scan": 3 * 256 + (8 if vec else 0) + 512 + 256,
+        "bwd_scan": 4 * 256 + 128 + (8 if vec else 0) + 512 + 2 * 256,
+        "chunk_adjoint": 5 * 256 + gate_b + extra_gates + 128 + 2 * 512 + 2 * 256 + 3 * 256 + gate_b + extra_gates,
     }
-    # DRAM bytes per token-head from the ncu captures summarised under profiles/ (B=4,T=2048,H=32; per-token-head
-    # traffic of these kernels does not depend on B or T), scaled to this launch
-    ncu_traffic = {"chunk_adjoint": 4645, "bwd_scan": 2036}
+    # DRAM bytes per token-head measured with ncu on a smaller case of the same kernels (the per-token-head traffic of
+    # these kernels does not depend on B or T); the file is rewritten whenever the captures are refreshed
+    traffic_file = ROOT / "profiles" / "traffic.json"
+    ncu_traffic = json.loads(traffic_file.read_text()) if traffic_file.exists() else {}
     dom = max(stages_head, key=lambda s: stages_head[s])
     dom_ms = stages_head[dom]
     achieved = alg[dom] * n_th / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
-    path_bytes = (4616 if head_saved else 3080) * n_th + state_bytes
+    per_th = boundary_bytes(prob.op, head_saved, prob.T, prob.state)
+    path_bytes = per_th * n_th
+    t_entry = ncu_traffic.get(f"{prob.op}:{dom}")
     roofline = {
         "bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-        "traffic": ncu_traffic[dom] * n_th if dom in ncu_traffic else None,
-        "traffic_source": "profiles/ (ncu dram__bytes_read+write per token-head on a smaller case, scaled)",
+        "traffic": t_entry["dram_bytes_per_token_head"] * n_th if t_entry else None,
+        "traffic_source": (f"ncu dram__bytes_read+write per token-head on {t_entry['captured_on']}, scaled by "
+                           f"token-heads" if t_entry else None),
         "peak_source": peak_src, "ms_per_launch": dom_ms,
         "algorithmic_bytes_per_token_head": alg[dom],
-        "whole_path": {"algorithmic_bytes_per_token_head": path_bytes / n_th,
+        "whole_path": {"algorithmic_bytes_per_token_head": per_th,
                        "achieved": path_bytes / (ms_head * 1e-3) / 1e9, "frac": path_bytes / (ms_head * 1e-3) / 1e9 / peak},
         "stage_ms": stages_head,
     }
 
     # end to end through the family function with HOST buffers (pinned), copies inside the timed region
     def measure_e2e(pol_saved):
-        names_in = ["q", "k", "v", "do"]
-        host_in = {n: xs[n] for n in names_in}
-        host_in.update(beta=beta32, g=saved["g_cumsum"], Aqk=saved["Aqk"], Akk=saved["Akk"])
+        xs, sv = prob.xs, prob.sv
+        host_in = {n: xs[n] for n in ("q", "k", "v", "do")}
+        host_in.update(beta=prob.beta32, g_cumsum=sv["g_cumsum"], Aqk=sv["Aqk"], Akk=sv["Akk"])
         if pol_saved:
-            host_in.update({n: saved[n] for n in ("w", "qg", "kg", "v_new", "h")})
+            host_in.update({n: sv[n] for n in ("w", "qg", "kg", "v_new", "h")})
         if xs["initial_state"] is not None:
-            host_in.update(h0=xs["initial_state"], dht=xs["dht"])
+            host_in.update(initial_state=xs["initial_state"], dht=xs["dht"])
         pinned = {n: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for n, t in host_in.items()}
         h2d = sum(t.numel() * t.element_size() for t in pinned.values())
-        fam, pol = _capi.KDA, (_capi.SAVED if pol_saved else _capi.RECOMPUTE)
+        fam, pol = prob.family_policy(pol_saved)
         # The path is independent per batch element, so the host-facing call streams it: one batch element per call,
         # two sets of device buffers, and three streams so that the copy in, the backward and the copy out overlap.
         slots = [{n: torch.empty((1,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev) for n, t in host_in.items()}
                  for _ in range(2)]
-        ws_slot = [torch.empty(_capi.workspace_bytes(fam, pol, 1, T, H), dtype=torch.uint8, device=dev) for _ in range(2)]
+        ws_slot = [torch.empty(_capi.workspace_bytes(fam, pol, 1, prob.T, prob.nh), dtype=torch.uint8, device=dev)
+                   for _ in range(2)]
         s_in, s_comp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
         out_host = None
 
@@ -284,7 +366,7 @@ def main():
                 st.wait_stream(cur)
             computed = [None, None]
             keep, nbytes = [], 0
-            for ib in range(B):
+            for ib in range(prob.B):
                 slot = ib % 2
                 d = slots[slot]
                 with torch.cuda.stream(s_in):
@@ -296,16 +378,14 @@ def main():
                     arrived.record(s_in)
                 with torch.cuda.stream(s_comp):
                     s_comp.wait_event(arrived)
-                    r = bw.kda_backward(
-                        q=d["q"], k=d["k"], v=d["v"], beta=d["beta"], Aqk=d["Aqk"], Akk=d["Akk"], scale=128 ** -0.5,
-                        initial_state=d.get("h0"), do=d["do"], dht=d.get("dht"), g=d["g"], disable_recompute=pol_saved,
-                        w=d.get("w"), qg=d.get("qg"), kg=d.get("kg"), v_new=d.get("v_new"), h=d.get("h"),
-                        out_dtype=torch.bfloat16, workspace=ws_slot[slot])
+                    dx = dict(q=d["q"], k=d["k"], v=d["v"], do=d["do"], initial_state=d.get("initial_state"),
+                              dht=d.get("dht"))
+                    r = prob.call(pol_saved, ws_slot[slot], xs=dx, sv=d, beta32=d["beta"])
                     computed[slot] = torch.cuda.Event()
                     computed[slot].record(s_comp)
                 outs = [t for t in r if t is not None]
                 if out_host is None:
-                    out_host = [torch.empty((B,) + tuple(t.shape[1:]), dtype=t.dtype, pin_memory=True) for t in outs]
+                    out_host = [torch.empty((prob.B,) + tuple(t.shape[1:]), dtype=t.dtype, pin_memory=True) for t in outs]
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(computed[slot])
                     for hb, t in zip(out_host, outs):
@@ -326,22 +406,68 @@ def main():
             e2e_step()
         ev1.record()
         barrier()
-        ms = ev0.elapsed_time(ev1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+        ms = max_over_ranks(ev0.elapsed_time(ev1))
         return {"value": tokens / (ms / e_steps * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "steps": e_steps, "ms_per_step": ms / e_steps,
-               "api": "rewy_b200.backward.kda_backward (the function the autograd backward calls), one batch element per "
-                      "call, pinned host inputs copied H2D and gradients copied D2H every step on three streams "
-                      "(copy in, backward, copy out overlap)"}
+                "d2h_bytes_per_step": d2h, "steps": e_steps, "ms_per_step": ms / e_steps,
+                "api": "rewy_b200.backward.kda_backward (the function the autograd backward calls), one batch element per "
+                       "call, pinned host inputs copied H2D and gradients copied D2H every step on three streams "
+                       "(copy in, backward, copy out overlap)"}
 
     e2e = e2e_other = None
-    if not args.no_e2e:
+    if not args.no_e2e and prob.op == "kda":
         e2e = measure_e2e(head_saved)
         e2e_other = measure_e2e(not head_saved)
         e2e_other["policy"] = "recompute" if head_saved else "full saving"
+
+    workload_desc = (f"{prob.op.upper()} backward B={prob.global_B} global ({prob.B} x {prob.nh} heads on this rank), "
+                     f"T={prob.T}, H={prob.H}, K=V=128, chunk=64 ({args.workload})")
+    global_batch, n_heads = prob.global_B, prob.H
+    del prob
+    torch.cuda.empty_cache()
+
+    # the other benchmark configurations, same public functions, device-resident inputs (N=1 only)
+    families = None
+    if world == 1 and not args.no_families and args.workload == "cfg2_kda" and args.batch is None and args.seq is None:
+        families = {}
+        for name in ("cfg1_gdn", "cfg3_delta", "cfg4_gdn2"):
+            try:
+                fp = Problem(name, dev)
+                entry = {"workload": f"{fp.op} B={fp.B} T={fp.T} H={fp.H}", "token_heads": fp.token_heads}
+                for pol_saved in fp.policies:
+                    ms, st, _, _ = timed(fp, pol_saved, min(K, 10), 3)
+                    bb = boundary_bytes(fp.op, pol_saved, fp.T, fp.state)
+                    entry["saved" if pol_saved else "recompute"] = {
+                        "ms_per_step": ms, "tokens_per_s": fp.B * fp.T / (ms * 1e-3),
+                        "token_heads_per_s": fp.token_heads / (ms * 1e-3), "stage_ms": st,
+                        "boundary_bytes_per_token_head": bb,
+                        "whole_path_frac_of_hbm_peak": bb * fp.token_heads / (ms * 1e-3) / 1e9 / peak}
+                families[name] = entry
+                del fp
+            except Exception as exc:  # e.g. out of memory on a smaller device: report, keep the headline
+                families[name] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+            torch.cuda.empty_cache()
+
+    # the reference's Triton backward on this GPU, in a child process (its own CUDA context; a failure there cannot
+    # take the headline down).  N=1 only.
+    triton_baseline = None
+    if rank == 0 and world == 1 and not args.no_triton and args.workload == "cfg2_kda":
+        cmd = [sys.executable, str(ROOT / "baseline" / "triton_reference.py"), "--steps", str(min(K, 10)), "--warmup", "3",
+               "--policy", "saved" if head_saved else "recompute"]
+        if args.batch:
+            cmd += ["--batch", str(args.batch)]
+        if args.seq:
+            cmd += ["--seq", str(args.seq)]
+        try:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=420,
+                               env=dict(os.environ, CUDA_VISIBLE_DEVICES=os.environ.get("CUDA_VISIBLE_DEVICES", str(local))))
+            lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+            triton_baseline = json.loads(lines[-1]) if lines else {
+                "unavailable": f"exit code {r.returncode}: {r.stderr.strip()[-300:]}"}
+        except subprocess.TimeoutExpired:
+            triton_baseline = {"unavailable": "the child process did not finish within 420 s"}
+        ref_arm = (triton_baseline or {}).get("reference_optimized") or {}
+        if "ms" in ref_arm:
+            triton_baseline["speedup_of_this_library"] = ref_arm["ms"] / ms_head
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -349,21 +475,18 @@ def main():
 
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms_head, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "metric": metric_name(args.workload, head_saved), "value": value, "unit": UNIT, "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": ms_head, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"KDA backward B={B} per GPU, T={T}, H={H}, K=V=128, chunk=64 ({args.workload})",
+            "config": {"workload": workload_desc,
                        "policy": "full saving (disable_recompute=True)" if head_saved else "recompute",
-                       "global_batch": world * B, "parallelism": f"(batch,head) shards x{world}, no collective",
-                       "l2": "inputs (>= 9 GB per step) are far larger than the 126 MB L2; no flush needed",
-                       "outputs": "dq,dk,dv BF16; dg,dbeta FP32"},
-            "policies": {("saved" if head_saved else "recompute"): {"tokens_per_s": value, "ms_per_step": ms_head,
-                                                                     "stage_ms": stages_head},
-                         ("recompute" if head_saved else "saved"): {"tokens_per_s": tokens / (ms_other * 1e-3),
-                                                                     "ms_per_step": ms_other, "stage_ms": stages_other}},
-            "token_heads_per_s": value * H,
+                       "global_batch": global_batch,
+                       "parallelism": f"(batch,head) shards x{world}, no collective",
+                       "l2": "inputs are far larger than the 126 MB L2; no flush needed",
+                       "outputs": "dq,dk,dv (and GDN2's db,dw) BF16; dg,dbeta FP32"},
+            "policies": policies, "token_heads_per_s": value * n_heads,
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "e2e_other_policy": e2e_other, "clocks": clocks,
-            "gpu_launches": launches,
+            "gpu_launches": launches, "families": families, "triton_baseline": triton_baseline,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

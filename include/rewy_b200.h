@@ -49,7 +49,8 @@ typedef struct RewyBwdArgs {
   int32_t policy;      /* REWY_RECOMPUTE: w,qg,kg,v_new,h are rebuilt; REWY_SAVED: they are passed in */
   int32_t B, T, H;
   int32_t out_dtype;   /* dtype of dq, dk (and db_gate, dw_gate): REWY_OUT_BF16 or REWY_OUT_F32 */
-  int32_t intra_passes;/* 0 = default (3); 1, 2 or 3 BF16 split passes for the matrix-intra products */
+  int32_t intra_passes;/* 0 = default.  Option of chunk variant 1 (warp-MMA kernel) only: 1 or 3 BF16 split passes of
+                          the matrix-intra products; the tensor-core kernel always runs 3 and refuses other values */
   float scale;
   /* inputs */
   const void* q;       /* bf16 [B,T,H,128] */
@@ -184,6 +185,13 @@ int rewy_set_scan_variant(int variant);
  * err: device int, non-zero if a bounded wait inside the kernel gave up. */
 int rewy_selftest_tensor_core(const void* A, const void* B, const void* Akk, const void* dR, const float* Y,
                               const float* H, float* out, int* err, rewy_stream_t stream);
+
+/* Self-test of the failure path (no counterpart in the reference): one CTA waits, for at most limit_us
+ * microseconds (1..1000000), on an mbarrier phase that nothing completes - no copy or product is in flight - then
+ * records `site` (non-zero) in *err exactly as the stages do, writes 2 to *done (1 if the wait had succeeded) and
+ * returns normally.  err, done: device ints, zero on entry.  rewy_device_status(err, stream) then reports
+ * REWY_ERR_DEVICE. */
+int rewy_selftest_bounded_wait(int* err, int* done, uint32_t limit_us, int site, rewy_stream_t stream);
 
 /* Diagnostics. */
 const char* rewy_last_error(void);       /* thread-local text of the last non-zero status */

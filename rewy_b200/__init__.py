@@ -15,16 +15,19 @@ __version__ = "0.1.0"
 
 
 def enable(backend="optimized", *, strict=True, ops=None, integrations=()):
-    """Select the CUDA backward for the given operators.  ``integrations`` other than () are rejected:
-    registering into FLA's backend registry needs the FLA revision the reference pins."""
+    """Select the CUDA backward for the given operators.  ``integrations=("fla",)`` also registers the four
+    operators in flash-linear-attention's backend registry when the installed FLA has one (see
+    ``rewy_b200.integrations``); an FLA without that registry, or an unknown name, raises."""
     from .runtime import configure
     from . import _capi
     for name in integrations:
-        if name == "fla":
-            continue
-        raise ValueError(f"Unknown integration: {name}")
+        if name != "fla":
+            raise ValueError(f"Unknown integration: {name}")
     if backend == "optimized":
         _capi.load()  # fail here, loudly, if the CUDA library has not been built
+    if "fla" in integrations:
+        from .integrations import install
+        install()
     configure(backend, strict=strict, ops=ops)
 
 

@@ -9,8 +9,7 @@ from ctypes import c_char_p, c_float, c_int, c_int32, c_size_t, c_void_p
 from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
-import os as _os
-LIB_PATH = PKG / _os.environ.get("REWY_LIB_NAME", "librewy_b200.so")
+LIB_PATH = PKG / "librewy_b200.so"
 
 DELTA, GDN, KDA, GDN2 = 0, 1, 2, 3
 FAMILY_ID = {"delta": DELTA, "gdn": GDN, "kda": KDA, "gdn2": GDN2}
@@ -20,7 +19,7 @@ OUT_BF16, OUT_F32 = 0, 1
 EXPORTS = (
     "rewy_kda_bwd", "rewy_gdn2_bwd", "rewy_gdn_bwd", "rewy_delta_bwd", "rewy_bwd_workspace_bytes",
     "rewy_stage_prepare", "rewy_stage_fwd_scan", "rewy_stage_bwd_scan", "rewy_stage_chunk_adjoint",
-    "rewy_stage_timing_enable", "rewy_stage_timing_read", "rewy_selftest_tensor_core",
+    "rewy_stage_timing_enable", "rewy_stage_timing_read", "rewy_selftest_tensor_core", "rewy_selftest_bounded_wait",
     "rewy_device_status", "rewy_wide_chunk_count", "rewy_set_chunk_variant", "rewy_set_scan_variant",
     "rewy_stage_chunk_adjoint_static", "rewy_static_device_status",
     "rewy_last_error", "rewy_version", "rewy_kernel_launch_count",
@@ -79,6 +78,8 @@ def load():
     lib.rewy_stage_timing_read.restype = c_int
     lib.rewy_selftest_tensor_core.argtypes = [c_void_p] * 9
     lib.rewy_selftest_tensor_core.restype = c_int
+    lib.rewy_selftest_bounded_wait.argtypes = [c_void_p, c_void_p, ctypes.c_uint32, c_int, c_void_p]
+    lib.rewy_selftest_bounded_wait.restype = c_int
     lib.rewy_device_status.argtypes = [c_void_p, c_void_p]
     lib.rewy_device_status.restype = c_int
     lib.rewy_wide_chunk_count.argtypes = [c_void_p, c_void_p]

@@ -1,6 +1,5 @@
 """In-tree build of librewy_b200.so (sm_100a) with nvcc.  ``python -m rewy_b200.build``."""
 import hashlib
-import os
 import shutil
 import subprocess
 import sys
@@ -10,12 +9,9 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "csrc" / "build"
-LIB = PKG / os.environ.get("REWY_LIB_NAME", "librewy_b200.so")
-if LIB.name != "librewy_b200.so":
-    OBJ = OBJ / LIB.stem  # experimental builds keep their own object directory
+LIB = PKG / "librewy_b200.so"
 SOURCES = ("capi.cu", "prepare.cu", "state_scan.cu", "state_scan_tc.cu", "chunk_adjoint.cu", "chunk_adjoint_tc.cu", "tc_selftest.cu")
-EXTRA = os.environ.get("REWY_NVCC_EXTRA", "").split()
-NVCC_FLAGS = EXTRA + ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "--expt-extended-lambda", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 
 

@@ -60,13 +60,23 @@ bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) !=
       return fail(REWY_ERR_ALIGN, "pointer '%s' is not 16-byte aligned", #name);           \
   } while (0)
 
+std::atomic<int> g_chunk_variant{0};  // 0 = tensor-core kernel (+ pairwise list), 1 = warp-MMA kernel everywhere
+
+// intra_passes is an option of the warp-MMA chunk kernel (1 or 3 split passes); the tensor-core kernel always runs 3.
+int rc_passes(int passes) {
+  const bool warp_variant = g_chunk_variant.load(std::memory_order_relaxed) == 1;
+  if (passes == 0 || passes == 3 || (passes == 1 && warp_variant)) return REWY_OK;
+  return fail(REWY_ERR_UNSUPPORTED,
+              warp_variant ? "intra_passes must be 0, 1 or 3%s" : "intra_passes must be 0 or 3 with the tensor-core chunk kernel%s");
+}
+
 int validate_common(const RewyBwdArgs* a, int family) {
   if (a == nullptr) return fail(REWY_ERR_NULL, "args is NULL%s");
   if (a->family != family) return fail(REWY_ERR_UNSUPPORTED, "args->family does not match the entry point%s");
   if (a->policy != REWY_RECOMPUTE && a->policy != REWY_SAVED) return fail(REWY_ERR_UNSUPPORTED, "unknown policy%s");
   if (a->out_dtype != REWY_OUT_BF16 && a->out_dtype != REWY_OUT_F32)
     return fail(REWY_ERR_UNSUPPORTED, "unknown out_dtype%s");
-  if (a->intra_passes < 0 || a->intra_passes > 3) return fail(REWY_ERR_UNSUPPORTED, "intra_passes must be 0..3%s");
+  if ((rc_passes(a->intra_passes)) != REWY_OK) return REWY_ERR_UNSUPPORTED;
   if (a->B <= 0 || a->H <= 0) return fail(REWY_ERR_SHAPE, "B and H must be positive%s");
   if (a->T < C || a->T % C != 0) return fail(REWY_ERR_SHAPE, "T must be a positive multiple of 64 (got %s%lld)", "", a->T);
   if ((long long)a->B * a->H > 65535) return fail(REWY_ERR_SHAPE, "B*H exceeds the grid limit 65535%s");
@@ -110,8 +120,6 @@ void timing_mark(int set, int idx, cudaStream_t st) {
   g_timing.have[set][idx] = true;
 }
 
-std::atomic<int> g_chunk_variant{0};  // 0 = tensor-core kernel (+ pairwise list), 1 = warp-MMA kernel everywhere
-
 std::atomic<int> g_scan_variant{0};   // 0 = tensor-core reverse scan, 1 = warp-MMA reverse scan
 
 cudaError_t run_fwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
@@ -120,14 +128,14 @@ cudaError_t run_fwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaSt
 }
 
 cudaError_t run_bwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
-  if (g_scan_variant.load(std::memory_order_relaxed) == 1 || s.ctrl == nullptr) {
-    if (s.ctrl != nullptr) {
-      cudaError_t e = cudaMemsetAsync(s.ctrl, 0, sizeof(int), st);
-      if (e != cudaSuccess) return e;
-    }
-    return launch_bwd_scan(a, s, st);
-  }
+  if (g_scan_variant.load(std::memory_order_relaxed) == 1 || s.ctrl == nullptr) return launch_bwd_scan(a, s, st);
   return launch_bwd_scan_tc(a, s, static_cast<int*>(s.ctrl), st);
+}
+
+// The status word is zeroed ONCE per call, before its first stage: every kernel records a give-up with
+// atomicCAS(word, 0, site), so the first failing site of the call is what the host reads afterwards.
+cudaError_t clear_status(void* ctrl, cudaStream_t st) {
+  return ctrl == nullptr ? cudaSuccess : cudaMemsetAsync(ctrl, 0, sizeof(int), st);
 }
 
 cudaError_t run_chunk_adjoint(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
@@ -174,6 +182,7 @@ int run_family(const RewyBwdArgs* a, int family, cudaStream_t st) {
     set = g_timing.used++;
     for (int i = 0; i <= TIMING_STAGES; i++) g_timing.have[set][i] = false;
   }
+  if ((rc = check_cuda(clear_status(s.ctrl, st), "status word")) != REWY_OK) return rc;
   timing_mark(set, 0, st);
   if (p.prepare) {
     if ((rc = check_cuda(launch_prepare(*a, s, st), "prepare")) != REWY_OK) return rc;
@@ -203,6 +212,28 @@ int validate_stage(const RewyBwdArgs* a, const RewyStageBuffers* s) {
   } while (0)
 
 }  // namespace
+
+// Host-side validation of a chunk-stage call (shape envelope, every pointer present and 16-byte aligned);
+// shared by rewy_stage_chunk_adjoint and rewy_stage_chunk_adjoint_static.
+int validate_chunk_stage(const RewyBwdArgs* a, const RewyStageBuffers* s, bool need_ctrl) {
+  int rc = validate_stage(a, s);
+  if (rc != REWY_OK) return rc;
+  if (a->out_dtype != REWY_OUT_BF16 && a->out_dtype != REWY_OUT_F32) return fail(REWY_ERR_UNSUPPORTED, "unknown out_dtype%s");
+  if (rc_passes(a->intra_passes) != REWY_OK) return REWY_ERR_UNSUPPORTED;
+  STAGE_PTR(a->q, "q"); STAGE_PTR(a->k, "k"); STAGE_PTR(a->v, "v"); STAGE_PTR(a->Akk, "Akk"); STAGE_PTR(a->d_o, "d_o");
+  STAGE_PTR(s->v_new, "v_new"); STAGE_PTR(s->h, "h"); STAGE_PTR(s->dh, "dh"); STAGE_PTR(s->dR, "dR");
+  STAGE_PTR(s->dR_lo, "dR_lo");
+  if (need_ctrl) STAGE_PTR(s->ctrl, "ctrl");
+  STAGE_PTR(a->dq, "dq"); STAGE_PTR(a->dk, "dk"); STAGE_PTR(a->dv, "dv");
+  if (a->family != REWY_DELTA) { STAGE_PTR(a->g, "g"); STAGE_PTR(a->dg, "dg"); }
+  if (a->family == REWY_GDN2) {
+    STAGE_PTR(a->b_gate, "b_gate"); STAGE_PTR(a->w_gate, "w_gate"); STAGE_PTR(a->db_gate, "db_gate");
+    STAGE_PTR(a->dw_gate, "dw_gate");
+  } else {
+    STAGE_PTR(a->beta, "beta"); STAGE_PTR(a->dbeta, "dbeta");
+  }
+  return REWY_OK;
+}
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
@@ -244,6 +275,7 @@ int rewy_stage_fwd_scan(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_st
   if (rc != REWY_OK) return rc;
   STAGE_PTR(s->kg, "kg"); STAGE_PTR(s->w, "w"); STAGE_PTR(s->u, "u"); STAGE_PTR(s->h, "h"); STAGE_PTR(s->v_new, "v_new");
   if (a->family != REWY_DELTA) STAGE_PTR(a->g, "g");
+  if ((rc = check_cuda(clear_status(s->ctrl, (cudaStream_t)st), "status word")) != REWY_OK) return rc;
   return check_cuda(run_fwd_scan(*a, *s, (cudaStream_t)st), "forward state scan");
 }
 
@@ -253,28 +285,15 @@ int rewy_stage_bwd_scan(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_st
   STAGE_PTR(s->qg, "qg"); STAGE_PTR(s->kg, "kg"); STAGE_PTR(s->w, "w"); STAGE_PTR(s->Aqk, "Aqk");
   STAGE_PTR(a->d_o, "d_o"); STAGE_PTR(s->dh, "dh"); STAGE_PTR(s->dR, "dR"); STAGE_PTR(s->dR_lo, "dR_lo");
   if (a->family != REWY_DELTA) STAGE_PTR(a->g, "g");
+  if ((rc = check_cuda(clear_status(s->ctrl, (cudaStream_t)st), "status word")) != REWY_OK) return rc;
   return check_cuda(run_bwd_scan(*a, *s, (cudaStream_t)st), "reverse state scan");
 }
 
 int rewy_stage_chunk_adjoint(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_stream_t st) {
-  int rc = validate_stage(a, s);
+  int rc = validate_chunk_stage(a, s, g_chunk_variant.load(std::memory_order_relaxed) != 1);
   if (rc != REWY_OK) return rc;
-  STAGE_PTR(a->q, "q"); STAGE_PTR(a->k, "k"); STAGE_PTR(a->v, "v"); STAGE_PTR(a->Akk, "Akk"); STAGE_PTR(a->d_o, "d_o");
-  STAGE_PTR(s->v_new, "v_new"); STAGE_PTR(s->h, "h"); STAGE_PTR(s->dh, "dh"); STAGE_PTR(s->dR, "dR");
-  STAGE_PTR(s->dR_lo, "dR_lo");
-  if (g_chunk_variant.load(std::memory_order_relaxed) != 1) STAGE_PTR(s->ctrl, "ctrl");
-  STAGE_PTR(a->dq, "dq"); STAGE_PTR(a->dk, "dk"); STAGE_PTR(a->dv, "dv");
-  if (a->family != REWY_DELTA) { STAGE_PTR(a->g, "g"); STAGE_PTR(a->dg, "dg"); }
-  if (a->family == REWY_GDN2) {
-    STAGE_PTR(a->b_gate, "b_gate"); STAGE_PTR(a->w_gate, "w_gate"); STAGE_PTR(a->db_gate, "db_gate");
-    STAGE_PTR(a->dw_gate, "dw_gate");
-  } else {
-    STAGE_PTR(a->beta, "beta"); STAGE_PTR(a->dbeta, "dbeta");
-  }
-  if (s->ctrl != nullptr) {  // standalone stage call: start from a clean status word
-    int rc0 = check_cuda(cudaMemsetAsync(s->ctrl, 0, sizeof(int), (cudaStream_t)st), "chunk adjoint");
-    if (rc0 != REWY_OK) return rc0;
-  }
+  // standalone stage call: start from a clean status word
+  if ((rc = check_cuda(clear_status(s->ctrl, (cudaStream_t)st), "status word")) != REWY_OK) return rc;
   return check_cuda(run_chunk_adjoint(*a, *s, (cudaStream_t)st), "chunk adjoint");
 }
 

@@ -49,9 +49,6 @@ struct TcParams {
   int T, H, NT, total_chunks, out_f32;
   FastDiv div_nt, div_h;
   float scale;
-#ifdef REWY_PHASE_PROF
-  long long* prof;  // [CTA 0's chunk iteration][16] clock64 stamps (debug builds only)
-#endif
 };
 
 // Shared-memory plan (byte offsets from a 1024-byte aligned base).  Regions are reused as soon as the product that
@@ -358,16 +355,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   };
   fetch_rows(blockIdx.x, 0);
 
-#ifdef REWY_PHASE_PROF
-  int prof_it = 0;
-#define STAMP(i) do { if (p.prof != nullptr && blockIdx.x == 0 && tid == 64 && prof_it < 64) p.prof[prof_it * 32 + (i)] = clock64(); } while (0)
-#define STAMP0(i) do { if (p.prof != nullptr && blockIdx.x == 0 && tid == 0 && prof_it < 64) p.prof[2048 + prof_it * 32 + (i)] = clock64(); } while (0)
-#else
-#define STAMP(i) do {} while (0)
-#define STAMP0(i) do {} while (0)
-#endif
   for (int chunk = blockIdx.x; chunk < p.total_chunks && alive; chunk += gridDim.x) {
-    STAMP(0);
     // Work order: head fastest, then chunk, then batch.  CTAs that run at the same time then read the same token rows
     // (the heads of a row are contiguous in memory) and neighbouring state tiles.
     const int bn = p.div_h.quot(chunk), h = chunk - bn * H, b = p.div_nt.quot(bn), n = bn - b * NT;
@@ -377,19 +365,15 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     const int hrow0 = ((b * NT + n) * H + h) * 128;        // first row of this chunk's state in [B*NT*H*128]
     const int next_chunk = chunk + gridDim.x;
     uint32_t used = (1u << BAR_A) | (1u << BAR_G);
-    STAMP(28);
 
     const float* sBeta = sBeta2 + buf * C;
     const float* sGs = sGs2 + buf * C;
-    STAMP(16);
     // ---- this thread's 32 tokens of its key channel: k and q (packed BF16 pair) and the gate row ------------
     uint32_t kq[HALF];
     uint32_t bgp[VB ? HALF / 2 : 1];  // GDN2: key gate of the thread's tokens, two BF16 per register
     float g[HALF];
     // k, q and g from the tiles TMA brought in while the previous chunk's epilogue ran
-    STAMP(13);
     wait(BAR_G, 11);
-    STAMP(14);
 #pragma unroll
     for (int j = 0; j < HALF; j++) {
       const int t = t0 + j;
@@ -406,7 +390,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     }
     if (GATE == GATE_VECTOR && wg == NWG - 1) sGl[kch] = g[HALF - 1];
     __syncthreads();  // everyone has its k / g out of the tiles before they are rebuilt as Ec / dAkk tiles
-    STAMP(15);
     float cen = 0.f;
     bool wide = false;
     if (GATE != GATE_NONE) {
@@ -460,7 +443,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       __syncwarp();
     }
     used |= (1u << BAR_B) | (1u << BAR_C) | (VB ? 1u << BAR_W : 0u);
-    STAMP(1);  // operands in registers, centre known
     // From here on g[] holds the centred factor alpha = 2^(g - c) of each token; zeta = 1 / alpha (vector gate), or
     // gamma = 2^g (scalar gate, c = 0).
     if (GATE != GATE_NONE) {
@@ -475,9 +457,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
 
     // ---- P = Akk^T (dR_hi + dR_lo) ----------------------------------------------------------------
     if (warp == 0) {
-      STAMP0(0);
       wait(BAR_A, 1);
-      STAMP0(1);
       if (alive) {
         tc_fence_after_sync();
         if (leader) {
@@ -489,7 +469,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           mma_f16_lo(tb + TM_P, dl(Smem::AKK + ks * 2048, 0), dl(Smem::DRLO + ks * 2048, 8192), ID_P, true);
         mma_commit(&bars[BAR_P]);
         }
-        STAMP0(2);
       }
       __syncwarp();
     }
@@ -513,12 +492,10 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     }
     tmem_st_wait();
 
-    STAMP(2);  // Yc tiles built
     // ---- after P: dh takes the place of the dR tiles; P epilogue (rows 0..63 live in TMEM lanes 0..63) ---------
     wait(BAR_P, 2);
     tc_fence_after_sync();
     if (VB) wait(BAR_W, 15);
-    STAMP(3);  // P ready
     if (warp == 0 && alive) {
       if (leader) {
         mbar_expect_tx(&bars[BAR_D], 32768);
@@ -590,16 +567,13 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       }
       if (!VB) sDbP[(wg * 2 + hs) * 64 + i] = dbv;
     }
-    STAMP(24);
     fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
 
-    STAMP(4);  // P epilogue + Qc done (after barrier)
     // ---- [dAqk/scale ; -dAkk] = [dO ; P] R^T ---------------------------------------------------------
     if (warp == 0) {
-      STAMP0(3);
       wait(BAR_B, 3);
       if (alive) {
         tc_fence_after_sync();
@@ -613,7 +587,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           tma_store_wait_read();
           mma_commit(&bars[BAR_HD]);
         }
-        STAMP0(4);
       }
       __syncwarp();
     }
@@ -634,7 +607,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       tmem_st4(tlane + TM_E + 32 + (wg * (HALF / 8) + t8) * 4, lo);
     }
     tmem_st_wait();
-    STAMP(25);
     // this thread's 32 values of its channel's h row, kept for the chunk-end gate term (the h tile is gone by
     // the time dh arrives)
     uint4 hrow[4];
@@ -646,10 +618,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     } else if (tid == 0) {
       wait(BAR_C, 6);
     }
-    STAMP(26);
     wait(BAR_HD, 4);
     tc_fence_after_sync();
-    STAMP(5);  // HD ready
     if (alive) {
       const int i = kch & 63;
       const bool lower_incl = kch < C;  // lanes 0..63: dAqk (diagonal kept); lanes 64..127: dAkk (strictly lower)
@@ -660,7 +630,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         const int col0 = 16 * wg;
         tmem_ld16(tlane + TM_HD + col0, x);
         tmem_ld_wait();
-        STAMP(29);
 #pragma unroll
         for (int half = 0; half < 2; half++) {
           float y[8];
@@ -679,29 +648,23 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         }
       }
     }
-    STAMP(27);
     fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
 
-    STAMP(6);  // HD epilogue done (after barrier)
     // ---- second product group: [X1|X3], [X2|X4] and the Ec part of X6 ----------------------------------------
     if (warp == 0 && alive) {
-      STAMP0(5);
       tc_fence_after_sync();
       if (leader) {
         // [X1 | X3] = h [dO ; P]^T as one N=128 product (the sign of X3 is applied in the epilogue)
         mma_kmajor<8>(tb + TM_X1, dl(Smem::HS, 16), 16384, dl(Smem::DOP, 16), 16384, ID_KK128, false);
-        STAMP0(6);
         // [X2 | X4] = Yc^T [dAqk ; dAkk]^T, hi/lo split in three passes, Yc^T from tensor memory
         mma_ts4(tb + TM_X2, tb + TM_Y, dl(Smem::HHI, 16), 32, ID_KK128, false);
         mma_ts4(tb + TM_X2, tb + TM_Y + 32, dl(Smem::HHI, 16), 32, ID_KK128, true);
         mma_ts4(tb + TM_X2, tb + TM_Y, dl(Smem::HLO, 16), 32, ID_KK128, true);
         mma_commit(&bars[BAR_Q]);  // X1 and X2 complete: dq can be finished while the rest still runs
-        STAMP0(7);
       }
-      STAMP0(8);
       __syncwarp();
     }
     if (warp == 1 && alive) {
@@ -716,7 +679,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     }
     used |= (1u << BAR_C3) | (1u << BAR_Q) | (1u << BAR_QR);
     // Qc^T into the columns the stacked product has left
-    STAMP(20);
 #pragma unroll
     for (int t8 = 0; t8 < HALF / 8; t8++) {
       float x[8];
@@ -734,9 +696,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) mbar_arrive(&bars[BAR_QR]);  // this warp's part of Qc^T is complete in tensor memory
-    STAMP(21);
     wait(BAR_D, 8);
-    STAMP(22);
     // chunk-end gate term, part 1: sum_v h[k,v] dh[k,v] over this thread's 32 value columns (h from registers,
     // dh from the tile that just landed)
     float hd = 0.f;  // written to the scratch columns once every product is complete
@@ -753,11 +713,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         }
       }
     }
-    STAMP(23);
-    STAMP(7);
     if (warp == 1) {
       wait(BAR_QR, 13);  // Qc^T complete (all sixteen warps), and the leader has issued everything before it
-      STAMP(30);
       if (alive) {
         tc_fence_after_sync();
         if (leader2) {
@@ -770,7 +727,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           mma_commit(&bars[BAR_C3]);
         }
       }
-      STAMP(31);
       __syncwarp();
     }
 
@@ -786,14 +742,12 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     // pass A (needs X1, X2 only): dq, and q*dq parked for the gate row
     wait(BAR_Q, 12);
     tc_fence_after_sync();
-    STAMP(17);
     if (alive) {
       const float ecs = ec * scale;
       float x1[16], x2[16];
       tmem_ld16(tlane + TM_X1 + t0, x1);
       tmem_ld16(tlane + TM_X2 + t0, x2);
       tmem_ld_wait();
-    STAMP(18);
 #pragma unroll
       for (int j = 0; j < HALF; j++) {
         const size_t go = go0 + (size_t)j * ldt;
@@ -806,20 +760,15 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         if (GATE != GATE_NONE) sPark[(t0 + j) * 128 + kch] = qf(j) * dq;
       }
     }
-    STAMP(19);
     wait(BAR_C3, 10);
     tc_fence_after_sync();
     if (GATE != GATE_NONE && alive) tmem_st1(tlane + TM_SCR + wg, hd);
-    STAMP(8);  // all products done
     // every tile of this chunk has been consumed by the tensor core and (barrier above) by the threads: start the
     // next chunk's loads under the rest of the epilogue
-    STAMP0(11);
     if (warp == 0 && alive && next_chunk < p.total_chunks) {
       if (leader) issue_loads(next_chunk, LOAD_G);
       __syncwarp();
     }
-    STAMP0(12);
-    STAMP(9);
     // pass B: dk, db, gate rows in reverse token order
     float run = 0.f;
     const float nec = -ec;
@@ -893,8 +842,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       if (leader) issue_loads(next_chunk, LOAD_A);
       __syncwarp();
     }
-    STAMP(11);  // main epilogue loop done
-    STAMP0(13);
     if (!OUTF32) fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();
@@ -905,7 +852,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       if (VB) tma_store_2d(&tmDBG, sm + Smem::DBT, h * 128, row0);
       tma_store_commit();
     }
-    STAMP(12);  // after its barrier
     if (alive) {
       // chunk-end term of this channel: lambda * sum_v h dh + sum_t k 2^(g_last - g) (R dh^T)
       float endk = 0.f;
@@ -958,7 +904,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         }
       }
     }
-    STAMP(10);  // epilogue done
     ph ^= used;
     buf ^= 1;
     alive = __syncthreads_and(alive ? 1 : 0) != 0;
@@ -966,9 +911,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       tma_store_2d(&tmDG, sPark, h * 128, row0);
       tma_store_commit();
     }
-#ifdef REWY_PHASE_PROF
-    prof_it++;
-#endif
   }
 
   if (leader) tma_store_wait_read();  // shared memory stays valid until the last store has read it
@@ -977,9 +919,6 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
   if (warp == 0) tmem_dealloc(tb, 512);
 }
 
-#ifdef REWY_PHASE_PROF
-long long* g_prof = nullptr;
-#endif
 constexpr size_t TC_SMEM = Smem::TOTAL + 1024;
 
 // mul = ceil(2^(31 + ceil(log2 d)) / d), shift = ceil(log2 d) - 1: exact for every dividend below 2^31.
@@ -1065,9 +1004,6 @@ cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers
   p.wg = (const bf16*)a.w_gate; p.dh = (const bf16*)s.dh; p.g = a.g; p.beta = a.beta;
   p.dq = a.dq; p.dk = a.dk; p.dbg = a.db_gate; p.dwg = a.dw_gate; p.dv = (bf16*)a.dv; p.dg = a.dg; p.dbeta = a.dbeta;
   p.wide_list = ctrl + 1; p.err = ctrl;
-#ifdef REWY_PHASE_PROF
-  p.prof = g_prof;
-#endif
   p.T = T; p.H = H; p.NT = NT; p.total_chunks = B * H * NT; p.out_f32 = a.out_dtype == REWY_OUT_F32;
   p.scale = a.scale;
   p.div_nt = make_fastdiv(NT);
@@ -1129,29 +1065,20 @@ int* static_ctrl_for_current_device(char* why, size_t why_len) {
 extern "C" int rewy_stage_chunk_adjoint_static(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_stream_t stream) {
   using namespace rewy;
   char why[256];
-  if (a == nullptr || s == nullptr) return report_error(REWY_ERR_NULL, "args or buffers is NULL");
-  if (a->family < REWY_DELTA || a->family > REWY_GDN2) return report_error(REWY_ERR_UNSUPPORTED, "unknown family");
-  if (a->B <= 0 || a->H <= 0 || a->T < C || a->T % C != 0) return report_error(REWY_ERR_SHAPE, "bad B/T/H");
-  const long long chunks = (long long)a->B * a->H * (a->T / C);
-  if (chunks > STATIC_MAX_CHUNKS) {
-    snprintf(why, sizeof(why),
-             "rewy_stage_chunk_adjoint_static handles at most %d chunks (B*H*T/64); this call has %lld - use "
-             "rewy_stage_chunk_adjoint with a caller-provided control block",
-             STATIC_MAX_CHUNKS, chunks);
-    return report_error(REWY_ERR_SHAPE, why);
+  // the size limit of the built-in block first (it needs no pointer), then exactly the host-side checks of
+  // rewy_stage_chunk_adjoint (shape envelope, every pointer present and 16-byte aligned) minus RewyStageBuffers.ctrl
+  if (a != nullptr && a->B > 0 && a->H > 0 && a->T >= C) {
+    const long long chunks = (long long)a->B * a->H * (a->T / C);
+    if (chunks > STATIC_MAX_CHUNKS) {
+      snprintf(why, sizeof(why),
+               "rewy_stage_chunk_adjoint_static handles at most %d chunks (B*H*T/64); this call has %lld - use "
+               "rewy_stage_chunk_adjoint with a caller-provided control block",
+               STATIC_MAX_CHUNKS, chunks);
+      return report_error(REWY_ERR_SHAPE, why);
+    }
   }
-  const void* need[] = {a->q, a->k, a->v, a->Akk, a->d_o, s->v_new, s->h, s->dh, s->dR, s->dR_lo, a->dq, a->dk, a->dv};
-  for (const void* ptr : need) {
-    if (ptr == nullptr) return report_error(REWY_ERR_NULL, "a required input or output pointer is NULL");
-    if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return report_error(REWY_ERR_ALIGN, "a pointer is not 16-byte aligned");
-  }
-  if (a->family != REWY_DELTA && (a->g == nullptr || a->dg == nullptr)) return report_error(REWY_ERR_NULL, "g or dg is NULL");
-  if (a->family == REWY_GDN2) {
-    if (a->b_gate == nullptr || a->w_gate == nullptr || a->db_gate == nullptr || a->dw_gate == nullptr)
-      return report_error(REWY_ERR_NULL, "a GDN2 gate pointer is NULL");
-  } else if (a->beta == nullptr || a->dbeta == nullptr) {
-    return report_error(REWY_ERR_NULL, "beta or dbeta is NULL");
-  }
+  const int rc = validate_chunk_stage(a, s, false);
+  if (rc != REWY_OK) return rc;
   int* ctrl = static_ctrl_for_current_device(why, sizeof(why));
   if (ctrl == nullptr) return report_error(REWY_ERR_LAUNCH, why);
   cudaStream_t st = (cudaStream_t)stream;
@@ -1178,7 +1105,3 @@ extern "C" int rewy_static_device_status(rewy_stream_t stream) {
   if (word != 0) return report_error(REWY_ERR_DEVICE, "a kernel gave up on a bounded wait (static control block)");
   return REWY_OK;
 }
-
-#ifdef REWY_PHASE_PROF
-extern "C" void rewy_debug_set_prof(long long* ptr) { rewy::g_prof = ptr; }
-#endif

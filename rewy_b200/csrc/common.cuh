@@ -31,6 +31,8 @@ cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers
 cudaError_t launch_chunk_adjoint_warp(const RewyBwdArgs& a, const RewyStageBuffers& s, const int* list, cudaStream_t st);
 void count_launch(int n = 1);
 int report_error(int code, const char* text);  // stores the text rewy_last_error() returns; gives back `code`
+// shape envelope + presence and 16-byte alignment of every pointer of a chunk-stage call (REWY_OK or an error code)
+int validate_chunk_stage(const RewyBwdArgs* a, const RewyStageBuffers* s, bool need_ctrl);
 
 __host__ __device__ inline int gate_mode_of(int family) {
   return family == REWY_DELTA ? GATE_NONE : (family == REWY_GDN ? GATE_SCALAR : GATE_VECTOR);

@@ -562,7 +562,8 @@ cudaError_t run(const CUtensorMap* tm, const ScanParams& p, int grid, cudaStream
 
 }  // namespace
 
-// err: device status word (set non-zero if a bounded wait gives up); must be zero on entry.
+// err: device status word.  A bounded wait that gives up records its site there with atomicCAS(err, 0, site), so the
+// first failing site of a call survives; the caller zeroes the word once per call, before its first stage.
 cudaError_t launch_bwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* err, cudaStream_t st) {
   const int B = a.B, T = a.T, H = a.H, NT = T / C;
   const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
@@ -574,8 +575,6 @@ cudaError_t launch_bwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, 
             encode_tmap_2d(&tm[4], s.Aqk, 2, (uint64_t)H * 64, rows, (uint64_t)H * 128, 64, 64) &&
             encode_tmap_2d(&tm[5], s.dh, 2, 128, srows, 256, 64, 128);
   if (!ok) return cudaErrorInvalidValue;
-  cudaError_t e0 = cudaMemsetAsync(err, 0, sizeof(int), st);
-  if (e0 != cudaSuccess) return e0;
   ScanParams p;
   p.g = a.g; p.dht = a.dht; p.dR = (bf16*)s.dR; p.dRlo = (bf16*)s.dR_lo; p.dh0 = a.dh0; p.err = err;
   p.T = T; p.H = H; p.NT = NT; p.scale = a.scale;
@@ -586,7 +585,7 @@ cudaError_t launch_bwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, 
   }
 }
 
-// err: device status word; must be zero on entry (the reverse scan that follows clears it again).
+// err: device status word, same contract as for the reverse scan.
 cudaError_t launch_fwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* err, cudaStream_t st) {
   const int B = a.B, T = a.T, H = a.H, NT = T / C;
   const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
@@ -596,8 +595,6 @@ cudaError_t launch_fwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, 
             encode_tmap_2d(&tm[2], s.u, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 64) &&
             encode_tmap_2d(&tm[3], s.h, 2, 128, srows, 256, 64, 128);
   if (!ok) return cudaErrorInvalidValue;
-  cudaError_t e0 = cudaMemsetAsync(err, 0, sizeof(int), st);
-  if (e0 != cudaSuccess) return e0;
   FwdParams p;
   p.g = a.g; p.h0 = a.h0; p.v_new = (bf16*)s.v_new; p.err = err; p.T = T; p.H = H; p.NT = NT;
   switch (gate_mode_of(a.family)) {

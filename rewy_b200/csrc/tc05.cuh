@@ -35,8 +35,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (and sets *err to `code`) if the phase never completed.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
+// Bounded wait.  Returns false (and records `code` in *err, first failing site wins) if the phase has not completed
+// after limit_ns nanoseconds of %globaltimer.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, int* err, int code, unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0, t1;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
@@ -46,10 +47,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-    if (t1 - t0 > WAIT_LIMIT_NS) break;
+    if (t1 - t0 > limit_ns) break;
   }
   if (err != nullptr) atomicCAS(err, 0, code);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
+  return mbar_wait_limit(bar, parity, err, code, WAIT_LIMIT_NS);
 }
 
 // One lane of a fully active warp (used inside warp-uniform branches, so that the operands of the single-thread

@@ -163,10 +163,34 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
   if (warp == 0) tmem_dealloc(tb, 512);
 }
 
+// Self-test of the give-up path of the bounded waits: every thread waits, with a short limit, for a phase of an
+// mbarrier that nobody ever arrives on (no copy and no product is in flight), records the site, folds the per-thread
+// flags exactly like the stages do and returns normally.
+__global__ void bounded_wait_selftest_kernel(int* err, int* done, unsigned long long limit_ns, int site) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  bool alive = mbar_wait_limit(&bar, 0, err, site, limit_ns);
+  alive = __syncthreads_and(alive ? 1 : 0) != 0;
+  if (threadIdx.x == 0) *done = alive ? 1 : 2;  // 2: the wait ran out and the CTA left through the give-up path
+}
+
 }  // namespace
 }  // namespace rewy
 
 using namespace rewy;
+
+extern "C" int rewy_selftest_bounded_wait(int* err, int* done, uint32_t limit_us, int site, rewy_stream_t stream) {
+  if (err == nullptr || done == nullptr) return report_error(REWY_ERR_NULL, "err or done is NULL");
+  if (limit_us == 0 || limit_us > 1000000u || site == 0)
+    return report_error(REWY_ERR_UNSUPPORTED, "limit_us must be 1..1000000 and site non-zero");
+  bounded_wait_selftest_kernel<<<1, 128, 0, (cudaStream_t)stream>>>(err, done, (unsigned long long)limit_us * 1000ull, site);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? REWY_OK : REWY_ERR_LAUNCH;
+}
 
 // A [128x128] bf16, B [64x128] bf16, Akk [64x64] bf16, dR [64x128] bf16, Y [128x64] f32, H [64x64] f32 (row-major,
 // device); out [128x384] f32: columns 0-63 A B^T, 64-127 -(A B^T), 128-255 rows 0-63 Akk^T dR, 256-319 Y H^T,

@@ -128,8 +128,10 @@ def rejection_reason(op, arguments, device_types=("cuda",)):
     return None
 
 
+@lru_cache(None)
 def original_operator(op):
-    """The installed FLA operator, if any ('original' backend / non-strict forwarding)."""
+    """The installed FLA operator, if any ('original' backend / non-strict forwarding).  Cached at first use, so
+    aliases patched later by ``rewy_b200.integrations`` do not shadow it."""
     family, name = OPERATORS[op]
     try:
         module = importlib.import_module(f"fla.ops.{family}.chunk")

@@ -41,3 +41,26 @@ def test_tensor_core_operand_forms():
     }
     errs = {n: ((got.double() - ref).norm() / ref.norm()).item() for n, (got, ref) in want.items()}
     assert all(e < 1e-5 for e in errs.values()), errs
+
+
+def test_a_bounded_wait_that_runs_out_returns_and_is_reported():
+    """The failure path of every device-side wait: a wait on an mbarrier phase that nothing completes gives up after
+    its limit (2 ms here), records its site in the status word, the CTA folds the per-thread flags and returns
+    normally; the host then reads REWY_ERR_DEVICE.  Nothing faults, traps or spins without a bound, and the context
+    stays usable (the operand self-test runs afterwards in the same process)."""
+    lib = _capi.load()
+    words = torch.zeros(2, dtype=torch.int32, device=DEV)      # [status word, wide-chunk count] like a control block
+    done = torch.zeros(1, dtype=torch.int32, device=DEV)
+    stream = _capi.current_stream(torch.device(DEV))
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    with torch.cuda.device(DEV):
+        assert lib.rewy_selftest_bounded_wait(p(words), p(done), 2000, 77, stream) == 0
+        torch.cuda.synchronize()
+        assert done.item() == 2 and words[0].item() == 77
+        assert lib.rewy_device_status(p(words), stream) == 6          # REWY_ERR_DEVICE
+        assert b"site 77" in lib.rewy_last_error()
+        # the first failing site is kept: a second give-up does not overwrite it
+        assert lib.rewy_selftest_bounded_wait(p(words), p(done), 1000, 78, stream) == 0
+        torch.cuda.synchronize()
+        assert words[0].item() == 77
+    test_tensor_core_operand_forms()

@@ -152,3 +152,96 @@ def test_forward_producer_matches_oracle_forward_on_cpu():
             assert err < 6e-3, (op, n, err)
         if op != "delta":
             assert torch.allclose(got["g_cumsum"].double(), ref["g_cumsum"], atol=1e-5)
+
+
+def _fake_stage_call(family, skew=None):
+    """A chunk-stage call whose pointers are made-up, 16-byte aligned addresses (never dereferenced: validation
+    happens on the host before any CUDA call); `skew` names one pointer that is moved off the 16-byte grid."""
+    from rewy_b200 import _capi
+    a, s = _capi.BwdArgs(), _capi.StageBuffers()
+    a.family, a.B, a.T, a.H, a.out_dtype, a.scale = family, 1, 128, 2, _capi.OUT_F32, 1.0
+    names_a = ["q", "k", "v", "Akk", "d_o", "dq", "dk", "dv", "g", "dg"]
+    names_a += ["b_gate", "w_gate", "db_gate", "dw_gate"] if family == _capi.GDN2 else ["beta", "dbeta"]
+    addr = 0x10000
+    for n in names_a:
+        setattr(a, n, addr + (4 if n == skew else 0))
+        addr += 0x1000
+    for n in ("v_new", "h", "dh", "dR", "dR_lo", "ctrl"):
+        setattr(s, n, addr + (4 if n == skew else 0))
+        addr += 0x1000
+    return a, s
+
+
+@pytest.mark.parametrize("entry", ("rewy_stage_chunk_adjoint", "rewy_stage_chunk_adjoint_static"))
+@pytest.mark.parametrize("family,skew", [("KDA", "g"), ("KDA", "dg"), ("GDN2", "dw_gate"), ("GDN2", "b_gate"),
+                                         ("KDA", "dR_lo"), ("KDA", "dbeta")])
+def test_chunk_stage_entries_report_misaligned_pointers_before_any_launch(entry, family, skew):
+    """Both chunk-stage entry points run the same host-side checks: a pointer off the 16-byte grid is
+    REWY_ERR_ALIGN (3), naming the pointer, and nothing is launched."""
+    from rewy_b200 import _capi
+    lib = _capi.load()
+    a, s = _fake_stage_call(getattr(_capi, family), skew)
+    before = lib.rewy_kernel_launch_count()
+    assert getattr(lib, entry)(a, s, None) == 3
+    assert skew.encode() in lib.rewy_last_error()
+    assert lib.rewy_kernel_launch_count() == before
+
+
+def test_static_chunk_stage_checks_the_grid_limit_and_missing_pointers():
+    from rewy_b200 import _capi
+    lib = _capi.load()
+    a, s = _fake_stage_call(_capi.KDA)
+    a.B, a.H, a.T = 2048, 32, 64            # B*H = 65536 is beyond the grid limit, yet within the block's chunk count
+    assert lib.rewy_stage_chunk_adjoint_static(a, s, None) == 2 and b"65535" in lib.rewy_last_error()
+    a, s = _fake_stage_call(_capi.KDA)
+    a.dbeta = None
+    assert lib.rewy_stage_chunk_adjoint_static(a, s, None) == 1 and b"dbeta" in lib.rewy_last_error()
+
+
+def test_intra_passes_is_an_option_of_the_warp_mma_variant_only():
+    from rewy_b200 import _capi
+    lib = _capi.load()
+    a, s = _fake_stage_call(_capi.KDA)
+    for passes, want in ((1, 7), (2, 7), (4, 7)):
+        a.intra_passes = passes
+        assert lib.rewy_stage_chunk_adjoint(a, s, None) == want, passes
+    assert b"intra_passes" in lib.rewy_last_error()
+    a.intra_passes, a.family, a.policy, a.T = 2, _capi.KDA, _capi.SAVED, 128
+    assert lib.rewy_kda_bwd(a, None) == 7
+
+
+def test_selftest_bounded_wait_rejects_bad_arguments():
+    from rewy_b200 import _capi
+    lib = _capi.load()
+    assert lib.rewy_selftest_bounded_wait(None, None, 1000, 5, None) == 1
+    assert lib.rewy_selftest_bounded_wait(0x1000, 0x2000, 0, 5, None) == 7
+    assert lib.rewy_selftest_bounded_wait(0x1000, 0x2000, 2000000, 5, None) == 7
+
+
+def test_fla_integration_patches_and_restores_public_aliases():
+    """enable(integrations=('fla',)) makes FLA's public names resolve to the dispatching entries; the captured
+    originals stay reachable; uninstall puts the aliases back.  Families the installed FLA lacks are reported."""
+    fla = pytest.importorskip("fla")
+    import importlib
+    from rewy_b200 import integrations, runtime
+    mod = importlib.import_module("fla.ops.kda")
+    before = mod.chunk_kda
+    try:
+        report = integrations.install()
+        assert "kda" in report["patched"] and "gdn" in report["patched"] and "delta" in report["patched"]
+        assert mod.chunk_kda is runtime.operator("kda")
+        assert importlib.import_module("fla.ops.kda.chunk").chunk_kda is runtime.operator("kda")
+        assert importlib.import_module("fla.ops.delta_rule").chunk_delta_rule is runtime.operator("delta")
+        assert runtime.original_operator("kda") is not runtime.operator("kda")
+        assert integrations.install() is report                      # idempotent
+        for op, why in report["skipped"].items():
+            assert "no original (FLA) operator" in why, (op, why)
+    finally:
+        integrations.uninstall()
+    assert mod.chunk_kda is before
+
+
+def test_unknown_integration_is_rejected():
+    import rewy_b200 as fdr
+    with pytest.raises(ValueError, match="Unknown integration"):
+        fdr.enable("original", integrations=("jax",))
