@@ -43,7 +43,7 @@ def metric_name(workload, policy_saved):
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="rewy_b200", choices=("rewy_b200", "reference"))
     ap.add_argument("--workload", default="cfg2_kda", choices=("cfg1_gdn", "cfg2_kda", "cfg3_delta", "cfg4_gdn2"))
@@ -62,48 +62,90 @@ def parse():
 # ---------------------------------------------------------------------------------------------
 # clocks
 class ClockSampler:
-    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+    """Samples the SM clock and the throttle reasons of one GPU while the timed region runs (read-only NVML queries
+    from a thread, every few milliseconds; nvidia-smi in a loop if the NVML binding is missing)."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
-    def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index, uuid=None):
+        self.index, self.uuid, self.rows, self.proc, self.nvml = index, uuid, [], None, None
+        self.stop_flag = threading.Event()
+        self.max_mhz = None
+
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [x.strip() for x in vis.split(",") if x.strip()]
+            if self.index < len(ids) and ids[self.index].isdigit():
+                return int(ids[self.index])
+        return self.index
 
     def start(self):
         try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            if self.uuid:   # the CUDA device's own UUID: immune to CUDA_VISIBLE_DEVICES renumbering
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(self.uuid.encode())
+            else:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
+        try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+                ["nvidia-smi", f"--id={self._physical_index()}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read_smi, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
 
-    def _read(self):
+    def _poll_nvml(self):
+        nv = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                mhz = float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+            except Exception:
+                break
+            self.rows.append((time.perf_counter(), mhz, {n for n, bit in self.REASONS.items() if mask & bit}))
+            time.sleep(0.004)
+
+    def _read_smi(self):
         for line in self.proc.stdout:
-            self.rows.append((time.perf_counter(), line.strip()))
+            f = [x.strip() for x in line.split(",")]
+            try:
+                mhz, self.max_mhz = float(f[0]), float(f[1])
+            except (ValueError, IndexError):
+                continue
+            names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+            self.rows.append((time.perf_counter(), mhz, {n for n, v in zip(names, f[2:6]) if v.lower().startswith("active")}))
 
     def stop(self, t0, t1):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        rows = [r for t, r in self.rows if t0 <= t <= t1] or [r for _, r in self.rows[-3:]]
-        mhz, mx, reasons = [], None, set()
-        for r in rows:
-            f = [x.strip() for x in r.split(",")]
-            if len(f) < 6:
-                continue
-            try:
-                mhz.append(float(f[0]))
-                mx = float(f[1])
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[2:6]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(mhz)}
+        """Summary of the samples taken between t0 and t1 (perf_counter); if the region was shorter than one sampling
+        period, of the samples closest to it (the warm-up just before runs the same load)."""
+        time.sleep(0.03)
+        self.stop_flag.set()
+        if self.proc is not None:
+            self.proc.terminate()
+        if self.nvml is None and self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no NVML binding and no nvidia-smi"], "samples": 0}
+        inside = [r for r in self.rows if t0 <= r[0] <= t1]
+        where = "inside the timed region"
+        if not inside:
+            inside = sorted(self.rows, key=lambda r: min(abs(r[0] - t0), abs(r[0] - t1)))[:5]
+            where = "nearest to the timed region (it was shorter than one sampling period)"
+        reasons = set()
+        for r in inside:
+            reasons |= r[2]
+        mhz = [r[1] for r in inside]
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(reasons),
+                "samples": len(mhz), "sampled": where, "source": "NVML" if self.nvml is not None else "nvidia-smi"}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -245,6 +287,10 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)   # NCCL logs to stderr; stdout stays the one JSON line
     _capi.load()
+    try:
+        gpu_uuid = "GPU-" + str(torch.cuda.get_device_properties(local).uuid)
+    except Exception:
+        gpu_uuid = None
 
     def barrier():
         if world > 1:
@@ -260,13 +306,12 @@ def main():
 
     def timed(prob, policy_saved, steps, warmup, sample_clocks=False):
         ws = prob.workspace(policy_saved)
+        sampler = ClockSampler(local, gpu_uuid) if sample_clocks else None
+        if sampler:
+            sampler.start()
         for _ in range(warmup):
             prob.call(policy_saved, ws)
         barrier()
-        sampler = ClockSampler(local) if sample_clocks else None
-        if sampler:
-            sampler.start()
-            time.sleep(0.3)
         _capi.stage_timing_enable(True)
         launches0 = _capi.launch_count()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -6,11 +6,85 @@ autograd backwards call as ``chunk_kda_bwd`` / ``chunk_gdn2_bwd`` / ``chunk_gate
 ``chunk_delta_rule_bwd`` (src/fast_delta_rule/_compat/kda.py:169-201, gdn2.py:145-171, gdn.py:240-260,
 delta.py:125-138).  All arithmetic happens in librewy_b200.so; this module only checks the envelope,
 allocates outputs and workspace with torch and marshals raw pointers.
+
+The call into the library is a torch custom operator, ``torch.ops.rewy_b200.family_bwd`` (registered with
+``torch.library`` for CUDA tensors, with a shape-only fake implementation): the four functions below are
+thin bindings of it, so the backward is a single opaque node for ``torch.compile`` / export, and the C ABI
+stays the only thing underneath.
 """
+from typing import Optional
+
 import torch
+from torch import Tensor
 
 from . import _capi
 from .runtime import record
+
+_FAMILY_FN = {_capi.KDA: "rewy_kda_bwd", _capi.GDN2: "rewy_gdn2_bwd", _capi.GDN: "rewy_gdn_bwd",
+              _capi.DELTA: "rewy_delta_bwd"}
+_NONE = None
+
+
+def _empty(dev):
+    return torch.empty(0, device=dev)
+
+
+@torch.library.custom_op("rewy_b200::family_bwd", mutates_args=("workspace",), device_types="cuda")
+def _family_bwd(family: int, policy: int, out_f32: bool, intra_passes: int, scale: float,
+                q: Tensor, k: Tensor, v: Tensor, d_o: Tensor, Akk: Tensor, workspace: Tensor,
+                g: Optional[Tensor], beta: Optional[Tensor], b_gate: Optional[Tensor], w_gate: Optional[Tensor],
+                Aqk: Optional[Tensor], h0: Optional[Tensor], dht: Optional[Tensor], w: Optional[Tensor],
+                qg: Optional[Tensor], kg: Optional[Tensor], v_new: Optional[Tensor], h: Optional[Tensor],
+                ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """(dq, dk, dv, dg, dbeta, db_gate, dw_gate, dh0); outputs a family does not have are empty tensors.
+    Tensors must be contiguous, on one CUDA device, in the dtypes of RewyBwdArgs."""
+    lib = _capi.load()
+    B, T, H, _ = k.shape
+    dev = q.device
+    odt = torch.float32 if out_f32 else torch.bfloat16
+    shape = (B, T, H, 128)
+    vector_gates = family == _capi.GDN2
+    out = dict(
+        dq=torch.empty(shape, dtype=odt, device=dev), dk=torch.empty(shape, dtype=odt, device=dev),
+        dv=torch.empty(shape, dtype=torch.bfloat16, device=dev),
+        dg=torch.empty_like(g) if g is not None else None,
+        dbeta=torch.empty((B, T, H), dtype=torch.float32, device=dev) if not vector_gates else None,
+        db_gate=torch.empty(shape, dtype=odt, device=dev) if vector_gates else None,
+        dw_gate=torch.empty(shape, dtype=odt, device=dev) if vector_gates else None,
+        dh0=torch.empty((B, H, 128, 128), dtype=torch.float32, device=dev) if h0 is not None else None,
+    )
+    a = _capi.BwdArgs()
+    a.family, a.policy, a.B, a.T, a.H = family, policy, B, T, H
+    a.out_dtype = _capi.OUT_F32 if out_f32 else _capi.OUT_BF16
+    a.intra_passes = intra_passes
+    a.scale = scale
+    for name, t in dict(q=q, k=k, v=v, d_o=d_o, Akk=Akk, g=g, beta=beta, b_gate=b_gate, w_gate=w_gate, Aqk=Aqk, h0=h0,
+                        dht=dht, w=w, qg=qg, kg=kg, v_new=v_new, h=h).items():
+        setattr(a, name, _capi.ptr(t))
+    for name, t in out.items():
+        setattr(a, name, _capi.ptr(t))
+    a.workspace = _capi.ptr(workspace)
+    a.workspace_bytes = workspace.numel() * workspace.element_size()
+    fn = getattr(lib, _FAMILY_FN[family])
+    with torch.cuda.device(dev):
+        # Inputs, outputs and workspace are allocated on (or already in use by) the current stream, the same
+        # stream the launches go to, so the caching allocator's stream-ordered reuse keeps them valid.
+        _capi.check(fn(a, _capi.current_stream(dev)), fn.__name__)
+    return tuple(out[n] if out[n] is not None else _empty(dev)
+                 for n in ("dq", "dk", "dv", "dg", "dbeta", "db_gate", "dw_gate", "dh0"))
+
+
+@_family_bwd.register_fake
+def _family_bwd_fake(family, policy, out_f32, intra_passes, scale, q, k, v, d_o, Akk, workspace, g, beta, b_gate, w_gate,
+                     Aqk, h0, dht, w, qg, kg, v_new, h):
+    B, T, H, _ = k.shape
+    odt = torch.float32 if out_f32 else torch.bfloat16
+    big = lambda dt: q.new_empty((B, T, H, 128), dtype=dt)
+    none = q.new_empty(0, dtype=torch.float32)
+    vec = family == _capi.GDN2
+    return (big(odt), big(odt), big(torch.bfloat16), torch.empty_like(g) if g is not None else none,
+            q.new_empty((B, T, H), dtype=torch.float32) if not vec else none, big(odt) if vec else none,
+            big(odt) if vec else none, q.new_empty((B, H, 128, 128), dtype=torch.float32) if h0 is not None else none)
 
 
 def _unsupported(name, value, allowed=(None, False)):
@@ -51,46 +125,26 @@ def _run(family, policy, B, T, H, scale, tensors, out_dtype, intra_passes, works
          check_status=False):
     """tensors: dict name -> tensor or None for every input pointer of RewyBwdArgs."""
     lib = _capi.load()
-    q = tensors["q"]
-    dev = q.device
-    odt = torch.float32 if out_dtype in (None, torch.float32) else torch.bfloat16
+    dev = tensors["q"].device
     if out_dtype not in (None, torch.float32, torch.bfloat16):
         raise RuntimeError("rewy_b200 backward: out_dtype must be torch.float32 or torch.bfloat16")
-    shape = (B, T, H, 128)
-    out = dict(
-        dq=torch.empty(shape, dtype=odt, device=dev), dk=torch.empty(shape, dtype=odt, device=dev),
-        dv=torch.empty(shape, dtype=torch.bfloat16, device=dev),
-        dg=torch.empty_like(tensors["g"]) if want_dg else None,
-        dbeta=torch.empty((B, T, H), dtype=torch.float32, device=dev) if want_dbeta else None,
-        db_gate=torch.empty(shape, dtype=odt, device=dev) if vector_gates else None,
-        dw_gate=torch.empty(shape, dtype=odt, device=dev) if vector_gates else None,
-        dh0=torch.empty((B, H, 128, 128), dtype=torch.float32, device=dev) if tensors["h0"] is not None else None,
-    )
+    out_f32 = out_dtype in (None, torch.float32)
     need = _capi.workspace_bytes(family, policy, B, T, H)
     if workspace is None:
         workspace = torch.empty(need, dtype=torch.uint8, device=dev)
     elif workspace.numel() * workspace.element_size() < need or workspace.device != dev:
         raise RuntimeError(f"rewy_b200 backward: workspace must hold {need} bytes on {dev}")
-    a = _capi.BwdArgs()
-    a.family, a.policy, a.B, a.T, a.H = family, policy, B, T, H
-    a.out_dtype = _capi.OUT_F32 if odt == torch.float32 else _capi.OUT_BF16
-    a.intra_passes = int(intra_passes or 0)
-    a.scale = float(scale)
-    for name, t in tensors.items():
-        setattr(a, name, _capi.ptr(t))
-    for name, t in out.items():
-        setattr(a, name, _capi.ptr(t))
-    a.workspace = _capi.ptr(workspace)
-    a.workspace_bytes = workspace.numel() * workspace.element_size()
-    fn = {_capi.KDA: lib.rewy_kda_bwd, _capi.GDN2: lib.rewy_gdn2_bwd, _capi.GDN: lib.rewy_gdn_bwd,
-          _capi.DELTA: lib.rewy_delta_bwd}[family]
-    with torch.cuda.device(dev):
-        _capi.check(fn(a, _capi.current_stream(dev)), fn.__name__)
-        if check_status:  # synchronises: reads the device status word at the start of the workspace
+    t = tensors
+    r = torch.ops.rewy_b200.family_bwd(
+        family, policy, out_f32, int(intra_passes or 0), float(scale), t["q"], t["k"], t["v"], t["d_o"], t["Akk"],
+        workspace, t["g"], t["beta"], t["b_gate"], t["w_gate"], t["Aqk"], t["h0"], t["dht"], t["w"], t["qg"], t["kg"],
+        t["v_new"], t["h"])
+    names = ("dq", "dk", "dv", "dg", "dbeta", "db_gate", "dw_gate", "dh0")
+    out = {n: (x if x.numel() else None) for n, x in zip(names, r)}
+    if check_status:  # synchronises: reads the device status word at the start of the workspace
+        with torch.cuda.device(dev):
             _capi.check(lib.rewy_device_status(_capi.ptr(workspace), _capi.current_stream(dev)), "device status")
             out["wide_chunks"] = int(lib.rewy_wide_chunk_count(_capi.ptr(workspace), _capi.current_stream(dev)))
-    # Inputs, outputs and workspace were allocated on (or are already in use by) the current stream, the
-    # same stream the launches went to, so the caching allocator's stream-ordered reuse keeps them valid.
     return out
 
 

@@ -18,6 +18,7 @@ import pytest
 import torch
 
 from gpu_util import nrmse, oracle_backward
+from rewy_b200 import _capi
 from rewy_b200 import backward as bw
 from rewy_b200.forward import chunk_forward
 from rewy_b200.synthetic import CONFIGS, make_inputs
@@ -30,8 +31,23 @@ SCALE = 128 ** -0.5
 
 
 def _call(op, xs, sv, saved, out_dtype):
+    r = _call_family(op, xs, sv, saved, out_dtype)
+    torch.cuda.synchronize()
+    return r
+
+
+def _call_family(op, xs, sv, saved, out_dtype):
+    B, T, H, _ = xs["k"].shape
+    ws = torch.empty(_capi.workspace_bytes(_capi.FAMILY_ID[op], _capi.SAVED if saved else _capi.RECOMPUTE, B, T, H),
+                     dtype=torch.uint8, device=DEV)
     common = dict(q=xs["q"], k=xs["k"], v=xs["v"], scale=SCALE, initial_state=xs.get("initial_state"), do=xs["do"],
-                  dht=xs.get("dht"), out_dtype=out_dtype, check_status=True)
+                  dht=xs.get("dht"), out_dtype=out_dtype, workspace=ws, check_status=True)
+    out = _call_op(op, xs, sv, saved, common)
+    out["wide_chunks"] = _capi.load().rewy_wide_chunk_count(_capi.ptr(ws), _capi.current_stream(torch.device(DEV)))
+    return out
+
+
+def _call_op(op, xs, sv, saved, common):
     if op == "kda":
         r = bw.kda_backward(beta=xs["beta"], Aqk=sv["Aqk"], Akk=sv["Akk"], g=sv["g_cumsum"], disable_recompute=saved,
                             w=sv["w"], u=sv["u"], qg=sv["qg"], kg=sv["kg"], v_new=sv["v_new"], h=sv["h"], **common)

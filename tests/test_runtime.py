@@ -245,3 +245,24 @@ def test_unknown_integration_is_rejected():
     import rewy_b200 as fdr
     with pytest.raises(ValueError, match="Unknown integration"):
         fdr.enable("original", integrations=("jax",))
+
+
+def test_custom_op_is_registered_with_a_shape_only_implementation():
+    """The backward is one torch custom operator over the C ABI; its fake implementation gives the output shapes and
+    dtypes of every family without touching a device."""
+    from rewy_b200 import _capi, backward
+    assert "rewy_b200::family_bwd" in str(torch.ops.rewy_b200.family_bwd.default._schema)
+    B, T, H = 2, 128, 3
+    m = lambda *s, dt=torch.bfloat16: torch.empty(*s, dtype=dt, device="meta")
+    big, a64 = m(B, T, H, 128), m(B, T, H, 64)
+    ws = m(1024, dt=torch.uint8)
+    g = m(B, T, H, 128, dt=torch.float32)
+    h0 = m(B, H, 128, 128, dt=torch.float32)
+    r = backward._family_bwd_fake(_capi.KDA, _capi.RECOMPUTE, False, 0, 1.0, big, big, big, big, a64, ws, g,
+                                  m(B, T, H, dt=torch.float32), None, None, a64, h0, h0, None, None, None, None, None)
+    assert [tuple(x.shape) for x in r] == [(B, T, H, 128)] * 4 + [(B, T, H), (0,), (0,), (B, H, 128, 128)]
+    assert r[0].dtype == torch.bfloat16 and r[3].dtype == torch.float32
+    r = backward._family_bwd_fake(_capi.GDN2, _capi.SAVED, True, 0, 1.0, big, big, big, big, a64, ws, g, None, big, big,
+                                  a64, None, None, big, big, big, big, m(B, T // 64, H, 128, 128))
+    assert [tuple(x.shape) for x in r] == [(B, T, H, 128)] * 4 + [(0,)] + [(B, T, H, 128)] * 2 + [(0,)]
+    assert r[0].dtype == torch.float32 and r[5].dtype == torch.float32

@@ -42,11 +42,10 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, B=2, T=128, H=2):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from oracle import chunk_backward, chunk_forward
-    B, T, H = 2, 128, 2
     bs, hs = shard(B, H, world, rank)
     xs = make_inputs("gdn2", B, T, H, seed=4, batches=bs, heads=hs)
     ins = {n: (x.double() if x is not None else None) for n, x in operator_inputs("gdn2", xs).items()}
@@ -76,3 +75,22 @@ def test_two_rank_shards_assemble_to_the_unsharded_gradients(tmp_path):
         h0, h1 = part["hs"][0], part["hs"][-1] + 1
         for n in ("dq", "dk", "dv", "dg", "db", "dw"):
             assert torch.allclose(part[n], full[n][b0:b1, :, h0:h1], atol=1e-12), n
+
+
+def test_head_split_shards_of_a_fixed_problem_assemble_to_the_unsharded_gradients(tmp_path):
+    """Fixed-problem (strong scaling) partition with more ranks than batch elements: both ranks own the one batch
+    element and half of its heads each; the per-rank gradients are the matching head slices of the full problem."""
+    from oracle import chunk_backward, chunk_forward
+    B, T, H = 1, 128, 4
+    assert shard(B, H, 2, 0) == ([0], [0, 1]) and shard(B, H, 2, 1) == ([0], [2, 3])
+    out = tmp_path / "gathered_heads.pt"
+    mp.spawn(_worker, args=(2, _free_port(), str(out), B, T, H), nprocs=2, join=True)
+    res = torch.load(out, weights_only=False)
+    xs = make_inputs("gdn2", B, T, H, seed=4)
+    ins = {n: (x.double() if x is not None else None) for n, x in operator_inputs("gdn2", xs).items()}
+    full = chunk_backward("gdn2", ins, chunk_forward("gdn2", ins), xs["do"], xs["dht"])
+    assert sorted(tuple(p["hs"]) for p in res["parts"]) == [(0, 1), (2, 3)]
+    for part in res["parts"]:
+        h0, h1 = part["hs"][0], part["hs"][-1] + 1
+        for n in ("dq", "dk", "dv", "dg", "db", "dw"):
+            assert torch.allclose(part[n], full[n][:, :, h0:h1], atol=1e-12), n
