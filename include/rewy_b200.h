@@ -13,7 +13,7 @@
  *   [B,T,H,64]     ((b*T + t)*H + h)*64 + j           Aqk, Akk: row t%64, column j of the chunk's 64x64 matrix
  *   [B,T,H]        (b*T + t)*H + h                    beta, scalar gate, dbeta
  *   [B,NT,H,K,V]   (((b*NT + n)*H + h)*128 + k)*128+v h, dh (NT = T/64)
- *   [B,H,K,V]      ((b*H + h)*128 + k)*128 + v        initial_state, dht, dh0
+ *   [B,H,K,V]      ((b*H + h)*128 + k)*128 + v        initial_state, dht, dh0 ([B,H,V,K] with state_v_first)
  * Gates are chunk-local inclusive cumulative sums in LOG2 units (FP32), as the forward saves them.
  */
 #ifndef REWY_B200_H
@@ -51,6 +51,9 @@ typedef struct RewyBwdArgs {
   int32_t out_dtype;   /* dtype of dq, dk (and db_gate, dw_gate): REWY_OUT_BF16 or REWY_OUT_F32 */
   int32_t intra_passes;/* 0 = default.  Option of chunk variant 1 (warp-MMA kernel) only: 1 or 3 BF16 split passes of
                           the matrix-intra products; the tensor-core kernel always runs 3 and refuses other values */
+  int32_t state_v_first; /* 0: h0, dht, dh0 are [B,H,K,V]; 1: they are [B,H,V,K] (FLA's state_v_first / transposed state
+                            layout).  The per-chunk states h and dh keep the [K,V] layout either way: they are produced and
+                            consumed inside this library (its own forward saves h). */
   float scale;
   /* inputs */
   const void* q;       /* bf16 [B,T,H,128] */
@@ -133,6 +136,34 @@ int rewy_stage_prepare(const RewyBwdArgs* args, const RewyStageBuffers* buf, rew
 int rewy_stage_fwd_scan(const RewyBwdArgs* args, const RewyStageBuffers* buf, rewy_stream_t stream);
 int rewy_stage_bwd_scan(const RewyBwdArgs* args, const RewyStageBuffers* buf, rewy_stream_t stream);
 int rewy_stage_chunk_adjoint(const RewyBwdArgs* args, const RewyStageBuffers* buf, rewy_stream_t stream);
+
+/* Element-wise stages of the autograd wrappers (one HBM pass each; rows = B*T*H rows of 128 values).
+ *   rewy_l2norm_fwd / _bwd       <- FLA l2norm_fwd / l2norm_bwd as used at src/fast_delta_rule/_compat/kda.py:56-59,202-204
+ *                                   (same in _compat/gdn.py, gdn2.py, delta.py).  x, y BF16 [rows,128]; rstd FP32 [rows];
+ *                                   dy BF16 or FP32 (the dq/dk of the family backward); dx BF16: the cast to the input
+ *                                   dtype (_compat/kda.py:208) is part of the same pass.
+ *   rewy_beta_sigmoid_fwd / _bwd <- fused_beta_sigmoid / fused_beta_sigmoid_bwd, _compat/kda.py:61-63,205-206.
+ *                                   x raw logits (BF16 or FP32) [n]; forward writes scale*sigmoid(x) as FP32 (y32) and/or
+ *                                   BF16 (y16; then y32 holds the BF16-rounded value); backward dx FP32 [n].
+ *   rewy_gate_cumsum_fwd         <- FLA chunk_local_cumsum(scale=RCP_LN2) and, with A_log != NULL, kda_gate_chunk_cumsum
+ *                                   (chunk_kda_fwd with use_gate_in_kernel, _compat/kda.py:89-113): the per-step gate
+ *                                   g = -exp(A_log[h]) * softplus(x + dt_bias[h*128+k]) (dt_bias may be NULL) is written to
+ *                                   g_act (optional) and its chunk-local inclusive cumulative sum in log2 units to g_cumsum.
+ *                                   x [B,T,H,128] BF16 or FP32; A_log FP32 [H]; dt_bias FP32 [H*128].
+ *   rewy_gate_act_bwd            <- FLA kda_gate_bwd (chunk_kda_bwd with use_gate_in_kernel): dg is the gradient of the
+ *                                   activated per-step gate; dx FP32 [B,T,H,128]; per-chunk partial sums
+ *                                   dA_part FP32 [B*T/64*H] and dbias_part FP32 [B*T/64*H*128] whose sums over the leading
+ *                                   (batch, chunk) index are dA_log[h] and ddt_bias[h*128+k]. */
+int rewy_l2norm_fwd(const void* x, void* y, float* rstd, int64_t rows, float eps, rewy_stream_t stream);
+int rewy_l2norm_bwd(const void* y, const float* rstd, const void* dy, int dy_is_f32, void* dx, int64_t rows,
+                    rewy_stream_t stream);
+int rewy_beta_sigmoid_fwd(const void* x, int x_is_f32, float* y32, void* y16, int64_t n, float scale, rewy_stream_t stream);
+int rewy_beta_sigmoid_bwd(const void* x, int x_is_f32, const float* dy, float* dx, int64_t n, float scale,
+                          rewy_stream_t stream);
+int rewy_gate_cumsum_fwd(const void* x, int x_is_f32, const float* A_log, const float* dt_bias, float* g_cumsum,
+                         float* g_act, int32_t B, int32_t T, int32_t H, rewy_stream_t stream);
+int rewy_gate_act_bwd(const void* x, int x_is_f32, const float* A_log, const float* dt_bias, const float* dg, float* dx,
+                      float* dA_part, float* dbias_part, int32_t B, int32_t T, int32_t H, rewy_stream_t stream);
 
 /* Optional per-stage device timing of the whole-family calls (no counterpart in the reference, which
  * times stages by re-capturing them: research/operators/a800_ablation/audit.py:38-47).  While enabled, each

@@ -22,6 +22,8 @@ EXPORTS = (
     "rewy_stage_timing_enable", "rewy_stage_timing_read", "rewy_selftest_tensor_core", "rewy_selftest_bounded_wait",
     "rewy_device_status", "rewy_wide_chunk_count", "rewy_set_chunk_variant", "rewy_set_scan_variant",
     "rewy_stage_chunk_adjoint_static", "rewy_static_device_status",
+    "rewy_l2norm_fwd", "rewy_l2norm_bwd", "rewy_beta_sigmoid_fwd", "rewy_beta_sigmoid_bwd", "rewy_gate_cumsum_fwd",
+    "rewy_gate_act_bwd",
     "rewy_last_error", "rewy_version", "rewy_kernel_launch_count",
 )
 
@@ -29,7 +31,7 @@ EXPORTS = (
 class BwdArgs(ctypes.Structure):
     _fields_ = [
         ("family", c_int32), ("policy", c_int32), ("B", c_int32), ("T", c_int32), ("H", c_int32),
-        ("out_dtype", c_int32), ("intra_passes", c_int32), ("scale", c_float),
+        ("out_dtype", c_int32), ("intra_passes", c_int32), ("state_v_first", c_int32), ("scale", c_float),
         ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("g", c_void_p), ("beta", c_void_p),
         ("b_gate", c_void_p), ("w_gate", c_void_p), ("Aqk", c_void_p), ("Akk", c_void_p), ("h0", c_void_p),
         ("d_o", c_void_p), ("dht", c_void_p),
@@ -78,6 +80,18 @@ def load():
     lib.rewy_stage_timing_read.restype = c_int
     lib.rewy_selftest_tensor_core.argtypes = [c_void_p] * 9
     lib.rewy_selftest_tensor_core.restype = c_int
+    i64 = ctypes.c_int64
+    lib.rewy_l2norm_fwd.argtypes = [c_void_p, c_void_p, c_void_p, i64, c_float, c_void_p]
+    lib.rewy_l2norm_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, i64, c_void_p]
+    lib.rewy_beta_sigmoid_fwd.argtypes = [c_void_p, c_int, c_void_p, c_void_p, i64, c_float, c_void_p]
+    lib.rewy_beta_sigmoid_bwd.argtypes = [c_void_p, c_int, c_void_p, c_void_p, i64, c_float, c_void_p]
+    lib.rewy_gate_cumsum_fwd.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
+                                         c_void_p]
+    lib.rewy_gate_act_bwd.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
+                                      c_int32, c_int32, c_void_p]
+    for name in ("rewy_l2norm_fwd", "rewy_l2norm_bwd", "rewy_beta_sigmoid_fwd", "rewy_beta_sigmoid_bwd",
+                 "rewy_gate_cumsum_fwd", "rewy_gate_act_bwd"):
+        getattr(lib, name).restype = c_int
     lib.rewy_selftest_bounded_wait.argtypes = [c_void_p, c_void_p, ctypes.c_uint32, c_int, c_void_p]
     lib.rewy_selftest_bounded_wait.restype = c_int
     lib.rewy_device_status.argtypes = [c_void_p, c_void_p]

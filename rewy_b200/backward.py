@@ -30,7 +30,7 @@ def _empty(dev):
 
 
 @torch.library.custom_op("rewy_b200::family_bwd", mutates_args=("workspace",), device_types="cuda")
-def _family_bwd(family: int, policy: int, out_f32: bool, intra_passes: int, scale: float,
+def _family_bwd(family: int, policy: int, out_f32: bool, intra_passes: int, state_v_first: bool, scale: float,
                 q: Tensor, k: Tensor, v: Tensor, d_o: Tensor, Akk: Tensor, workspace: Tensor,
                 g: Optional[Tensor], beta: Optional[Tensor], b_gate: Optional[Tensor], w_gate: Optional[Tensor],
                 Aqk: Optional[Tensor], h0: Optional[Tensor], dht: Optional[Tensor], w: Optional[Tensor],
@@ -57,6 +57,7 @@ def _family_bwd(family: int, policy: int, out_f32: bool, intra_passes: int, scal
     a.family, a.policy, a.B, a.T, a.H = family, policy, B, T, H
     a.out_dtype = _capi.OUT_F32 if out_f32 else _capi.OUT_BF16
     a.intra_passes = intra_passes
+    a.state_v_first = int(state_v_first)
     a.scale = scale
     for name, t in dict(q=q, k=k, v=v, d_o=d_o, Akk=Akk, g=g, beta=beta, b_gate=b_gate, w_gate=w_gate, Aqk=Aqk, h0=h0,
                         dht=dht, w=w, qg=qg, kg=kg, v_new=v_new, h=h).items():
@@ -75,16 +76,16 @@ def _family_bwd(family: int, policy: int, out_f32: bool, intra_passes: int, scal
 
 
 @_family_bwd.register_fake
-def _family_bwd_fake(family, policy, out_f32, intra_passes, scale, q, k, v, d_o, Akk, workspace, g, beta, b_gate, w_gate,
+def _family_bwd_fake(family, policy, out_f32, intra_passes, state_v_first, scale, q, k, v, d_o, Akk, workspace, g, beta, b_gate, w_gate,
                      Aqk, h0, dht, w, qg, kg, v_new, h):
     B, T, H, _ = k.shape
     odt = torch.float32 if out_f32 else torch.bfloat16
     big = lambda dt: q.new_empty((B, T, H, 128), dtype=dt)
-    none = q.new_empty(0, dtype=torch.float32)
+    none = lambda: q.new_empty(0, dtype=torch.float32)   # a fresh tensor each time: outputs must not alias each other
     vec = family == _capi.GDN2
-    return (big(odt), big(odt), big(torch.bfloat16), torch.empty_like(g) if g is not None else none,
-            q.new_empty((B, T, H), dtype=torch.float32) if not vec else none, big(odt) if vec else none,
-            big(odt) if vec else none, q.new_empty((B, H, 128, 128), dtype=torch.float32) if h0 is not None else none)
+    return (big(odt), big(odt), big(torch.bfloat16), torch.empty_like(g) if g is not None else none(),
+            q.new_empty((B, T, H), dtype=torch.float32) if not vec else none(), big(odt) if vec else none(),
+            big(odt) if vec else none(), q.new_empty((B, H, 128, 128), dtype=torch.float32) if h0 is not None else none())
 
 
 def _unsupported(name, value, allowed=(None, False)):
@@ -106,8 +107,7 @@ def _check_common(q, k, v, do, chunk_size, cu_seqlens, cp_context, state_v_first
         raise RuntimeError("rewy_b200 backward: chunk_size must be 64")
     _unsupported("cu_seqlens", cu_seqlens, (None,))
     _unsupported("cp_context", cp_context, (None,))
-    _unsupported("state_v_first", state_v_first)
-    _unsupported("use_gate_in_kernel", use_gate_in_kernel)
+    _unsupported("use_gate_in_kernel", use_gate_in_kernel)   # the gate activation is a wrapper stage (elementwise.py)
     if do.shape != v.shape:
         raise RuntimeError("rewy_b200 backward: do must have the shape of v")
     return B, T, H
@@ -122,7 +122,7 @@ def _c(t, dtype=None):
 
 
 def _run(family, policy, B, T, H, scale, tensors, out_dtype, intra_passes, workspace, want_dg, want_dbeta, vector_gates,
-         check_status=False):
+         check_status=False, state_v_first=False):
     """tensors: dict name -> tensor or None for every input pointer of RewyBwdArgs."""
     lib = _capi.load()
     dev = tensors["q"].device
@@ -136,7 +136,7 @@ def _run(family, policy, B, T, H, scale, tensors, out_dtype, intra_passes, works
         raise RuntimeError(f"rewy_b200 backward: workspace must hold {need} bytes on {dev}")
     t = tensors
     r = torch.ops.rewy_b200.family_bwd(
-        family, policy, out_f32, int(intra_passes or 0), float(scale), t["q"], t["k"], t["v"], t["d_o"], t["Akk"],
+        family, policy, out_f32, int(intra_passes or 0), bool(state_v_first), float(scale), t["q"], t["k"], t["v"], t["d_o"], t["Akk"],
         workspace, t["g"], t["beta"], t["b_gate"], t["w_gate"], t["Aqk"], t["h0"], t["dht"], t["w"], t["qg"], t["kg"],
         t["v_new"], t["h"])
     names = ("dq", "dk", "dv", "dg", "dbeta", "db_gate", "dw_gate", "dh0")
@@ -169,7 +169,7 @@ def kda_backward(q, k, v, beta, Aqk, Akk, scale, initial_state, do, dht, g=None,
         kg=_c(kg, torch.bfloat16) if saved else None, v_new=_c(v_new, torch.bfloat16) if saved else None,
         h=_c(h, torch.bfloat16) if saved else None)
     out = _run(_capi.KDA, _capi.SAVED if saved else _capi.RECOMPUTE, B, T, H, scale, tensors, out_dtype,
-               intra_passes, workspace, True, True, False, check_status)
+               intra_passes, workspace, True, True, False, check_status, state_v_first)
     record("kda", "optimized_backward")
     return out["dq"], out["dk"], out["dv"], out["dbeta"], out["dg"], out["dh0"], None, None
 
@@ -193,7 +193,7 @@ def gdn2_backward(q, k, v, b, w_gate, Aqk, Akk, scale, initial_state, do, dht, g
         kg=_c(kg, torch.bfloat16) if saved else None, v_new=_c(v_new, torch.bfloat16) if saved else None,
         h=_c(h, torch.bfloat16) if saved else None)
     out = _run(_capi.GDN2, _capi.SAVED if saved else _capi.RECOMPUTE, B, T, H, scale, tensors, out_dtype,
-               intra_passes, workspace, True, False, True, check_status)
+               intra_passes, workspace, True, False, True, check_status, state_v_first)
     record("gdn2", "optimized_backward")
     return out["dq"], out["dk"], out["dv"], out["db_gate"], out["dw_gate"], out["dg"], out["dh0"], None, None
 
@@ -209,7 +209,7 @@ def gdn_backward(q, k, v, g, beta, A, scale, initial_state, do, dht, cu_seqlens=
         Aqk=None, Akk=_c(A, torch.bfloat16), h0=_c(initial_state, torch.float32), d_o=_c(do, torch.bfloat16),
         dht=_c(dht, torch.float32), w=None, qg=None, kg=None, v_new=None, h=None)
     out = _run(_capi.GDN, _capi.RECOMPUTE, B, T, H, scale, tensors, out_dtype, intra_passes, workspace,
-               True, True, False, check_status)
+               True, True, False, check_status, state_v_first)
     record("gdn", "optimized_backward")
     return out["dq"], out["dk"], out["dv"], out["dbeta"], out["dg"], out["dh0"], None, None
 

@@ -61,6 +61,7 @@ bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) !=
   } while (0)
 
 std::atomic<int> g_chunk_variant{0};  // 0 = tensor-core kernel (+ pairwise list), 1 = warp-MMA kernel everywhere
+std::atomic<int> g_scan_variant{0};   // 0 = tensor-core scans, 1 = warp-MMA scans
 
 // intra_passes is an option of the warp-MMA chunk kernel (1 or 3 split passes); the tensor-core kernel always runs 3.
 int rc_passes(int passes) {
@@ -77,6 +78,9 @@ int validate_common(const RewyBwdArgs* a, int family) {
   if (a->out_dtype != REWY_OUT_BF16 && a->out_dtype != REWY_OUT_F32)
     return fail(REWY_ERR_UNSUPPORTED, "unknown out_dtype%s");
   if ((rc_passes(a->intra_passes)) != REWY_OK) return REWY_ERR_UNSUPPORTED;
+  if (a->state_v_first != 0 && a->state_v_first != 1) return fail(REWY_ERR_UNSUPPORTED, "state_v_first must be 0 or 1%s");
+  if (a->state_v_first && g_scan_variant.load(std::memory_order_relaxed) == 1)
+    return fail(REWY_ERR_UNSUPPORTED, "the warp-MMA scan variant reads [K,V] states only (state_v_first)%s");
   if (a->B <= 0 || a->H <= 0) return fail(REWY_ERR_SHAPE, "B and H must be positive%s");
   if (a->T < C || a->T % C != 0) return fail(REWY_ERR_SHAPE, "T must be a positive multiple of 64 (got %s%lld)", "", a->T);
   if ((long long)a->B * a->H > 65535) return fail(REWY_ERR_SHAPE, "B*H exceeds the grid limit 65535%s");
@@ -119,8 +123,6 @@ void timing_mark(int set, int idx, cudaStream_t st) {
   cudaEventRecord(g_timing.ev[set][idx], st);
   g_timing.have[set][idx] = true;
 }
-
-std::atomic<int> g_scan_variant{0};   // 0 = tensor-core reverse scan, 1 = warp-MMA reverse scan
 
 cudaError_t run_fwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
   if (g_scan_variant.load(std::memory_order_relaxed) == 1 || s.ctrl == nullptr) return launch_fwd_scan(a, s, st);

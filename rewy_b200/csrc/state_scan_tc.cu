@@ -22,6 +22,7 @@ struct ScanParams {
   float* dh0;
   int* err;
   int T, H, NT;
+  int svf;  // initial / final state tensors (dht, dh0) are stored value-first: [B,H,V,K]
   float scale;
 };
 
@@ -160,15 +161,23 @@ bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_consta
     issue_do(NT - 1);
   }
 
-  // initial state S' = dht / scale
+  // initial state S' = dht / scale (element (k, v) at k*128 + v, or at v*128 + k in the value-first layout)
   {
-    const float* src = p.dht == nullptr ? nullptr : p.dht + (size_t)bh * DK * DV + (size_t)ch * DV + 64 * wg;
+    const float* st0 = p.dht == nullptr ? nullptr : p.dht + (size_t)bh * DK * DV;
 #pragma unroll
     for (int c = 0; c < 4; c++) {
       float x[16];
 #pragma unroll
       for (int j = 0; j < 16; j += 4) {
-        float4 v4 = src == nullptr ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(src + 16 * c + j);
+        float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int v0 = 64 * wg + 16 * c + j;
+        if (st0 != nullptr) {
+          if (p.svf)
+            v4 = make_float4(st0[(size_t)v0 * DK + ch], st0[(size_t)(v0 + 1) * DK + ch], st0[(size_t)(v0 + 2) * DK + ch],
+                             st0[(size_t)(v0 + 3) * DK + ch]);
+          else
+            v4 = *reinterpret_cast<const float4*>(st0 + (size_t)ch * DV + v0);
+        }
         x[j] = v4.x * inv_scale; x[j + 1] = v4.y * inv_scale; x[j + 2] = v4.z * inv_scale; x[j + 3] = v4.w * inv_scale;
       }
       tmem_st16f(tlane + TM_S + 64 * wg + 16 * c, x);
@@ -316,16 +325,22 @@ bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_consta
   wait(B_S, 6);
   tc_fence_after_sync();
   if (p.dh0 != nullptr && alive) {
-    float* dst = p.dh0 + (size_t)bh * DK * DV + (size_t)ch * DV + 64 * wg;
+    float* dst = p.dh0 + (size_t)bh * DK * DV;
 #pragma unroll
     for (int c = 0; c < 4; c++) {
       float x[16];
       tmem_ld16f(tlane + TM_S + 64 * wg + 16 * c, x);
       tmem_ld_wait();
+      const int v0 = 64 * wg + 16 * c;
+      if (p.svf) {
 #pragma unroll
-      for (int j = 0; j < 16; j += 4)
-        *reinterpret_cast<float4*>(dst + 16 * c + j) =
-            make_float4(scale * x[j], scale * x[j + 1], scale * x[j + 2], scale * x[j + 3]);
+        for (int j = 0; j < 16; j++) dst[(size_t)(v0 + j) * DK + ch] = scale * x[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<float4*>(dst + (size_t)ch * DV + v0 + j) =
+              make_float4(scale * x[j], scale * x[j + 1], scale * x[j + 2], scale * x[j + 3]);
+      }
     }
   }
   if (tid == 0) bulk_wait0();
@@ -345,6 +360,7 @@ struct FwdParams {
   bf16* v_new;
   int* err;
   int T, H, NT;
+  int svf;  // h0 is stored value-first: [B,H,V,K]
 };
 struct FS {
   static constexpr uint32_t W = 0;                // [64 i][128 k] two panels   16 KB
@@ -404,14 +420,22 @@ fwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     load2(FS::U, &tmU, 0, F_U);
     load2(FS::KG, &tmKg, 0, F_KG);
   }
-  {  // initial state
-    const float* src = p.h0 == nullptr ? nullptr : p.h0 + (size_t)bh * DK * DV + (size_t)ch * DV + 64 * wg;
+  {  // initial state (element (k, v) at k*128 + v, or at v*128 + k in the value-first layout)
+    const float* st0 = p.h0 == nullptr ? nullptr : p.h0 + (size_t)bh * DK * DV;
 #pragma unroll
     for (int c = 0; c < 4; c++) {
       float x[16];
 #pragma unroll
       for (int j = 0; j < 16; j += 4) {
-        float4 v4 = src == nullptr ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(src + 16 * c + j);
+        float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int v0 = 64 * wg + 16 * c + j;
+        if (st0 != nullptr) {
+          if (p.svf)
+            v4 = make_float4(st0[(size_t)v0 * DK + ch], st0[(size_t)(v0 + 1) * DK + ch], st0[(size_t)(v0 + 2) * DK + ch],
+                             st0[(size_t)(v0 + 3) * DK + ch]);
+          else
+            v4 = *reinterpret_cast<const float4*>(st0 + (size_t)ch * DV + v0);
+        }
         x[j] = v4.x; x[j + 1] = v4.y; x[j + 2] = v4.z; x[j + 3] = v4.w;
       }
       tmem_st16f(tlane + TMF_S + 64 * wg + 16 * c, x);
@@ -577,7 +601,7 @@ cudaError_t launch_bwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, 
   if (!ok) return cudaErrorInvalidValue;
   ScanParams p;
   p.g = a.g; p.dht = a.dht; p.dR = (bf16*)s.dR; p.dRlo = (bf16*)s.dR_lo; p.dh0 = a.dh0; p.err = err;
-  p.T = T; p.H = H; p.NT = NT; p.scale = a.scale;
+  p.T = T; p.H = H; p.NT = NT; p.svf = a.state_v_first; p.scale = a.scale;
   switch (gate_mode_of(a.family)) {
     case GATE_NONE: return run<GATE_NONE>(tm, p, B * H, st);
     case GATE_SCALAR: return run<GATE_SCALAR>(tm, p, B * H, st);
@@ -596,7 +620,7 @@ cudaError_t launch_fwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, 
             encode_tmap_2d(&tm[3], s.h, 2, 128, srows, 256, 64, 128);
   if (!ok) return cudaErrorInvalidValue;
   FwdParams p;
-  p.g = a.g; p.h0 = a.h0; p.v_new = (bf16*)s.v_new; p.err = err; p.T = T; p.H = H; p.NT = NT;
+  p.g = a.g; p.h0 = a.h0; p.v_new = (bf16*)s.v_new; p.err = err; p.T = T; p.H = H; p.NT = NT; p.svf = a.state_v_first;
   switch (gate_mode_of(a.family)) {
     case GATE_NONE: return run_fwd<GATE_NONE>(tm, p, B * H, st);
     case GATE_SCALAR: return run_fwd<GATE_SCALAR>(tm, p, B * H, st);

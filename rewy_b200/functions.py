@@ -3,7 +3,9 @@
 Same contracts as the reference's private autograd copies (src/fast_delta_rule/_compat/kda.py:23-210,
 gdn.py:128-267, gdn2.py:43-201, delta.py:19-141): the forward saves FLA's tensor set (policy
 ``disable_recompute`` decides whether w,u,qg,kg,v_new,h are kept), the backward hands them to the
-whole-family backward of ``rewy_b200.backward`` and casts to the input dtypes.  The backward stays bound
+whole-family backward of ``rewy_b200.backward`` and casts to the input dtypes.  The wrapper-level options the
+reference accepts for KDA on CUDA (fused gate activation, beta sigmoid, q/k L2 normalisation, value-first state
+layout: docs/compatibility.md:12-13, tests/test_accelerator.py:65-83) run as CUDA passes of ``rewy_b200.elementwise``.  The backward stays bound
 to this implementation after a ``use_backend`` context exits, like the reference's.
 """
 import torch
@@ -12,124 +14,132 @@ from . import backward as _bwd
 from .forward import chunk_forward
 
 
-def _l2norm_fwd(x, eps=1e-6):
-    xf = x.float()
-    rstd = torch.rsqrt(xf.pow(2).sum(-1, keepdim=True) + eps)
-    return (xf * rstd).to(x.dtype), rstd
+from . import elementwise as _ew
 
 
-def _l2norm_bwd(y, rstd, dy):
-    yf, dyf = y.float(), dy.float()
-    return (dyf * rstd - (dyf * yf).sum(-1, keepdim=True) * yf * rstd)
+def _vfirst(t, state_v_first):
+    """[B,H,V,K] <-> [B,H,K,V] view change for the torch forward (the CUDA backward reads either layout itself)."""
+    return t if (t is None or not state_v_first) else t.transpose(-1, -2).contiguous()
 
 
-def _sigmoid_bwd(x, dy, scale):
-    s = torch.sigmoid(x.float())
-    return dy.float() * scale * s * (1 - s)
+def _cumulative_gate(g, A_log=None, dt_bias=None):
+    """Chunk-local cumulative gate in log2 units on the device (vector gates), optionally with the KDA gate activation."""
+    return _ew.gate_cumsum_fwd(g, A_log, dt_bias)
 
 
 class ChunkKDAFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
-                use_beta_sigmoid_in_kernel, allow_neg_eigval, disable_recompute):
+    def forward(ctx, q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
+                use_gate_in_kernel, use_beta_sigmoid_in_kernel, allow_neg_eigval, disable_recompute, state_v_first):
         q_rstd = k_rstd = None
         if use_qk_l2norm_in_kernel:
-            q, q_rstd = _l2norm_fwd(q)
-            k, k_rstd = _l2norm_fwd(k)
+            q, q_rstd = _ew.l2norm_fwd(q)
+            k, k_rstd = _ew.l2norm_fwd(k)
         beta_raw = beta
         if use_beta_sigmoid_in_kernel:
-            beta = (torch.sigmoid(beta_raw.float()) * (2.0 if allow_neg_eigval else 1.0)).to(beta_raw.dtype)
-        f = chunk_forward("kda", q, k, v, g=g, beta=beta, scale=scale, initial_state=initial_state,
-                          output_final_state=output_final_state)
+            beta = _ew.beta_sigmoid_fwd(beta_raw, 2.0 if allow_neg_eigval else 1.0)
+        # with use_gate_in_kernel, g is the raw gate input: -exp(A_log) * softplus(g + dt_bias) and the chunk cumsum are
+        # one pass; otherwise g is the per-step natural-log decay
+        g_cumsum = _cumulative_gate(g, A_log if use_gate_in_kernel else None, dt_bias if use_gate_in_kernel else None)
+        f = chunk_forward("kda", q, k, v, g=g_cumsum, beta=beta, scale=scale, initial_state=_vfirst(initial_state, state_v_first),
+                          output_final_state=output_final_state, g_is_cumsum=True)
         keep = (lambda x: x) if disable_recompute else (lambda x: None)
-        ctx.save_for_backward(q, q_rstd, k, k_rstd, v, f["g_cumsum"], g, beta_raw, beta, f["Aqk"], f["Akk"],
+        ctx.save_for_backward(q, q_rstd, k, k_rstd, v, g_cumsum, g, beta_raw, beta, A_log, dt_bias, f["Aqk"], f["Akk"],
                               keep(f["w"]), keep(f["u"]), keep(f["qg"]), keep(f["kg"]), keep(f["v_new"]),
                               keep(f["h"]), initial_state)
         ctx.scale, ctx.disable_recompute = scale, disable_recompute
         ctx.use_qk_l2norm_in_kernel, ctx.use_beta_sigmoid_in_kernel = use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel
-        ctx.allow_neg_eigval = allow_neg_eigval
-        return f["o"].type_as(q), f["final_state"]
+        ctx.use_gate_in_kernel, ctx.allow_neg_eigval, ctx.state_v_first = use_gate_in_kernel, allow_neg_eigval, state_v_first
+        return f["o"].type_as(q), _vfirst(f["final_state"], state_v_first)
 
     @staticmethod
     def backward(ctx, do, dht):
-        (q, q_rstd, k, k_rstd, v, g_cumsum, g_input, beta_raw, beta, Aqk, Akk, w, u, qg, kg, v_new, h,
+        (q, q_rstd, k, k_rstd, v, g_cumsum, g_input, beta_raw, beta, A_log, dt_bias, Aqk, Akk, w, u, qg, kg, v_new, h,
          initial_state) = ctx.saved_tensors
-        fuse_cast = not ctx.use_qk_l2norm_in_kernel
         dq, dk, dv, db, dg, dh0, _, _ = _bwd.kda_backward(
             q=q, k=k, v=v, beta=beta, Aqk=Aqk, Akk=Akk, scale=ctx.scale, initial_state=initial_state, do=do, dht=dht,
-            g=g_cumsum, disable_recompute=ctx.disable_recompute, w=w, u=u, qg=qg, kg=kg, v_new=v_new, h=h,
-            out_dtype=torch.bfloat16 if fuse_cast else torch.float32)
+            g=g_cumsum, state_v_first=ctx.state_v_first, disable_recompute=ctx.disable_recompute, w=w, u=u, qg=qg, kg=kg,
+            v_new=v_new, h=h, out_dtype=torch.float32 if ctx.use_qk_l2norm_in_kernel else torch.bfloat16)
+        dA = dbias = None
+        if ctx.use_gate_in_kernel:
+            dg, dA, dbias = _ew.gate_act_bwd(g_input, A_log, dt_bias, dg)
+            dA = dA.view_as(A_log).to(A_log.dtype)
+            dbias = None if dbias is None else dbias.view_as(dt_bias).to(dt_bias.dtype)
         if ctx.use_qk_l2norm_in_kernel:
-            dq = _l2norm_bwd(q, q_rstd, dq)
-            dk = _l2norm_bwd(k, k_rstd, dk)
+            dq = _ew.l2norm_bwd(q, q_rstd, dq)
+            dk = _ew.l2norm_bwd(k, k_rstd, dk)
         if ctx.use_beta_sigmoid_in_kernel:
-            db = _sigmoid_bwd(beta_raw, db, 2.0 if ctx.allow_neg_eigval else 1.0)
-        return (dq.to(q), dk.to(k), dv.to(v), dg.to(g_input), db.to(beta_raw), None, dh0, None, None, None, None, None)
+            db = _ew.beta_sigmoid_bwd(beta_raw, db, 2.0 if ctx.allow_neg_eigval else 1.0)
+        return (dq.to(q), dk.to(k), dv.to(v), dg.to(g_input), db.to(beta_raw), dA, dbias, None, dh0, None, None, None,
+                None, None, None, None)
 
 
 class ChunkGDN2Function(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, b, w, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
-                disable_recompute):
+                disable_recompute, state_v_first):
         q_rstd = k_rstd = None
         if use_qk_l2norm_in_kernel:
-            q, q_rstd = _l2norm_fwd(q)
-            k, k_rstd = _l2norm_fwd(k)
-        f = chunk_forward("gdn2", q, k, v, g=g, b=b, w=w, scale=scale, initial_state=initial_state,
-                          output_final_state=output_final_state)
+            q, q_rstd = _ew.l2norm_fwd(q)
+            k, k_rstd = _ew.l2norm_fwd(k)
+        g_cumsum = _cumulative_gate(g)
+        f = chunk_forward("gdn2", q, k, v, g=g_cumsum, b=b, w=w, scale=scale, initial_state=_vfirst(initial_state, state_v_first),
+                          output_final_state=output_final_state, g_is_cumsum=True)
         keep = (lambda x: x) if disable_recompute else (lambda x: None)
-        ctx.save_for_backward(q, q_rstd, k, k_rstd, v, f["g_cumsum"], g, b, w, f["Aqk"], f["Akk"], keep(f["w"]),
+        ctx.save_for_backward(q, q_rstd, k, k_rstd, v, g_cumsum, g, b, w, f["Aqk"], f["Akk"], keep(f["w"]),
                               keep(f["u"]), keep(f["qg"]), keep(f["kg"]), keep(f["v_new"]), keep(f["h"]), initial_state)
         ctx.scale, ctx.disable_recompute, ctx.use_qk_l2norm_in_kernel = scale, disable_recompute, use_qk_l2norm_in_kernel
-        return f["o"].type_as(q), f["final_state"]
+        ctx.state_v_first = state_v_first
+        return f["o"].type_as(q), _vfirst(f["final_state"], state_v_first)
 
     @staticmethod
     def backward(ctx, do, dht):
         (q, q_rstd, k, k_rstd, v, g_cumsum, g_input, b, w, Aqk, Akk, w_wy, u_wy, qg, kg, v_new, h,
          initial_state) = ctx.saved_tensors
-        fuse_cast = not ctx.use_qk_l2norm_in_kernel
         dq, dk, dv, db, dw, dg, dh0, _, _ = _bwd.gdn2_backward(
             q=q, k=k, v=v, b=b, w_gate=w, Aqk=Aqk, Akk=Akk, scale=ctx.scale, initial_state=initial_state, do=do,
-            dht=dht, g=g_cumsum, w_wy=w_wy, u_wy=u_wy, qg=qg, kg=kg, v_new=v_new, h=h,
-            disable_recompute=ctx.disable_recompute, out_dtype=torch.bfloat16 if fuse_cast else torch.float32)
+            dht=dht, g=g_cumsum, state_v_first=ctx.state_v_first, w_wy=w_wy, u_wy=u_wy, qg=qg, kg=kg, v_new=v_new, h=h,
+            disable_recompute=ctx.disable_recompute,
+            out_dtype=torch.float32 if ctx.use_qk_l2norm_in_kernel else torch.bfloat16)
         if ctx.use_qk_l2norm_in_kernel:
-            dq = _l2norm_bwd(q, q_rstd, dq)
-            dk = _l2norm_bwd(k, k_rstd, dk)
+            dq = _ew.l2norm_bwd(q, q_rstd, dq)
+            dk = _ew.l2norm_bwd(k, k_rstd, dk)
         return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg.to(g_input.dtype), db.to(b.dtype), dw.to(w.dtype),
-                None, dh0, None, None, None)
+                None, dh0, None, None, None, None)
 
 
 class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
-                use_beta_sigmoid_in_kernel, allow_neg_eigval):
+                use_beta_sigmoid_in_kernel, allow_neg_eigval, state_v_first):
         q_rstd = k_rstd = None
         if use_qk_l2norm_in_kernel:
-            q, q_rstd = _l2norm_fwd(q)
-            k, k_rstd = _l2norm_fwd(k)
+            q, q_rstd = _ew.l2norm_fwd(q)
+            k, k_rstd = _ew.l2norm_fwd(k)
         beta_raw = beta
         if use_beta_sigmoid_in_kernel:
-            beta = (torch.sigmoid(beta_raw.float()) * (2.0 if allow_neg_eigval else 1.0)).to(beta_raw.dtype)
-        f = chunk_forward("gdn", q, k, v, g=g, beta=beta, scale=scale, initial_state=initial_state,
+            beta = _ew.beta_sigmoid_fwd(beta_raw, 2.0 if allow_neg_eigval else 1.0)
+        f = chunk_forward("gdn", q, k, v, g=g, beta=beta, scale=scale, initial_state=_vfirst(initial_state, state_v_first),
                           output_final_state=output_final_state)
         ctx.save_for_backward(q, q_rstd, k, k_rstd, v, f["g_cumsum"], g, beta_raw, beta, f["Akk"], initial_state)
         ctx.scale, ctx.use_qk_l2norm_in_kernel = scale, use_qk_l2norm_in_kernel
         ctx.use_beta_sigmoid_in_kernel, ctx.allow_neg_eigval = use_beta_sigmoid_in_kernel, allow_neg_eigval
-        return f["o"].to(q.dtype), f["final_state"]
+        ctx.state_v_first = state_v_first
+        return f["o"].to(q.dtype), _vfirst(f["final_state"], state_v_first)
 
     @staticmethod
     def backward(ctx, do, dht):
         q, q_rstd, k, k_rstd, v, g, g_input, beta_raw, beta, A, initial_state = ctx.saved_tensors
-        fuse_cast = not ctx.use_qk_l2norm_in_kernel
         dq, dk, dv, db, dg, dh0, _, _ = _bwd.gdn_backward(
             q=q, k=k, v=v, g=g, beta=beta, A=A, scale=ctx.scale, initial_state=initial_state, do=do, dht=dht,
-            out_dtype=torch.bfloat16 if fuse_cast else torch.float32)
+            state_v_first=ctx.state_v_first,
+            out_dtype=torch.float32 if ctx.use_qk_l2norm_in_kernel else torch.bfloat16)
         if ctx.use_qk_l2norm_in_kernel:
-            dq = _l2norm_bwd(q, q_rstd, dq)
-            dk = _l2norm_bwd(k, k_rstd, dk)
+            dq = _ew.l2norm_bwd(q, q_rstd, dq)
+            dk = _ew.l2norm_bwd(k, k_rstd, dk)
         if ctx.use_beta_sigmoid_in_kernel:
-            db = _sigmoid_bwd(beta_raw, db, 2.0 if ctx.allow_neg_eigval else 1.0)
-        return (dq.to(q), dk.to(k), dv.to(v), dg.to(g_input), db.to(beta_raw), None, dh0, None, None, None, None)
+            db = _ew.beta_sigmoid_bwd(beta_raw, db, 2.0 if ctx.allow_neg_eigval else 1.0)
+        return (dq.to(q), dk.to(k), dv.to(v), dg.to(g_input), db.to(beta_raw), None, dh0, None, None, None, None, None)
 
 
 class ChunkDeltaRuleFunction(torch.autograd.Function):
@@ -137,8 +147,8 @@ class ChunkDeltaRuleFunction(torch.autograd.Function):
     def forward(ctx, q, k, v, beta, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel):
         q_rstd = k_rstd = None
         if use_qk_l2norm_in_kernel:
-            q, q_rstd = _l2norm_fwd(q)
-            k, k_rstd = _l2norm_fwd(k)
+            q, q_rstd = _ew.l2norm_fwd(q)
+            k, k_rstd = _ew.l2norm_fwd(k)
         f = chunk_forward("delta", q, k, v, beta=beta, scale=scale, initial_state=initial_state,
                           output_final_state=output_final_state)
         ctx.save_for_backward(q, q_rstd, k, k_rstd, v, beta, f["Akk"], initial_state)
@@ -148,13 +158,12 @@ class ChunkDeltaRuleFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, dht):
         q, q_rstd, k, k_rstd, v, beta, A, initial_state = ctx.saved_tensors
-        fuse_cast = not ctx.use_qk_l2norm_in_kernel
         dq, dk, dv, db, dh0 = _bwd.delta_backward(
             q=q, k=k, v=v, beta=beta, A=A, scale=ctx.scale, initial_state=initial_state, do=do, dht=dht,
-            out_dtype=torch.bfloat16 if fuse_cast else torch.float32)
+            out_dtype=torch.float32 if ctx.use_qk_l2norm_in_kernel else torch.bfloat16)
         if ctx.use_qk_l2norm_in_kernel:
-            dq = _l2norm_bwd(q, q_rstd, dq)
-            dk = _l2norm_bwd(k, k_rstd, dk)
+            dq = _ew.l2norm_bwd(q, q_rstd, dq)
+            dk = _ew.l2norm_bwd(k, k_rstd, dk)
         return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), db.to(beta.dtype), None, dh0, None, None
 
 
@@ -172,14 +181,22 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
               return_intermediate_states=False, state_v_first=False, cu_seqlens=None, cu_seqlens_cpu=None,
               cp_context=None, use_graph=False, max_num_seqs=None, **kwargs):
     """KDA (per-channel gated delta rule).  q,k [B,T,H,128] BF16, v [B,T,H,128], g [B,T,H,128] per-step
-    natural-log decay, beta [B,T,H].  Returns (o, final_state)."""
+    natural-log decay (or, with ``use_gate_in_kernel``, the raw gate input together with ``A_log`` [H] and the optional
+    ``dt_bias`` [H*128] keyword arguments), beta [B,T,H].  Returns (o, final_state)."""
     _common_checks(q, k, v, initial_state)
     if allow_neg_eigval and not use_beta_sigmoid_in_kernel:
         raise ValueError("`allow_neg_eigval=True` requires `use_beta_sigmoid_in_kernel=True`.")
+    A_log, dt_bias = kwargs.get("A_log"), kwargs.get("dt_bias")
+    if use_gate_in_kernel:
+        if A_log is None:
+            raise ValueError("A_log must be provided when use_gate_in_kernel=True.")
+        if lower_bound is not None:
+            raise ValueError("rewy_b200 chunk_kda: the lower_bound gate law belongs to safe_gate, which is not supported")
     if scale is None:
         scale = k.shape[-1] ** -0.5
-    return ChunkKDAFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
-                                  use_beta_sigmoid_in_kernel, allow_neg_eigval, disable_recompute)
+    return ChunkKDAFunction.apply(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state,
+                                  use_qk_l2norm_in_kernel, use_gate_in_kernel, use_beta_sigmoid_in_kernel, allow_neg_eigval,
+                                  disable_recompute, state_v_first)
 
 
 @torch.compiler.disable
@@ -192,7 +209,7 @@ def chunk_gdn2(q, k, v, g, b, w, scale=None, initial_state=None, output_final_st
     if scale is None:
         scale = k.shape[-1] ** -0.5
     return ChunkGDN2Function.apply(q, k, v, g, b, w, scale, initial_state, output_final_state,
-                                   use_qk_l2norm_in_kernel, disable_recompute)
+                                   use_qk_l2norm_in_kernel, disable_recompute, state_v_first)
 
 
 @torch.compiler.disable
@@ -205,7 +222,8 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
     if scale is None:
         scale = k.shape[-1] ** -0.5
     return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state,
-                                             use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel, allow_neg_eigval)
+                                             use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel, allow_neg_eigval,
+                                             state_v_first)
 
 
 @torch.compiler.disable

@@ -119,10 +119,10 @@ def rejection_reason(op, arguments, device_types=("cuda",)):
     scale = arguments.get("scale")
     if scale is not None and scale != k.shape[-1] ** -0.5:
         return "custom scale is not release-validated"
-    if arguments.get("use_gate_in_kernel", False):
-        return "fused gate activation is not supported"
-    if arguments.get("state_v_first", False):
-        return "value-first state layout is not supported"
+    if op == "gdn" and arguments.get("use_gate_in_kernel", False):
+        return "GDN fused gate is not release-validated"
+    if op == "gdn2" and arguments.get("use_gate_in_kernel", False):
+        return "GDN2 fused gate is not release-validated"
     if op == "delta" and arguments.get("head_first", False):
         return "head-first layout is not supported"
     return None

@@ -459,7 +459,7 @@ def test_custom_op_passes_opcheck():
     xs = _inputs("kda", T=128, H=2, seed=2)
     saved = forward_saved("kda", xs)
     ws = torch.empty(_capi.workspace_bytes(_capi.KDA, _capi.RECOMPUTE, 1, 128, 2), dtype=torch.uint8, device=DEV)
-    args = (_capi.KDA, _capi.RECOMPUTE, True, 0, 128 ** -0.5, xs["q"], xs["k"], xs["v"], xs["do"], saved["Akk"], ws,
+    args = (_capi.KDA, _capi.RECOMPUTE, True, 0, False, 128 ** -0.5, xs["q"], xs["k"], xs["v"], xs["do"], saved["Akk"], ws,
             saved["g_cumsum"], xs["beta"].float(), None, None, saved["Aqk"], xs["initial_state"], xs["dht"],
             None, None, None, None, None)
     torch.library.opcheck(torch.ops.rewy_b200.family_bwd.default, args,

@@ -61,7 +61,6 @@ def test_assert_used_reports_missing_backward():
     (lambda a: a.update(cu_seqlens=torch.tensor([0, 128])), "packed/variable"),
     (lambda a: a.update(scale=0.5), "custom scale"),
     (lambda a: a.update(safe_gate=True), "safe_gate"),
-    (lambda a: a.update(use_gate_in_kernel=True), "fused gate"),
     (lambda a: a.update(v=a["v"][..., :64]), "K=V=128"),
 ])
 def test_rejection_envelope(mutate, reason):
@@ -72,6 +71,18 @@ def test_rejection_envelope(mutate, reason):
     mutate(args)
     got = rejection_reason("kda", args, device_types=("cpu",))
     assert got is not None and reason in got, got
+
+
+def test_fused_gate_and_value_first_states_follow_the_reference_envelope():
+    """KDA accepts the fused gate activation and the value-first state layout (docs/compatibility.md:12-13 of the
+    reference); GDN and GDN2 reject the fused gate with the reference's wording (runtime.py:103-104)."""
+    from rewy_b200.runtime import rejection_reason
+    t = torch.zeros(1, 128, 2, 128, dtype=torch.bfloat16)
+    args = dict(q=t, k=t, v=t, use_gate_in_kernel=True, state_v_first=True)
+    assert rejection_reason("kda", args, device_types=("cpu",)) is None
+    assert rejection_reason("gdn", args, device_types=("cpu",)) == "GDN fused gate is not release-validated"
+    assert rejection_reason("gdn2", args, device_types=("cpu",)) == "GDN2 fused gate is not release-validated"
+    assert rejection_reason("gdn", dict(q=t, k=t, v=t, state_v_first=True), device_types=("cpu",)) is None
 
 
 def test_rejection_on_cpu_tensors_is_device():
@@ -258,11 +269,11 @@ def test_custom_op_is_registered_with_a_shape_only_implementation():
     ws = m(1024, dt=torch.uint8)
     g = m(B, T, H, 128, dt=torch.float32)
     h0 = m(B, H, 128, 128, dt=torch.float32)
-    r = backward._family_bwd_fake(_capi.KDA, _capi.RECOMPUTE, False, 0, 1.0, big, big, big, big, a64, ws, g,
+    r = backward._family_bwd_fake(_capi.KDA, _capi.RECOMPUTE, False, 0, False, 1.0, big, big, big, big, a64, ws, g,
                                   m(B, T, H, dt=torch.float32), None, None, a64, h0, h0, None, None, None, None, None)
     assert [tuple(x.shape) for x in r] == [(B, T, H, 128)] * 4 + [(B, T, H), (0,), (0,), (B, H, 128, 128)]
     assert r[0].dtype == torch.bfloat16 and r[3].dtype == torch.float32
-    r = backward._family_bwd_fake(_capi.GDN2, _capi.SAVED, True, 0, 1.0, big, big, big, big, a64, ws, g, None, big, big,
+    r = backward._family_bwd_fake(_capi.GDN2, _capi.SAVED, True, 0, True, 1.0, big, big, big, big, a64, ws, g, None, big, big,
                                   a64, None, None, big, big, big, big, m(B, T // 64, H, 128, 128))
     assert [tuple(x.shape) for x in r] == [(B, T, H, 128)] * 4 + [(0,)] + [(B, T, H, 128)] * 2 + [(0,)]
     assert r[0].dtype == torch.float32 and r[5].dtype == torch.float32
