@@ -137,6 +137,45 @@ int rewy_stage_fwd_scan(const RewyBwdArgs* args, const RewyStageBuffers* buf, re
 int rewy_stage_bwd_scan(const RewyBwdArgs* args, const RewyStageBuffers* buf, rewy_stream_t stream);
 int rewy_stage_chunk_adjoint(const RewyBwdArgs* args, const RewyStageBuffers* buf, rewy_stream_t stream);
 
+/* Forward pass.  rewy_chunk_fwd replaces FLA's chunk_kda_fwd / chunk_gdn2_fwd / chunk_gated_delta_rule_fwd /
+ * chunk_delta_rule_fwd as the reference's autograd forwards call them (src/fast_delta_rule/_compat/kda.py:89-113,
+ * gdn2.py:94-117, gdn.py:33-125, delta.py): from q, k, v, the cumulative gate and beta (or the two vector gates) it
+ * writes the output o, the final state and the whole saved set of the backward.  Three launches on the stream: the
+ * chunk-local kernel (Akk, Aqk, w, u, qg, kg), the forward state scan (h, v_new, final state) and the output kernel.
+ * g is the chunk-local cumulative gate in log2 units (rewy_gate_cumsum_fwd / rewy_scalar_gate_cumsum_fwd write it).
+ * Every output pointer except final_state is required; ctrl is an int32[2] control block whose first word is the
+ * device status word (rewy_device_status). */
+typedef struct RewyFwdArgs {
+  int32_t family;          /* REWY_DELTA / REWY_GDN / REWY_KDA / REWY_GDN2 */
+  int32_t B, T, H;
+  int32_t state_v_first;   /* h0 and final_state are [B,H,V,K] instead of [B,H,K,V] */
+  float scale;
+  const void* q;           /* bf16 [B,T,H,128] */
+  const void* k;           /* bf16 [B,T,H,128] */
+  const void* v;           /* bf16 [B,T,H,128] */
+  const float* g;          /* fp32 log2 cumsum: [B,T,H,128] (KDA, GDN2), [B,T,H] (GDN), NULL (DeltaNet) */
+  const float* beta;       /* fp32 [B,T,H] (DeltaNet, GDN, KDA), NULL (GDN2) */
+  const void* b_gate;      /* bf16 [B,T,H,128] (GDN2) */
+  const void* w_gate;      /* bf16 [B,T,H,128] (GDN2) */
+  const float* h0;         /* fp32 [B,H,128,128] or NULL */
+  void* o;                 /* bf16 [B,T,H,128] */
+  float* final_state;      /* fp32 [B,H,128,128] or NULL */
+  void* Aqk;               /* bf16 [B,T,H,64] */
+  void* Akk;               /* bf16 [B,T,H,64] */
+  void* w;                 /* bf16 [B,T,H,128] */
+  void* u;                 /* bf16 [B,T,H,128] */
+  void* qg;                /* bf16 [B,T,H,128] */
+  void* kg;                /* bf16 [B,T,H,128] */
+  void* v_new;             /* bf16 [B,T,H,128] */
+  void* h;                 /* bf16 [B,T/64,H,128,128] */
+  void* ctrl;              /* int32 [2] */
+} RewyFwdArgs;
+int rewy_chunk_fwd(const RewyFwdArgs* args, rewy_stream_t stream);
+/* Chunk-local cumulative sum in log2 units of a scalar per-head gate x [B,T,H] (BF16 or FP32), FLA chunk_local_cumsum
+ * as used by chunk_gated_delta_rule_fwd (_compat/gdn.py:52-69). */
+int rewy_scalar_gate_cumsum_fwd(const void* x, int x_is_f32, float* g_cumsum, int32_t B, int32_t T, int32_t H,
+                                rewy_stream_t stream);
+
 /* Element-wise stages of the autograd wrappers (one HBM pass each; rows = B*T*H rows of 128 values).
  *   rewy_l2norm_fwd / _bwd       <- FLA l2norm_fwd / l2norm_bwd as used at src/fast_delta_rule/_compat/kda.py:56-59,202-204
  *                                   (same in _compat/gdn.py, gdn2.py, delta.py).  x, y BF16 [rows,128]; rstd FP32 [rows];

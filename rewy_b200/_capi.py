@@ -23,7 +23,7 @@ EXPORTS = (
     "rewy_device_status", "rewy_wide_chunk_count", "rewy_set_chunk_variant", "rewy_set_scan_variant",
     "rewy_stage_chunk_adjoint_static", "rewy_static_device_status",
     "rewy_l2norm_fwd", "rewy_l2norm_bwd", "rewy_beta_sigmoid_fwd", "rewy_beta_sigmoid_bwd", "rewy_gate_cumsum_fwd",
-    "rewy_gate_act_bwd",
+    "rewy_gate_act_bwd", "rewy_chunk_fwd", "rewy_scalar_gate_cumsum_fwd",
     "rewy_last_error", "rewy_version", "rewy_kernel_launch_count",
 )
 
@@ -40,6 +40,13 @@ class BwdArgs(ctypes.Structure):
         ("db_gate", c_void_p), ("dw_gate", c_void_p), ("dh0", c_void_p),
         ("workspace", c_void_p), ("workspace_bytes", c_size_t),
     ]
+
+
+class FwdArgs(ctypes.Structure):
+    _fields_ = [("family", c_int32), ("B", c_int32), ("T", c_int32), ("H", c_int32), ("state_v_first", c_int32),
+                ("scale", c_float)] + [(n, c_void_p) for n in (
+                    "q", "k", "v", "g", "beta", "b_gate", "w_gate", "h0", "o", "final_state", "Aqk", "Akk", "w", "u", "qg",
+                    "kg", "v_new", "h", "ctrl")]
 
 
 class StageBuffers(ctypes.Structure):
@@ -81,6 +88,10 @@ def load():
     lib.rewy_selftest_tensor_core.argtypes = [c_void_p] * 9
     lib.rewy_selftest_tensor_core.restype = c_int
     i64 = ctypes.c_int64
+    lib.rewy_chunk_fwd.argtypes = [ctypes.POINTER(FwdArgs), c_void_p]
+    lib.rewy_chunk_fwd.restype = c_int
+    lib.rewy_scalar_gate_cumsum_fwd.argtypes = [c_void_p, c_int, c_void_p, c_int32, c_int32, c_int32, c_void_p]
+    lib.rewy_scalar_gate_cumsum_fwd.restype = c_int
     lib.rewy_l2norm_fwd.argtypes = [c_void_p, c_void_p, c_void_p, i64, c_float, c_void_p]
     lib.rewy_l2norm_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, i64, c_void_p]
     lib.rewy_beta_sigmoid_fwd.argtypes = [c_void_p, c_int, c_void_p, c_void_p, i64, c_float, c_void_p]

@@ -23,7 +23,9 @@ struct Dims {
 cudaError_t launch_prepare(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);
 cudaError_t launch_fwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);
 cudaError_t launch_bwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);      // warp-MMA kernel
-cudaError_t launch_fwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* err, cudaStream_t st);  // tcgen05
+// tcgen05 forward scan; final_state (optional) receives the state after the last chunk
+cudaError_t launch_fwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* err, cudaStream_t st,
+                               float* final_state = nullptr);
 cudaError_t launch_bwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* err, cudaStream_t st);  // tcgen05
 // chunk adjoint: tensor-core kernel (ctrl = device int[2 + chunks]: status word, wide-chunk count, indices)
 // followed by the warp-MMA kernel on the listed wide-span chunks; or the warp-MMA kernel on every chunk.

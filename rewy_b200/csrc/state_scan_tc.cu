@@ -357,6 +357,7 @@ bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_consta
 // needs 97 KB of shared memory and 192 TMEM columns and two CTAs share an SM.
 struct FwdParams {
   const float *g, *h0;
+  float* final_state;  // optional: state after the last chunk, FP32 [B,H,K,V] ([B,H,V,K] when svf)
   bf16* v_new;
   int* err;
   int T, H, NT;
@@ -553,6 +554,25 @@ fwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
   }
   wait(F_S, 6);
+  tc_fence_after_sync();
+  if (p.final_state != nullptr && alive) {
+    float* dst = p.final_state + (size_t)bh * DK * DV;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      float x[16];
+      tmem_ld16f(tlane + TMF_S + 64 * wg + 16 * c, x);
+      tmem_ld_wait();
+      const int v0 = 64 * wg + 16 * c;
+      if (p.svf) {
+#pragma unroll
+        for (int j = 0; j < 16; j++) dst[(size_t)(v0 + j) * DK + ch] = x[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<float4*>(dst + (size_t)ch * DV + v0 + j) = make_float4(x[j], x[j + 1], x[j + 2], x[j + 3]);
+      }
+    }
+  }
   if (tid == 0) bulk_wait0();
   tc_fence_before_sync();
   __syncthreads();
@@ -610,7 +630,8 @@ cudaError_t launch_bwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, 
 }
 
 // err: device status word, same contract as for the reverse scan.
-cudaError_t launch_fwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* err, cudaStream_t st) {
+cudaError_t launch_fwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* err, cudaStream_t st,
+                               float* final_state) {
   const int B = a.B, T = a.T, H = a.H, NT = T / C;
   const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
   CUtensorMap tm[4];
@@ -620,7 +641,7 @@ cudaError_t launch_fwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, 
             encode_tmap_2d(&tm[3], s.h, 2, 128, srows, 256, 64, 128);
   if (!ok) return cudaErrorInvalidValue;
   FwdParams p;
-  p.g = a.g; p.h0 = a.h0; p.v_new = (bf16*)s.v_new; p.err = err; p.T = T; p.H = H; p.NT = NT; p.svf = a.state_v_first;
+  p.g = a.g; p.h0 = a.h0; p.final_state = final_state; p.v_new = (bf16*)s.v_new; p.err = err; p.T = T; p.H = H; p.NT = NT; p.svf = a.state_v_first;
   switch (gate_mode_of(a.family)) {
     case GATE_NONE: return run_fwd<GATE_NONE>(tm, p, B * H, st);
     case GATE_SCALAR: return run_fwd<GATE_SCALAR>(tm, p, B * H, st);

@@ -1,10 +1,12 @@
-"""Chunked forward pass that produces the tensors the backward contract needs.
+"""Chunked forward pass that produces the output and the tensors the backward contract needs.
 
 The reference keeps FLA's Triton forward (``chunk_kda_fwd`` etc., bound at
 src/fast_delta_rule/_compat/kda.py:89-113, _compat/gdn2.py:94-117, _compat/gdn.py:33-125,
-_compat/delta.py); that library revision is not part of this package, so the forward half is
-stated here with batched torch ops on the inputs' device.  It is outside the timed backward.
-What it returns follows FLA's saved set exactly:
+_compat/delta.py).  Here ``chunk_forward`` runs the CUDA forward of librewy_b200.so (``rewy_chunk_fwd``: chunk-local
+kernel, tcgen05 state scan, output kernel; the chunk-local cumulative gate is ``rewy_gate_cumsum_fwd``); CPU tensors
+are refused.  ``chunk_forward_torch`` states the same forward with batched torch ops: it is the second implementation
+the CUDA forward is cross-checked against and what the host-only tests run; no operator calls it.
+What both return follows FLA's saved set exactly:
   g_cumsum  FP32 chunk-local cumulative gate in LOG2 units (scale RCP_LN2, _compat/gdn.py:52-69)
   Aqk, Akk  BF16 [B,T,H,64]; Akk = (I + tril(E Y^T,-1))^-1 without beta, Aqk = scale*tril(Qg Y^T)
   w,u,qg,kg,v_new  BF16 [B,T,H,128]; h BF16 [B,T/64,H,128,128] (state entering each chunk)
@@ -34,8 +36,65 @@ def _bf(x):
 
 @torch.no_grad()
 def chunk_forward(op, q, k, v, g=None, beta=None, b=None, w=None, scale=None, initial_state=None,
-                  output_final_state=True, g_is_cumsum=False):
-    """Returns dict(o, final_state, g_cumsum, Aqk, Akk, w, u, qg, kg, v_new, h).
+                  output_final_state=True, g_is_cumsum=False, state_v_first=False, check_status=False):
+    """CUDA forward.  Returns dict(o, final_state, g_cumsum, Aqk, Akk, w, u, qg, kg, v_new, h).
+
+    q,k,v BF16 [B,T,H,128]; g per-step natural-log gate ([B,T,H] for 'gdn', [B,T,H,128] for 'kda'/'gdn2', None for
+    'delta') or, with ``g_is_cumsum``, already the chunk-local cumulative gate in log2 units; beta [B,T,H] or
+    (b [B,T,H,128], w [B,T,H,128]) for 'gdn2'; ``state_v_first``: initial and final state are [B,H,V,K];
+    ``check_status`` synchronises and raises if a kernel gave up on a bounded wait."""
+    from . import _capi, elementwise
+    if not q.is_cuda:
+        raise RuntimeError("rewy_b200 chunk_forward needs CUDA tensors (there is no CPU fallback); "
+                           "chunk_forward_torch is the host restatement used for cross-checks")
+    B, T, H, K = k.shape
+    if T % CHUNK or K != 128 or v.shape[-1] != 128 or q.dtype != torch.bfloat16:
+        raise ValueError("chunk_forward needs BF16 inputs, T % 64 == 0 and K = V = 128")
+    scale = K ** -0.5 if scale is None else scale
+    dev = q.device
+    lib = _capi.load()
+    bf = lambda t: None if t is None else t.to(torch.bfloat16).contiguous()
+    q, k, v = bf(q), bf(k), bf(v)
+    g_cumsum = None
+    with torch.cuda.device(dev):
+        if op in ("kda", "gdn2"):
+            g_cumsum = g.float().contiguous() if g_is_cumsum else elementwise.gate_cumsum_fwd(g)
+        elif op == "gdn":
+            if g_is_cumsum:
+                g_cumsum = g.float().contiguous()
+            else:
+                gin = g if g.dtype in (torch.bfloat16, torch.float32) else g.float()
+                gin = gin.contiguous()
+                g_cumsum = torch.empty(gin.shape, dtype=torch.float32, device=dev)
+                _capi.check(lib.rewy_scalar_gate_cumsum_fwd(_capi.ptr(gin), int(gin.dtype == torch.float32), _capi.ptr(g_cumsum),
+                                                            B, T, H, _capi.current_stream(dev)), "rewy_scalar_gate_cumsum_fwd")
+        big = lambda: torch.empty(B, T, H, 128, dtype=torch.bfloat16, device=dev)
+        a64 = lambda: torch.empty(B, T, H, 64, dtype=torch.bfloat16, device=dev)
+        out = dict(o=big(), Aqk=a64(), Akk=a64(), w=big(), u=big(), qg=big(), kg=big(), v_new=big(),
+                   h=torch.empty(B, T // CHUNK, H, 128, 128, dtype=torch.bfloat16, device=dev))
+        final = torch.empty(B, H, 128, 128, dtype=torch.float32, device=dev) if output_final_state else None
+        ctrl = torch.empty(2, dtype=torch.int32, device=dev)
+        a = _capi.FwdArgs()
+        a.family, a.B, a.T, a.H, a.state_v_first, a.scale = _capi.FAMILY_ID[op], B, T, H, int(bool(state_v_first)), float(scale)
+        keep = [q, k, v, g_cumsum, None if beta is None else beta.float().contiguous(), bf(b), bf(w),
+                None if initial_state is None else initial_state.float().contiguous()]
+        for name, t in zip(("q", "k", "v", "g", "beta", "b_gate", "w_gate", "h0"), keep):
+            setattr(a, name, _capi.ptr(t))
+        for name, t in out.items():
+            setattr(a, name, _capi.ptr(t))
+        a.final_state, a.ctrl = _capi.ptr(final), _capi.ptr(ctrl)
+        _capi.check(lib.rewy_chunk_fwd(a, _capi.current_stream(dev)), "rewy_chunk_fwd")
+        if check_status:
+            _capi.check(lib.rewy_device_status(_capi.ptr(ctrl), _capi.current_stream(dev)), "device status (forward)")
+    out.update(final_state=final, g_cumsum=g_cumsum)
+    return out
+
+
+@torch.no_grad()
+def chunk_forward_torch(op, q, k, v, g=None, beta=None, b=None, w=None, scale=None, initial_state=None,
+                        output_final_state=True, g_is_cumsum=False):
+    """The same forward with batched torch ops on the inputs' device (cross-check implementation).
+    Returns dict(o, final_state, g_cumsum, Aqk, Akk, w, u, qg, kg, v_new, h).
 
     q,k,v BF16 [B,T,H,128]; g per-step natural-log gate FP32 ([B,T,H] for 'gdn', [B,T,H,128] for
     'kda'/'gdn2', None for 'delta'); beta [B,T,H] or (b [B,T,H,128], w [B,T,H,128]) for 'gdn2'."""

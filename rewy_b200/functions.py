@@ -17,11 +17,6 @@ from .forward import chunk_forward
 from . import elementwise as _ew
 
 
-def _vfirst(t, state_v_first):
-    """[B,H,V,K] <-> [B,H,K,V] view change for the torch forward (the CUDA backward reads either layout itself)."""
-    return t if (t is None or not state_v_first) else t.transpose(-1, -2).contiguous()
-
-
 def _cumulative_gate(g, A_log=None, dt_bias=None):
     """Chunk-local cumulative gate in log2 units on the device (vector gates), optionally with the KDA gate activation."""
     return _ew.gate_cumsum_fwd(g, A_log, dt_bias)
@@ -41,8 +36,8 @@ class ChunkKDAFunction(torch.autograd.Function):
         # with use_gate_in_kernel, g is the raw gate input: -exp(A_log) * softplus(g + dt_bias) and the chunk cumsum are
         # one pass; otherwise g is the per-step natural-log decay
         g_cumsum = _cumulative_gate(g, A_log if use_gate_in_kernel else None, dt_bias if use_gate_in_kernel else None)
-        f = chunk_forward("kda", q, k, v, g=g_cumsum, beta=beta, scale=scale, initial_state=_vfirst(initial_state, state_v_first),
-                          output_final_state=output_final_state, g_is_cumsum=True)
+        f = chunk_forward("kda", q, k, v, g=g_cumsum, beta=beta, scale=scale, initial_state=initial_state,
+                          output_final_state=output_final_state, g_is_cumsum=True, state_v_first=state_v_first)
         keep = (lambda x: x) if disable_recompute else (lambda x: None)
         ctx.save_for_backward(q, q_rstd, k, k_rstd, v, g_cumsum, g, beta_raw, beta, A_log, dt_bias, f["Aqk"], f["Akk"],
                               keep(f["w"]), keep(f["u"]), keep(f["qg"]), keep(f["kg"]), keep(f["v_new"]),
@@ -50,7 +45,7 @@ class ChunkKDAFunction(torch.autograd.Function):
         ctx.scale, ctx.disable_recompute = scale, disable_recompute
         ctx.use_qk_l2norm_in_kernel, ctx.use_beta_sigmoid_in_kernel = use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel
         ctx.use_gate_in_kernel, ctx.allow_neg_eigval, ctx.state_v_first = use_gate_in_kernel, allow_neg_eigval, state_v_first
-        return f["o"].type_as(q), _vfirst(f["final_state"], state_v_first)
+        return f["o"].type_as(q), f["final_state"]
 
     @staticmethod
     def backward(ctx, do, dht):
@@ -83,14 +78,14 @@ class ChunkGDN2Function(torch.autograd.Function):
             q, q_rstd = _ew.l2norm_fwd(q)
             k, k_rstd = _ew.l2norm_fwd(k)
         g_cumsum = _cumulative_gate(g)
-        f = chunk_forward("gdn2", q, k, v, g=g_cumsum, b=b, w=w, scale=scale, initial_state=_vfirst(initial_state, state_v_first),
-                          output_final_state=output_final_state, g_is_cumsum=True)
+        f = chunk_forward("gdn2", q, k, v, g=g_cumsum, b=b, w=w, scale=scale, initial_state=initial_state,
+                          output_final_state=output_final_state, g_is_cumsum=True, state_v_first=state_v_first)
         keep = (lambda x: x) if disable_recompute else (lambda x: None)
         ctx.save_for_backward(q, q_rstd, k, k_rstd, v, g_cumsum, g, b, w, f["Aqk"], f["Akk"], keep(f["w"]),
                               keep(f["u"]), keep(f["qg"]), keep(f["kg"]), keep(f["v_new"]), keep(f["h"]), initial_state)
         ctx.scale, ctx.disable_recompute, ctx.use_qk_l2norm_in_kernel = scale, disable_recompute, use_qk_l2norm_in_kernel
         ctx.state_v_first = state_v_first
-        return f["o"].type_as(q), _vfirst(f["final_state"], state_v_first)
+        return f["o"].type_as(q), f["final_state"]
 
     @staticmethod
     def backward(ctx, do, dht):
@@ -119,13 +114,13 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
         beta_raw = beta
         if use_beta_sigmoid_in_kernel:
             beta = _ew.beta_sigmoid_fwd(beta_raw, 2.0 if allow_neg_eigval else 1.0)
-        f = chunk_forward("gdn", q, k, v, g=g, beta=beta, scale=scale, initial_state=_vfirst(initial_state, state_v_first),
-                          output_final_state=output_final_state)
+        f = chunk_forward("gdn", q, k, v, g=g, beta=beta, scale=scale, initial_state=initial_state,
+                          output_final_state=output_final_state, state_v_first=state_v_first)
         ctx.save_for_backward(q, q_rstd, k, k_rstd, v, f["g_cumsum"], g, beta_raw, beta, f["Akk"], initial_state)
         ctx.scale, ctx.use_qk_l2norm_in_kernel = scale, use_qk_l2norm_in_kernel
         ctx.use_beta_sigmoid_in_kernel, ctx.allow_neg_eigval = use_beta_sigmoid_in_kernel, allow_neg_eigval
         ctx.state_v_first = state_v_first
-        return f["o"].to(q.dtype), _vfirst(f["final_state"], state_v_first)
+        return f["o"].to(q.dtype), f["final_state"]
 
     @staticmethod
     def backward(ctx, do, dht):

@@ -22,7 +22,7 @@ def forward_saved(op, xs):
         kw["b"], kw["w"] = xs["b"], xs["w"]
     else:
         kw["beta"] = xs["beta"]
-    return chunk_forward(op, **kw)
+    return chunk_forward(op, check_status=True, **kw)
 
 
 def base_args(op, xs, saved, out_dtype=_capi.OUT_F32, intra_passes=0):

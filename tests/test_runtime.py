@@ -148,9 +148,14 @@ def test_argument_validation_without_a_gpu():
 
 
 def test_forward_producer_matches_oracle_forward_on_cpu():
-    """The product's torch forward (BF16 operands) against the FP64 chunked forward of the oracle."""
+    """The torch statement of the forward (BF16 operands; the cross-check of the CUDA forward) against the FP64 chunked
+    forward of the oracle; the CUDA forward itself refuses CPU tensors."""
+    from rewy_b200.forward import chunk_forward as cuda_forward
+    t = torch.zeros(1, 64, 1, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        cuda_forward("delta", t, t, t, beta=torch.zeros(1, 64, 1))
     from oracle import chunk_forward as oracle_forward
-    from rewy_b200.forward import chunk_forward
+    from rewy_b200.forward import chunk_forward_torch as chunk_forward
     from rewy_b200.synthetic import make_inputs, operator_inputs
     for op in ("kda", "gdn", "gdn2", "delta"):
         xs = make_inputs(op, 1, 128, 2, seed=8)
