@@ -491,7 +491,7 @@ static_assert((size_t)C * LDG * sizeof(float) <= (size_t)2 * C * LD128 * sizeof(
 template <int GATE, bool VB>
 cudaError_t run(const ChunkParams& p, int B, cudaStream_t st) {
   auto kern = chunk_adjoint_kernel<GATE, VB>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CHUNK_SMEM);
+  cudaError_t e = ensure_dynamic_smem<chunk_adjoint_kernel<GATE, VB>>(CHUNK_SMEM);
   if (e != cudaSuccess) return e;
   dim3 grid(p.T / C, B * p.H);
   if (p.list != nullptr) grid = dim3(min(p.T / C * B * p.H, 296), 1);

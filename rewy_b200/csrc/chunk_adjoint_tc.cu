@@ -946,7 +946,7 @@ int sm_count() {
 template <int GATE, bool VB, bool OUTF32>
 cudaError_t run1(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
   auto kern = chunk_adjoint_tc_kernel<GATE, VB, OUTF32>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+  cudaError_t e = ensure_dynamic_smem<chunk_adjoint_tc_kernel<GATE, VB, OUTF32>>(TC_SMEM);
   if (e != cudaSuccess) return e;
   const int grid = p.total_chunks < sm_count() ? p.total_chunks : sm_count();
   kern<<<grid, TPB, TC_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9], tm[10], tm[11], tm[12], tm[13], tm[14], tm[15], tm[16], tm[17], tm[18], p);
@@ -961,12 +961,9 @@ cudaError_t run(const CUtensorMap* tm, const TcParams& p, cudaStream_t st) {
 
 }  // namespace
 
-// ctrl: device int[2 + total_chunks]: [0] status word (zeroed by the caller), [1] number of wide-span chunks,
-// [2..] their indices.
-cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* ctrl, cudaStream_t st) {
-  const int B = a.B, T = a.T, H = a.H, NT = T / C;
-  const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
-  CUtensorMap tm[19];
+// Encodes the 19 tensor maps of the chunk kernel (tile loads of every operand, tile stores of the gradients).
+bool encode_chunk_maps(CUtensorMap* tm, const RewyBwdArgs& a, const RewyStageBuffers& s, uint64_t rows, uint64_t srows) {
+  const int H = a.H;
   bool ok = encode_tmap_2d(&tm[0], a.Akk, 2, (uint64_t)H * 64, rows, (uint64_t)H * 128, 64, 64) &&
             encode_tmap_panels(&tm[1], s.dR, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
             encode_tmap_panels(&tm[2], s.dR_lo, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2) &&
@@ -996,7 +993,31 @@ cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers
       ok = encode_tmap_2d(&tm[16], a.db_gate, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 128, 64, false) &&
            encode_tmap_panels(&tm[18], a.dw_gate, 2, (uint64_t)H * 128, rows, (uint64_t)H * 256, 64, 2);
   }
-  if (!ok) return cudaErrorInvalidValue;
+  return ok;
+}
+
+// ctrl: device int[2 + total_chunks]: [0] status word (zeroed by the caller), [1] number of wide-span chunks,
+// [2..] their indices.
+cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* ctrl, cudaStream_t st) {
+  const int B = a.B, T = a.T, H = a.H, NT = T / C;
+  const uint64_t rows = (uint64_t)B * T, srows = (uint64_t)B * NT * H * 128;
+  struct Key {
+    const void* ptr[20];
+    int B, T, H, family, out_dtype;
+  } key;
+  memset(&key, 0, sizeof(key));
+  const void* ptrs[20] = {a.Akk, s.dR, s.dR_lo, a.d_o, s.v_new, s.h, s.dh, a.v, a.k, a.g, a.dg, a.q, a.dv, a.dq, a.dk,
+                          a.b_gate, a.db_gate, a.w_gate, a.dw_gate, nullptr};
+  memcpy(key.ptr, ptrs, sizeof(ptrs));
+  key.B = B; key.T = T; key.H = H; key.family = a.family; key.out_dtype = a.out_dtype;
+  thread_local TmapCache<19, sizeof(Key)> cache;
+  const CUtensorMap* tm = cache.find(&key);
+  if (tm == nullptr) {
+    CUtensorMap* w = cache.slot();
+    if (!encode_chunk_maps(w, a, s, rows, srows)) return cudaErrorInvalidValue;
+    cache.commit(&key);
+    tm = w;
+  }
   cudaError_t e = cudaMemsetAsync(ctrl + 1, 0, sizeof(int), st);  // wide-chunk count; the status word is kept
   if (e != cudaSuccess) return e;
   TcParams p;

@@ -10,8 +10,10 @@
 // The two 64x64x128 products that build the A matrices use centred gate factors (alpha = 2^(G - c), zeta = 1/alpha with
 // c the per-channel mid-point of G over the chunk) and BF16 hi/lo operand pairs in three passes (about 16 mantissa
 // bits), accumulated in FP32 by warp-level MMA; scalar gates apply their pairwise factor 2^(G_i - G_j) to the exact
-// q k^T and k k^T products instead.  The unit lower-triangular inverse is plain FP32 forward substitution, one thread
-// per column with the column held in registers.
+// q k^T and k k^T products instead.  A chunk whose cumulative gate spans 80 log2 units or more in some channel does not
+// use centred factors (they would leave the FP32 range): its two matrices are summed pair by pair on the CUDA cores,
+// sum_k q_ik k_jk 2^(G_ik - G_jk), like the exact pairwise path of the backward.  The unit lower-triangular inverse is
+// plain FP32 forward substitution, one thread per column with the column held in registers.
 #include <cstdio>
 #include "warp_mma.cuh"
 
@@ -21,6 +23,8 @@ namespace {
 constexpr int LD128 = 136;  // padded pitch of a 128-wide BF16 tile
 constexpr int LD64 = 72;    // padded pitch of a 64-wide BF16 tile
 constexpr int LDL = 68;     // padded pitch of the FP32 64x64 matrix (rows stay 16-byte aligned)
+constexpr int LDG = 132;    // padded pitch of the FP32 gate tile of a wide-span chunk
+constexpr float FWD_SPAN_LIMIT = 80.f;
 
 struct FwdLocalParams {
   const bf16 *q, *k, *v, *bg, *wg;
@@ -67,6 +71,7 @@ __global__ void __launch_bounds__(256) chunk_fwd_local_kernel(const FwdLocalPara
   const size_t base1 = row0 * H + h;
   const int tid = threadIdx.x;
 
+  bool wide_here = false;
   if (GATE == GATE_SCALAR && tid < C) sG[tid] = p.g[base1 + (size_t)tid * H];
   if (!VECTOR_BETA && tid >= C && tid < 2 * C) sBeta[tid - C] = p.beta[base1 + (size_t)(tid - C) * H];
   if (GATE == GATE_VECTOR && tid < 128) {
@@ -80,8 +85,11 @@ __global__ void __launch_bounds__(256) chunk_fwd_local_kernel(const FwdLocalPara
     }
     sGl[tid] = last;
     sCen[tid] = 0.5f * (lo + hi);
+    wide_here = !(hi - lo < FWD_SPAN_LIMIT);
   }
-  __syncthreads();
+  // wide gate span somewhere in the chunk: no centred factors, exact pairwise sums instead (vector gate only)
+  const bool wide = __syncthreads_or(wide_here ? 1 : 0) != 0;
+  float* sGf = reinterpret_cast<float*>(sT + 3 * TILE);  // [64][132] FP32 gate tile of a wide chunk
 
   // element-wise operands, 8 columns (16 bytes of BF16) per thread-iteration
   for (int i = tid; i < C * 16; i += blockDim.x) {
@@ -128,7 +136,7 @@ __global__ void __launch_bounds__(256) chunk_fwd_local_kernel(const FwdLocalPara
       zv[j] = vv * ww;
       qv[j] = qq * gam;
       kv[j] = kk * (GATE == GATE_NONE ? 1.f : exp2f(glast - gj));
-      if (GATE == GATE_VECTOR) {
+      if (GATE == GATE_VECTOR && !wide) {
         const float al = exp2f(gj - sCen[c + j]);
         qc[j] = qq * al;
         ec[j] = bb * kk * al;
@@ -147,19 +155,42 @@ __global__ void __launch_bounds__(256) chunk_fwd_local_kernel(const FwdLocalPara
     *reinterpret_cast<uint4*>(sZ + r * LD128 + c) = make_uint4(zo[0], zo[1], zo[2], zo[3]);
     *reinterpret_cast<uint4*>(p.qg + go) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
     *reinterpret_cast<uint4*>(p.kg + go) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
-    if (GATE == GATE_VECTOR) {
+    if (GATE == GATE_VECTOR && !wide) {
       split_store8(sT + 0 * TILE + r * LD128 + c, sT + 1 * TILE + r * LD128 + c, qc);
       split_store8(sT + 2 * TILE + r * LD128 + c, sT + 3 * TILE + r * LD128 + c, ec);
       split_store8(sT + 4 * TILE + r * LD128 + c, sT + 5 * TILE + r * LD128 + c, yc);
     } else {
       *reinterpret_cast<uint4*>(sT + 0 * TILE + r * LD128 + c) = qr;
       *reinterpret_cast<uint4*>(sT + 1 * TILE + r * LD128 + c) = kr;
+      if (GATE == GATE_VECTOR) {  // wide chunk: raw key gate and gate rows for the pairwise sums
+        if (VECTOR_BETA) *reinterpret_cast<uint4*>(sT + 2 * TILE + r * LD128 + c) = br;
+        *reinterpret_cast<float4*>(sGf + r * LDG + c) = make_float4(gg[0], gg[1], gg[2], gg[3]);
+        *reinterpret_cast<float4*>(sGf + r * LDG + c + 4) = make_float4(gg[4], gg[5], gg[6], gg[7]);
+      }
     }
   }
   __syncthreads();
 
   // ---- the two A products: Qc Yc^T (-> Aqk) and Ec Yc^T (-> strictly lower part of I + L) -------------------------
-  {
+  if (GATE == GATE_VECTOR && wide) {
+    // exact pairwise sums, thread = (row i, every fourth column j)
+    const bf16 *sQr = sT, *sKr = sT + TILE, *sBr = sT + 2 * TILE;
+    const int i = tid >> 2;
+    const float beta_i = VECTOR_BETA ? 0.f : sBeta[i];
+    for (int j = tid & 3; j < C; j += 4) {
+      float aq = 0.f, ak = 0.f;
+      if (j <= i) {
+        for (int kk = 0; kk < 128; kk++) {
+          const float f = exp2f(sGf[i * LDG + kk] - sGf[j * LDG + kk]) * bf2f(sKr[j * LD128 + kk]);
+          aq = fmaf(bf2f(sQr[i * LD128 + kk]), f, aq);
+          const float bi = VECTOR_BETA ? bf2f(sBr[i * LD128 + kk]) : beta_i;
+          ak = fmaf(bi * bf2f(sKr[i * LD128 + kk]), f, ak);
+        }
+      }
+      p.Aqk[base64 + (size_t)i * H * 64 + j] = f2bf(p.scale * aq);
+      sL[i * LDL + j] = j < i ? ak : 0.f;
+    }
+  } else {
     Tile<64, 64, 2, 4> aq, ak;
     aq.zero();
     ak.zero();
@@ -300,7 +331,7 @@ template <int GATE, bool VB>
 cudaError_t run_local(const FwdLocalParams& p, int B, cudaStream_t st) {
   auto kern = chunk_fwd_local_kernel<GATE, VB>;
   const size_t smem = GATE == GATE_VECTOR ? FWD_LOCAL_SMEM_VECTOR : FWD_LOCAL_SMEM_SCALAR;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = ensure_dynamic_smem<chunk_fwd_local_kernel<GATE, VB>>(smem);
   if (e != cudaSuccess) return e;
   dim3 grid(p.T / C, B * p.H);
   kern<<<grid, 256, smem, st>>>(p);
@@ -359,7 +390,7 @@ extern "C" int rewy_chunk_fwd(const RewyFwdArgs* a, rewy_stream_t stream) {
     e = launch_fwd_scan_tc(ba, sb, static_cast<int*>(a->ctrl), st, a->final_state);
   }
   if (e == cudaSuccess) {
-    e = cudaFuncSetAttribute(chunk_output_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)OUTPUT_SMEM);
+    e = ensure_dynamic_smem<chunk_output_kernel>(OUTPUT_SMEM);
     if (e == cudaSuccess) {
       dim3 grid(a->T / C, a->B * a->H);
       chunk_output_kernel<<<grid, 256, OUTPUT_SMEM, st>>>((const bf16*)a->qg, (const bf16*)a->Aqk, (const bf16*)a->v_new,

@@ -40,6 +40,21 @@ __host__ __device__ inline int gate_mode_of(int family) {
   return family == REWY_DELTA ? GATE_NONE : (family == REWY_GDN ? GATE_SCALAR : GATE_VECTOR);
 }
 
+// Opt a kernel in to `bytes` of dynamic shared memory once per device (the attribute sticks to the function in that
+// device's context), so that a launch costs no extra runtime call afterwards.  Kern is the kernel itself (one guard per
+// template instance).
+template <auto Kern>
+inline cudaError_t ensure_dynamic_smem(size_t bytes) {
+  static unsigned long long done = 0;  // bit d: set on device d
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 64 && ((__atomic_load_n(&done, __ATOMIC_ACQUIRE) >> dev) & 1ull)) return cudaSuccess;
+  e = cudaFuncSetAttribute(Kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess && dev < 64) __atomic_fetch_or(&done, 1ull << dev, __ATOMIC_RELEASE);
+  return e;
+}
+
 // ---- small device helpers -------------------------------------------------------------------
 __device__ __forceinline__ float bf2f(bf16 x) { return __bfloat162float(x); }
 __device__ __forceinline__ bf16 f2bf(float x) { return __float2bfloat16_rn(x); }

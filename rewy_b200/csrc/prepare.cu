@@ -146,7 +146,7 @@ template <int GATE, bool VB>
 cudaError_t run(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st, bool need_aqk) {
   auto kern = prepare_kernel<GATE, VB>;
   const size_t smem = need_aqk ? PREPARE_SMEM_AQK : PREPARE_SMEM_BASE;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREPARE_SMEM_AQK);
+  cudaError_t e = ensure_dynamic_smem<prepare_kernel<GATE, VB>>(PREPARE_SMEM_AQK);
   if (e != cudaSuccess) return e;
   dim3 grid(a.T / C, a.B * a.H);
   kern<<<grid, 256, smem, st>>>(

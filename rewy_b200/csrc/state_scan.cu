@@ -181,7 +181,7 @@ constexpr size_t FWD_SMEM = (size_t)(2 * C * LD128 + 2 * C * LD64 + DK * LD64) *
 template <int GATE>
 cudaError_t run_bwd(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
   auto kern = bwd_scan_kernel<GATE>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BWD_SMEM);
+  cudaError_t e = ensure_dynamic_smem<bwd_scan_kernel<GATE>>(BWD_SMEM);
   if (e != cudaSuccess) return e;
   dim3 grid(DV / BV, a.B * a.H);
   kern<<<grid, 256, BWD_SMEM, st>>>((const bf16*)s.qg, (const bf16*)s.kg, (const bf16*)s.w, (const bf16*)s.Aqk,
@@ -193,7 +193,7 @@ cudaError_t run_bwd(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_
 template <int GATE>
 cudaError_t run_fwd(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
   auto kern = fwd_scan_kernel<GATE>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FWD_SMEM);
+  cudaError_t e = ensure_dynamic_smem<fwd_scan_kernel<GATE>>(FWD_SMEM);
   if (e != cudaSuccess) return e;
   dim3 grid(DV / BV, a.B * a.H);
   kern<<<grid, 256, FWD_SMEM, st>>>((const bf16*)s.kg, (const bf16*)s.w, (const bf16*)s.u, a.g, a.h0, (bf16*)s.h,

@@ -585,7 +585,7 @@ static_assert(2 * (FWD_SCAN_SMEM + 1024) <= 233472, "two forward-scan CTAs must 
 template <int GATE>
 cudaError_t run_fwd(const CUtensorMap* tm, const FwdParams& p, int grid, cudaStream_t st) {
   auto kern = fwd_scan_tc_kernel<GATE>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FWD_SCAN_SMEM);
+  cudaError_t e = ensure_dynamic_smem<fwd_scan_tc_kernel<GATE>>(FWD_SCAN_SMEM);
   if (e != cudaSuccess) return e;
   kern<<<grid, TPB, FWD_SCAN_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], p);
   count_launch();
@@ -597,7 +597,7 @@ constexpr size_t SCAN_SMEM = SS::TOTAL + 1024;
 template <int GATE>
 cudaError_t run(const CUtensorMap* tm, const ScanParams& p, int grid, cudaStream_t st) {
   auto kern = bwd_scan_tc_kernel<GATE>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SCAN_SMEM);
+  cudaError_t e = ensure_dynamic_smem<bwd_scan_tc_kernel<GATE>>(SCAN_SMEM);
   if (e != cudaSuccess) return e;
   kern<<<grid, TPB, SCAN_SMEM, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], p);
   count_launch();

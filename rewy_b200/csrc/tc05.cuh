@@ -2,6 +2,7 @@
 // loads (no multicast anywhere), tcgen05 MMA with TMEM accumulators, shared-memory matrix descriptors.
 #pragma once
 #include <cuda.h>
+#include <cstring>
 #include "common.cuh"
 
 namespace rewy {
@@ -253,5 +254,33 @@ bool encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t
 // swizzled bytes - the operand layout of a K extent (or an MN extent) wider than one swizzle atom.
 bool encode_tmap_panels(CUtensorMap* out, const void* base, int elem_bytes, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
                         uint32_t box_rows, uint32_t panels);
+
+// Host-side cache of encoded tensor maps, one instance per launcher and host thread.  A call whose key (the pointers
+// and the shape the maps depend on, as raw bytes) matches one of the last SLOTS calls reuses the encoded maps, so
+// repeated launches on the same buffers (training steps, benchmark loops, graph re-captures) cost no driver calls.
+template <int N, int KEY_BYTES, int SLOTS = 4>
+struct TmapCache {
+  struct Entry {
+    unsigned char key[KEY_BYTES];
+    CUtensorMap tm[N];
+    bool valid = false;
+  } entry[SLOTS];
+  int next = 0;
+  const CUtensorMap* find(const void* key) const {
+    for (int i = 0; i < SLOTS; i++)
+      if (entry[i].valid && memcmp(entry[i].key, key, KEY_BYTES) == 0) return entry[i].tm;
+    return nullptr;
+  }
+  // the slot to encode into; call commit(key) once every map of the slot has been encoded
+  CUtensorMap* slot() {
+    entry[next].valid = false;
+    return entry[next].tm;
+  }
+  void commit(const void* key) {
+    memcpy(entry[next].key, key, KEY_BYTES);
+    entry[next].valid = true;
+    next = (next + 1) % SLOTS;
+  }
+};
 
 }  // namespace rewy
