@@ -246,6 +246,9 @@ int rewy_set_chunk_variant(int variant);
 /* Same for the reverse state scan: 0 (default) tensor-core kernel (needs RewyStageBuffers.ctrl for its status
  * word; without it the stage function uses the warp-MMA kernel), 1 warp-MMA kernel. */
 int rewy_set_scan_variant(int variant);
+/* Same for the prepare stage: 0 (default) TMA + tcgen05 kernel (needs RewyStageBuffers.ctrl for its status word; without
+ * it the stage function uses the warp-MMA kernel), 1 warp-MMA kernel. */
+int rewy_set_prepare_variant(int variant);
 
 /* Self-test of the tensor-core plumbing (no counterpart in the reference): one CTA pushes every shared-memory
  * operand form the stages use through tcgen05.mma.  Inputs row-major on the device: A [128x128] bf16,

@@ -124,6 +124,13 @@ void timing_mark(int set, int idx, cudaStream_t st) {
   g_timing.have[set][idx] = true;
 }
 
+std::atomic<int> g_prepare_variant{0};  // 0 = TMA + tcgen05 kernel, 1 = warp-MMA kernel
+
+cudaError_t run_prepare(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
+  if (g_prepare_variant.load(std::memory_order_relaxed) == 1 || s.ctrl == nullptr) return launch_prepare(a, s, st);
+  return launch_prepare_tc(a, s, static_cast<int*>(s.ctrl), st);
+}
+
 cudaError_t run_fwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
   if (g_scan_variant.load(std::memory_order_relaxed) == 1 || s.ctrl == nullptr) return launch_fwd_scan(a, s, st);
   return launch_fwd_scan_tc(a, s, static_cast<int*>(s.ctrl), st);
@@ -187,7 +194,7 @@ int run_family(const RewyBwdArgs* a, int family, cudaStream_t st) {
   if ((rc = check_cuda(clear_status(s.ctrl, st), "status word")) != REWY_OK) return rc;
   timing_mark(set, 0, st);
   if (p.prepare) {
-    if ((rc = check_cuda(launch_prepare(*a, s, st), "prepare")) != REWY_OK) return rc;
+    if ((rc = check_cuda(run_prepare(*a, s, st), "prepare")) != REWY_OK) return rc;
     timing_mark(set, 1, st);
     if ((rc = check_cuda(run_fwd_scan(*a, s, st), "forward state scan")) != REWY_OK) return rc;
   }
@@ -269,7 +276,8 @@ int rewy_stage_prepare(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_str
   if (a->family == REWY_GDN2) { STAGE_PTR(a->b_gate, "b_gate"); STAGE_PTR(a->w_gate, "w_gate"); }
   else STAGE_PTR(a->beta, "beta");
   if (a->family == REWY_DELTA || a->family == REWY_GDN) STAGE_PTR(s->Aqk, "Aqk");
-  return check_cuda(launch_prepare(*a, *s, (cudaStream_t)st), "prepare");
+  if ((rc = check_cuda(clear_status(s->ctrl, (cudaStream_t)st), "status word")) != REWY_OK) return rc;
+  return check_cuda(run_prepare(*a, *s, (cudaStream_t)st), "prepare");
 }
 
 int rewy_stage_fwd_scan(const RewyBwdArgs* a, const RewyStageBuffers* s, rewy_stream_t st) {
@@ -333,6 +341,12 @@ int rewy_stage_timing_read(float* ms_sum, int* calls) {
 int rewy_set_scan_variant(int variant) {
   if (variant != 0 && variant != 1) return fail(REWY_ERR_UNSUPPORTED, "scan variant must be 0 or 1%s");
   g_scan_variant.store(variant, std::memory_order_relaxed);
+  return REWY_OK;
+}
+
+int rewy_set_prepare_variant(int variant) {
+  if (variant != 0 && variant != 1) return fail(REWY_ERR_UNSUPPORTED, "prepare variant must be 0 or 1%s");
+  g_prepare_variant.store(variant, std::memory_order_relaxed);
   return REWY_OK;
 }
 

@@ -20,7 +20,8 @@ struct Dims {
 };
 
 // Host-side launchers (one per stage); each returns a cudaError_t from the launch.
-cudaError_t launch_prepare(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);
+cudaError_t launch_prepare(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);                // warp-MMA kernel
+cudaError_t launch_prepare_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* err, cudaStream_t st);  // TMA + tcgen05
 cudaError_t launch_fwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);
 cudaError_t launch_bwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st);      // warp-MMA kernel
 // tcgen05 forward scan; final_state (optional) receives the state after the last chunk

@@ -52,15 +52,27 @@ def _oracle_recompute(op, xs, saved):
     return {n: _unchunks(t) for n, t in out.items()}
 
 
+@pytest.mark.parametrize("variant", ("tensor_core", "warp_mma"))
 @pytest.mark.parametrize("op", OPS)
-def test_stage_prepare(op):
-    xs = _inputs(op)
+def test_stage_prepare(op, variant):
+    """The recompute stage: the TMA + tcgen05 kernel (production) and the warp-MMA kernel (cross-check), on a problem
+    with several chunks per persistent CTA slot."""
+    xs = _inputs(op, B=2, T=512, H=3)
     saved = forward_saved(op, xs)
     a, keep = base_args(op, xs, saved)
     B, T, H, _ = xs["k"].shape
     mk = lambda d: torch.full((B, T, H, d), float("nan"), dtype=torch.bfloat16, device=DEV)
     w, u, qg, kg, aqk = mk(128), mk(128), mk(128), mk(128), mk(64)
-    call_stage("rewy_stage_prepare", a, stage_buffers(w=w, u=u, qg=qg, kg=kg, Aqk=aqk), DEV)
+    ctrl = torch.zeros(8, dtype=torch.int32, device=DEV)
+    lib = _capi.load()
+    try:
+        assert lib.rewy_set_prepare_variant(1 if variant == "warp_mma" else 0) == 0
+        before = lib.rewy_kernel_launch_count()
+        call_stage("rewy_stage_prepare", a, stage_buffers(w=w, u=u, qg=qg, kg=kg, Aqk=aqk, ctrl=ctrl), DEV)
+        assert lib.rewy_kernel_launch_count() == before + 1
+    finally:
+        lib.rewy_set_prepare_variant(0)
+    assert ctrl[0].item() == 0, f"device status word {ctrl[0].item()}: a bounded wait gave up"
     # against the FP64 oracle, in the public dtype (BF16) of the stage's outputs: operands are rounded to BF16 before the
     # products (as the reference's recompute does), results once more on the way out
     ref = _oracle_recompute(op, xs, saved)
