@@ -235,6 +235,10 @@ int rewy_wide_chunk_count(const void* ctrl, rewy_stream_t stream);
  *  - All calls on one device share the one array, and it keeps the previous call's contents; each call clears
  *    the two words that must start at zero.  Two calls whose kernels may overlap on the GPU (different
  *    streams) race on it - serialise them.
+ *  - The array's device address is cached per device at that first call; a cudaDeviceReset invalidates it (the
+ *    library must be reloaded afterwards).
+ *  - The host-side checks are those of rewy_stage_chunk_adjoint (shape envelope, every pointer non-NULL and 16-byte
+ *    aligned), so a misaligned pointer is REWY_ERR_ALIGN before anything is launched.
  * rewy_static_device_status reads the array's status word on the current device (SYNCHRONISES the stream). */
 #define REWY_STATIC_MAX_CHUNKS 65536
 int rewy_stage_chunk_adjoint_static(const RewyBwdArgs* args, const RewyStageBuffers* buf, rewy_stream_t stream);
