@@ -83,6 +83,12 @@ typedef struct RewyBwdArgs {
   void* db_gate;       /* out_dtype [B,T,H,128] (GDN2) */
   void* dw_gate;       /* out_dtype [B,T,H,128] (GDN2) */
   float* dh0;          /* fp32 [B,H,128,128] or NULL (must be non-NULL iff h0 is) */
+  /* packed sequences (FLA's cu_seqlens): device int32 [num_seqs + 1] token offsets into a batch with B = 1, or NULL.
+   * Every sequence length must be a multiple of 64 (chunks never straddle sequences; a kernel that finds another
+   * length records it in the status word and leaves its sequence untouched); h0, dht and dh0 are then
+   * [num_seqs,H,128,128].  Only the two state scans look at sequence boundaries. */
+  const int32_t* cu_seqlens;
+  int32_t num_seqs;
   /* scratch */
   void* workspace;
   size_t workspace_bytes;
@@ -169,6 +175,8 @@ typedef struct RewyFwdArgs {
   void* v_new;             /* bf16 [B,T,H,128] */
   void* h;                 /* bf16 [B,T/64,H,128,128] */
   void* ctrl;              /* int32 [2] */
+  const int32_t* cu_seqlens; /* packed sequences, as in RewyBwdArgs (h0, final_state [num_seqs,H,128,128]); or NULL */
+  int32_t num_seqs;
 } RewyFwdArgs;
 int rewy_chunk_fwd(const RewyFwdArgs* args, rewy_stream_t stream);
 /* Chunk-local cumulative sum in log2 units of a scalar per-head gate x [B,T,H] (BF16 or FP32), FLA chunk_local_cumsum

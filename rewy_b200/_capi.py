@@ -39,6 +39,7 @@ class BwdArgs(ctypes.Structure):
         ("w", c_void_p), ("qg", c_void_p), ("kg", c_void_p), ("v_new", c_void_p), ("h", c_void_p),
         ("dq", c_void_p), ("dk", c_void_p), ("dv", c_void_p), ("dg", c_void_p), ("dbeta", c_void_p),
         ("db_gate", c_void_p), ("dw_gate", c_void_p), ("dh0", c_void_p),
+        ("cu_seqlens", c_void_p), ("num_seqs", c_int32),
         ("workspace", c_void_p), ("workspace_bytes", c_size_t),
     ]
 
@@ -47,7 +48,7 @@ class FwdArgs(ctypes.Structure):
     _fields_ = [("family", c_int32), ("B", c_int32), ("T", c_int32), ("H", c_int32), ("state_v_first", c_int32),
                 ("scale", c_float)] + [(n, c_void_p) for n in (
                     "q", "k", "v", "g", "beta", "b_gate", "w_gate", "h0", "o", "final_state", "Aqk", "Akk", "w", "u", "qg",
-                    "kg", "v_new", "h", "ctrl")]
+                    "kg", "v_new", "h", "ctrl", "cu_seqlens")] + [("num_seqs", c_int32)]
 
 
 class StageBuffers(ctypes.Structure):

@@ -35,7 +35,7 @@ def _family_bwd(family: int, policy: int, out_f32: bool, intra_passes: int, stat
                 g: Optional[Tensor], beta: Optional[Tensor], b_gate: Optional[Tensor], w_gate: Optional[Tensor],
                 Aqk: Optional[Tensor], h0: Optional[Tensor], dht: Optional[Tensor], w: Optional[Tensor],
                 qg: Optional[Tensor], kg: Optional[Tensor], v_new: Optional[Tensor], h: Optional[Tensor],
-                ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+                cu_seqlens: Optional[Tensor]) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
     """(dq, dk, dv, dg, dbeta, db_gate, dw_gate, dh0); outputs a family does not have are empty tensors.
     Tensors must be contiguous, on one CUDA device, in the dtypes of RewyBwdArgs."""
     lib = _capi.load()
@@ -51,7 +51,7 @@ def _family_bwd(family: int, policy: int, out_f32: bool, intra_passes: int, stat
         dbeta=torch.empty((B, T, H), dtype=torch.float32, device=dev) if not vector_gates else None,
         db_gate=torch.empty(shape, dtype=odt, device=dev) if vector_gates else None,
         dw_gate=torch.empty(shape, dtype=odt, device=dev) if vector_gates else None,
-        dh0=torch.empty((B, H, 128, 128), dtype=torch.float32, device=dev) if h0 is not None else None,
+        dh0=torch.empty_like(h0) if h0 is not None else None,   # [B,H,128,128], or [sequences,H,128,128] when packed
     )
     a = _capi.BwdArgs()
     a.family, a.policy, a.B, a.T, a.H = family, policy, B, T, H
@@ -59,6 +59,8 @@ def _family_bwd(family: int, policy: int, out_f32: bool, intra_passes: int, stat
     a.intra_passes = intra_passes
     a.state_v_first = int(state_v_first)
     a.scale = scale
+    if cu_seqlens is not None:   # int32, on the device, [sequences + 1]
+        a.cu_seqlens, a.num_seqs = _capi.ptr(cu_seqlens), cu_seqlens.numel() - 1
     for name, t in dict(q=q, k=k, v=v, d_o=d_o, Akk=Akk, g=g, beta=beta, b_gate=b_gate, w_gate=w_gate, Aqk=Aqk, h0=h0,
                         dht=dht, w=w, qg=qg, kg=kg, v_new=v_new, h=h).items():
         setattr(a, name, _capi.ptr(t))
@@ -77,7 +79,7 @@ def _family_bwd(family: int, policy: int, out_f32: bool, intra_passes: int, stat
 
 @_family_bwd.register_fake
 def _family_bwd_fake(family, policy, out_f32, intra_passes, state_v_first, scale, q, k, v, d_o, Akk, workspace, g, beta, b_gate, w_gate,
-                     Aqk, h0, dht, w, qg, kg, v_new, h):
+                     Aqk, h0, dht, w, qg, kg, v_new, h, cu_seqlens):
     B, T, H, _ = k.shape
     odt = torch.float32 if out_f32 else torch.bfloat16
     big = lambda dt: q.new_empty((B, T, H, 128), dtype=dt)
@@ -85,7 +87,7 @@ def _family_bwd_fake(family, policy, out_f32, intra_passes, state_v_first, scale
     vec = family == _capi.GDN2
     return (big(odt), big(odt), big(torch.bfloat16), torch.empty_like(g) if g is not None else none(),
             q.new_empty((B, T, H), dtype=torch.float32) if not vec else none(), big(odt) if vec else none(),
-            big(odt) if vec else none(), q.new_empty((B, H, 128, 128), dtype=torch.float32) if h0 is not None else none())
+            big(odt) if vec else none(), torch.empty_like(h0) if h0 is not None else none())
 
 
 def _unsupported(name, value, allowed=(None, False)):
@@ -105,12 +107,21 @@ def _check_common(q, k, v, do, chunk_size, cu_seqlens, cp_context, state_v_first
         raise RuntimeError("rewy_b200 backward: sequence length must be a positive multiple of 64")
     if chunk_size != 64:
         raise RuntimeError("rewy_b200 backward: chunk_size must be 64")
-    _unsupported("cu_seqlens", cu_seqlens, (None,))
+    if cu_seqlens is not None and B != 1:
+        raise RuntimeError("rewy_b200 backward: packed sequences (cu_seqlens) need a batch of 1")
     _unsupported("cp_context", cp_context, (None,))
     _unsupported("use_gate_in_kernel", use_gate_in_kernel)   # the gate activation is a wrapper stage (elementwise.py)
     if do.shape != v.shape:
         raise RuntimeError("rewy_b200 backward: do must have the shape of v")
     return B, T, H
+
+
+def _cu(cu_seqlens, device):
+    """cu_seqlens as the library takes them: int32, contiguous, on the device.  Lengths must be multiples of 64; the
+    operators check that on the host at forward time, the scan kernels again on the device."""
+    if cu_seqlens is None:
+        return None
+    return cu_seqlens.to(device=device, dtype=torch.int32).contiguous()
 
 
 def _c(t, dtype=None):
@@ -138,7 +149,7 @@ def _run(family, policy, B, T, H, scale, tensors, out_dtype, intra_passes, works
     r = torch.ops.rewy_b200.family_bwd(
         family, policy, out_f32, int(intra_passes or 0), bool(state_v_first), float(scale), t["q"], t["k"], t["v"], t["d_o"], t["Akk"],
         workspace, t["g"], t["beta"], t["b_gate"], t["w_gate"], t["Aqk"], t["h0"], t["dht"], t["w"], t["qg"], t["kg"],
-        t["v_new"], t["h"])
+        t["v_new"], t["h"], t.get("cu_seqlens"))
     names = ("dq", "dk", "dv", "dg", "dbeta", "db_gate", "dw_gate", "dh0")
     out = {n: (x if x.numel() else None) for n, x in zip(names, r)}
     if check_status:  # synchronises: reads the device status word at the start of the workspace
@@ -167,7 +178,7 @@ def kda_backward(q, k, v, beta, Aqk, Akk, scale, initial_state, do, dht, g=None,
         d_o=_c(do, torch.bfloat16), dht=_c(dht, torch.float32),
         w=_c(w, torch.bfloat16) if saved else None, qg=_c(qg, torch.bfloat16) if saved else None,
         kg=_c(kg, torch.bfloat16) if saved else None, v_new=_c(v_new, torch.bfloat16) if saved else None,
-        h=_c(h, torch.bfloat16) if saved else None)
+        h=_c(h, torch.bfloat16) if saved else None, cu_seqlens=_cu(cu_seqlens, q.device))
     out = _run(_capi.KDA, _capi.SAVED if saved else _capi.RECOMPUTE, B, T, H, scale, tensors, out_dtype,
                intra_passes, workspace, True, True, False, check_status, state_v_first)
     record("kda", "optimized_backward")
@@ -191,7 +202,7 @@ def gdn2_backward(q, k, v, b, w_gate, Aqk, Akk, scale, initial_state, do, dht, g
         h0=_c(initial_state, torch.float32), d_o=_c(do, torch.bfloat16), dht=_c(dht, torch.float32),
         w=_c(w_wy, torch.bfloat16) if saved else None, qg=_c(qg, torch.bfloat16) if saved else None,
         kg=_c(kg, torch.bfloat16) if saved else None, v_new=_c(v_new, torch.bfloat16) if saved else None,
-        h=_c(h, torch.bfloat16) if saved else None)
+        h=_c(h, torch.bfloat16) if saved else None, cu_seqlens=_cu(cu_seqlens, q.device))
     out = _run(_capi.GDN2, _capi.SAVED if saved else _capi.RECOMPUTE, B, T, H, scale, tensors, out_dtype,
                intra_passes, workspace, True, False, True, check_status, state_v_first)
     record("gdn2", "optimized_backward")
@@ -207,7 +218,7 @@ def gdn_backward(q, k, v, g, beta, A, scale, initial_state, do, dht, cu_seqlens=
     tensors = dict(
         q=_c(q), k=_c(k), v=_c(v), g=_c(g, torch.float32), beta=_c(beta, torch.float32), b_gate=None, w_gate=None,
         Aqk=None, Akk=_c(A, torch.bfloat16), h0=_c(initial_state, torch.float32), d_o=_c(do, torch.bfloat16),
-        dht=_c(dht, torch.float32), w=None, qg=None, kg=None, v_new=None, h=None)
+        dht=_c(dht, torch.float32), w=None, qg=None, kg=None, v_new=None, h=None, cu_seqlens=_cu(cu_seqlens, q.device))
     out = _run(_capi.GDN, _capi.RECOMPUTE, B, T, H, scale, tensors, out_dtype, intra_passes, workspace,
                True, True, False, check_status, state_v_first)
     record("gdn", "optimized_backward")
@@ -221,7 +232,7 @@ def delta_backward(q, k, v, beta, A, scale, initial_state, do, dht, cu_seqlens=N
     tensors = dict(
         q=_c(q), k=_c(k), v=_c(v), g=None, beta=_c(beta, torch.float32), b_gate=None, w_gate=None,
         Aqk=None, Akk=_c(A, torch.bfloat16), h0=_c(initial_state, torch.float32), d_o=_c(do, torch.bfloat16),
-        dht=_c(dht, torch.float32), w=None, qg=None, kg=None, v_new=None, h=None)
+        dht=_c(dht, torch.float32), w=None, qg=None, kg=None, v_new=None, h=None, cu_seqlens=_cu(cu_seqlens, q.device))
     out = _run(_capi.DELTA, _capi.RECOMPUTE, B, T, H, scale, tensors, out_dtype, intra_passes, workspace,
                False, True, False, check_status)
     record("delta", "optimized_backward")

@@ -82,6 +82,12 @@ int validate_common(const RewyBwdArgs* a, int family) {
   if (a->state_v_first && g_scan_variant.load(std::memory_order_relaxed) == 1)
     return fail(REWY_ERR_UNSUPPORTED, "the warp-MMA scan variant reads [K,V] states only (state_v_first)%s");
   if (a->B <= 0 || a->H <= 0) return fail(REWY_ERR_SHAPE, "B and H must be positive%s");
+  if (a->cu_seqlens != nullptr) {
+    if (a->B != 1 || a->num_seqs <= 0) return fail(REWY_ERR_SHAPE, "packed sequences need B = 1 and num_seqs > 0%s");
+    if ((long long)a->num_seqs * a->H > 65535) return fail(REWY_ERR_SHAPE, "num_seqs*H exceeds the grid limit 65535%s");
+    if (g_scan_variant.load(std::memory_order_relaxed) == 1)
+      return fail(REWY_ERR_UNSUPPORTED, "the warp-MMA scan variant does not take packed sequences%s");
+  }
   if (a->T < C || a->T % C != 0) return fail(REWY_ERR_SHAPE, "T must be a positive multiple of 64 (got %s%lld)", "", a->T);
   if ((long long)a->B * a->H > 65535) return fail(REWY_ERR_SHAPE, "B*H exceeds the grid limit 65535%s");
   REQUIRE_PTR(q); REQUIRE_PTR(k); REQUIRE_PTR(v); REQUIRE_PTR(Akk); REQUIRE_PTR(d_o);
@@ -132,12 +138,16 @@ cudaError_t run_prepare(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStr
 }
 
 cudaError_t run_fwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
-  if (g_scan_variant.load(std::memory_order_relaxed) == 1 || s.ctrl == nullptr) return launch_fwd_scan(a, s, st);
+  const bool warp_variant = g_scan_variant.load(std::memory_order_relaxed) == 1 || s.ctrl == nullptr;
+  if (warp_variant && (a.cu_seqlens != nullptr || a.state_v_first)) return cudaErrorNotSupported;  // tcgen05 scans only
+  if (warp_variant) return launch_fwd_scan(a, s, st);
   return launch_fwd_scan_tc(a, s, static_cast<int*>(s.ctrl), st);
 }
 
 cudaError_t run_bwd_scan(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
-  if (g_scan_variant.load(std::memory_order_relaxed) == 1 || s.ctrl == nullptr) return launch_bwd_scan(a, s, st);
+  const bool warp_variant = g_scan_variant.load(std::memory_order_relaxed) == 1 || s.ctrl == nullptr;
+  if (warp_variant && (a.cu_seqlens != nullptr || a.state_v_first)) return cudaErrorNotSupported;  // tcgen05 scans only
+  if (warp_variant) return launch_bwd_scan(a, s, st);
   return launch_bwd_scan_tc(a, s, static_cast<int*>(s.ctrl), st);
 }
 
@@ -211,6 +221,8 @@ int validate_stage(const RewyBwdArgs* a, const RewyStageBuffers* s) {
   if (a->family < REWY_DELTA || a->family > REWY_GDN2) return fail(REWY_ERR_UNSUPPORTED, "unknown family%s");
   if (a->B <= 0 || a->H <= 0 || a->T < C || a->T % C != 0) return fail(REWY_ERR_SHAPE, "bad B/T/H%s");
   if ((long long)a->B * a->H > 65535) return fail(REWY_ERR_SHAPE, "B*H exceeds the grid limit 65535%s");
+  if (a->cu_seqlens != nullptr && (a->B != 1 || a->num_seqs <= 0 || (long long)a->num_seqs * a->H > 65535))
+    return fail(REWY_ERR_SHAPE, "packed sequences need B = 1 and 0 < num_seqs*H <= 65535%s");
   return REWY_OK;
 }
 

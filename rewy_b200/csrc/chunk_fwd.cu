@@ -358,6 +358,8 @@ extern "C" int rewy_chunk_fwd(const RewyFwdArgs* a, rewy_stream_t stream) {
   if (a->B <= 0 || a->H <= 0 || a->T < C || a->T % C != 0) return report_error(REWY_ERR_SHAPE, "bad B/T/H");
   if ((long long)a->B * a->H > 65535) return report_error(REWY_ERR_SHAPE, "B*H exceeds the grid limit 65535");
   if (a->state_v_first != 0 && a->state_v_first != 1) return report_error(REWY_ERR_UNSUPPORTED, "state_v_first must be 0 or 1");
+  if (a->cu_seqlens != nullptr && (a->B != 1 || a->num_seqs <= 0 || (long long)a->num_seqs * a->H > 65535))
+    return report_error(REWY_ERR_SHAPE, "packed sequences need B = 1 and 0 < num_seqs*H <= 65535");
   FWD_REQUIRE(q); FWD_REQUIRE(k); FWD_REQUIRE(v); FWD_REQUIRE(o); FWD_REQUIRE(Aqk); FWD_REQUIRE(Akk); FWD_REQUIRE(w);
   FWD_REQUIRE(u); FWD_REQUIRE(qg); FWD_REQUIRE(kg); FWD_REQUIRE(v_new); FWD_REQUIRE(h); FWD_REQUIRE(ctrl);
   if (a->family != REWY_DELTA) FWD_REQUIRE(g);
@@ -384,7 +386,7 @@ extern "C" int rewy_chunk_fwd(const RewyFwdArgs* a, rewy_stream_t stream) {
   if (e == cudaSuccess) {
     RewyBwdArgs ba{};
     ba.family = a->family; ba.B = a->B; ba.T = a->T; ba.H = a->H; ba.state_v_first = a->state_v_first; ba.scale = a->scale;
-    ba.g = a->g; ba.h0 = a->h0;
+    ba.g = a->g; ba.h0 = a->h0; ba.cu_seqlens = a->cu_seqlens; ba.num_seqs = a->num_seqs;
     RewyStageBuffers sb{};
     sb.w = a->w; sb.u = a->u; sb.kg = a->kg; sb.h = a->h; sb.v_new = a->v_new;
     e = launch_fwd_scan_tc(ba, sb, static_cast<int*>(a->ctrl), st, a->final_state);

@@ -23,6 +23,7 @@ struct ScanParams {
   int* err;
   int T, H, NT;
   int svf;  // initial / final state tensors (dht, dh0) are stored value-first: [B,H,V,K]
+  const int* cu;  // packed sequences: device int32 [sequences + 1] token offsets (multiples of 64), or nullptr
   float scale;
 };
 
@@ -109,10 +110,28 @@ bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_consta
   const uint32_t sb = smem_u32(sm);
   const int tid = threadIdx.x, warp = tid >> 5;
   const int ch = tid & 127, wg = tid >> 7;  // channel (key row of S / value row of dR^T), column half
-  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
-  const int T = p.T, H = p.H, NT = p.NT;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;  // b: batch element, or sequence of a packed batch
+  const int H = p.H;
+  // token rows [bos, bos + 64 NT) of this sequence; its chunks are chunk0 .. chunk0 + NT - 1 of the h / dh tensors
+  int bos = b * p.T, NT = p.NT;
+  if (p.cu != nullptr) {
+    bos = p.cu[b];
+    const int len = p.cu[b + 1] - bos;
+    NT = len / C;
+    if (len < 0 || len % C != 0 || bos % C != 0) {  // outside the envelope: report, touch nothing
+      if (threadIdx.x == 0) atomicCAS(p.err, 0, 90);
+      return;
+    }
+  }
+  const int chunk0 = bos / C;
   const size_t ldt = (size_t)H * 128;
   const float scale = p.scale, inv_scale = 1.f / p.scale;
+  if (NT == 0) {  // empty sequence: the state gradient passes through unchanged
+    if (p.dh0 != nullptr)
+      for (int i = threadIdx.x; i < DK * DV; i += blockDim.x)
+        p.dh0[(size_t)bh * DK * DV + i] = p.dht == nullptr ? 0.f : p.dht[(size_t)bh * DK * DV + i];
+    return;
+  }
 
   if (tid == 0) {
     for (int i = 0; i < 8; i++) mbar_init(&bars[i], 1);
@@ -136,7 +155,7 @@ bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_consta
     ph ^= 1u << bar;
   };
 
-  auto row_of = [&](int n) { return b * T + n * C; };
+  auto row_of = [&](int n) { return bos + n * C; };
   auto issue_l1 = [&](int n) {  // kg and Aqk of chunk n
     const int row0 = row_of(n);
     mbar_expect_tx(&bars[B_L1], 16384 + 8192);
@@ -237,7 +256,7 @@ bwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmKg, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     if (tid == 0) {
-      const int hrow0 = ((b * NT + n) * H + h) * 128;
+      const int hrow0 = ((chunk0 + n) * H + h) * 128;
       if (alive) {
         for (int pn = 0; pn < 2; pn++) tma_store_2d(&tmDH, 64 * pn, hrow0, sm + SS::DHHI + pn * 16384);
         bulk_commit();
@@ -362,6 +381,7 @@ struct FwdParams {
   int* err;
   int T, H, NT;
   int svf;  // h0 is stored value-first: [B,H,V,K]
+  const int* cu;  // packed sequences: device int32 [sequences + 1] token offsets (multiples of 64), or nullptr
 };
 struct FS {
   static constexpr uint32_t W = 0;                // [64 i][128 k] two panels   16 KB
@@ -387,9 +407,26 @@ fwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const uint32_t sb = smem_u32(sm);
   const int tid = threadIdx.x, warp = tid >> 5;
   const int ch = tid & 127, wg = tid >> 7;
-  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
-  const int T = p.T, H = p.H, NT = p.NT;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;  // b: batch element, or sequence of a packed batch
+  const int H = p.H;
+  int bos = b * p.T, NT = p.NT;
+  if (p.cu != nullptr) {
+    bos = p.cu[b];
+    const int len = p.cu[b + 1] - bos;
+    NT = len / C;
+    if (len < 0 || len % C != 0 || bos % C != 0) {  // outside the envelope: report, touch nothing
+      if (threadIdx.x == 0) atomicCAS(p.err, 0, 91);
+      return;
+    }
+  }
+  const int chunk0 = bos / C;
   const size_t ldt = (size_t)H * 128;
+  if (NT == 0) {  // empty sequence: the state passes through unchanged
+    if (p.final_state != nullptr)
+      for (int i = threadIdx.x; i < DK * DV; i += blockDim.x)
+        p.final_state[(size_t)bh * DK * DV + i] = p.h0 == nullptr ? 0.f : p.h0[(size_t)bh * DK * DV + i];
+    return;
+  }
 
   if (tid == 0) {
     for (int i = 0; i < 8; i++) mbar_init(&bars[i], 1);
@@ -411,7 +448,7 @@ fwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     if (alive) alive = mbar_wait(&bars[bar], (ph >> bar) & 1u, p.err, code);
     ph ^= 1u << bar;
   };
-  auto row_of = [&](int n) { return b * T + n * C; };
+  auto row_of = [&](int n) { return bos + n * C; };
   auto load2 = [&](uint32_t dst, const CUtensorMap* m, int n, int bar) {
     mbar_expect_tx(&bars[bar], 16384);
     for (int pn = 0; pn < 2; pn++) tma_load_2d(sm + dst + pn * 8192, m, h * 128 + 64 * pn, row_of(n), &bars[bar]);
@@ -487,7 +524,7 @@ fwd_scan_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     if (tid == 0) {
-      const int hrow0 = ((b * NT + n) * H + h) * 128;
+      const int hrow0 = ((chunk0 + n) * H + h) * 128;
       if (alive) {
         for (int pn = 0; pn < 2; pn++) tma_store_2d(&tmH, 64 * pn, hrow0, sm + FS::HT + pn * 16384);
         bulk_commit();
@@ -621,11 +658,12 @@ cudaError_t launch_bwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, 
   if (!ok) return cudaErrorInvalidValue;
   ScanParams p;
   p.g = a.g; p.dht = a.dht; p.dR = (bf16*)s.dR; p.dRlo = (bf16*)s.dR_lo; p.dh0 = a.dh0; p.err = err;
-  p.T = T; p.H = H; p.NT = NT; p.svf = a.state_v_first; p.scale = a.scale;
+  p.T = T; p.H = H; p.NT = NT; p.svf = a.state_v_first; p.cu = a.cu_seqlens; p.scale = a.scale;
+  const int seqs = a.cu_seqlens != nullptr ? a.num_seqs : B;  // one CTA per (sequence, head)
   switch (gate_mode_of(a.family)) {
-    case GATE_NONE: return run<GATE_NONE>(tm, p, B * H, st);
-    case GATE_SCALAR: return run<GATE_SCALAR>(tm, p, B * H, st);
-    default: return run<GATE_VECTOR>(tm, p, B * H, st);
+    case GATE_NONE: return run<GATE_NONE>(tm, p, seqs * H, st);
+    case GATE_SCALAR: return run<GATE_SCALAR>(tm, p, seqs * H, st);
+    default: return run<GATE_VECTOR>(tm, p, seqs * H, st);
   }
 }
 
@@ -642,10 +680,12 @@ cudaError_t launch_fwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, 
   if (!ok) return cudaErrorInvalidValue;
   FwdParams p;
   p.g = a.g; p.h0 = a.h0; p.final_state = final_state; p.v_new = (bf16*)s.v_new; p.err = err; p.T = T; p.H = H; p.NT = NT; p.svf = a.state_v_first;
+  p.cu = a.cu_seqlens;
+  const int seqs = a.cu_seqlens != nullptr ? a.num_seqs : B;  // one CTA per (sequence, head)
   switch (gate_mode_of(a.family)) {
-    case GATE_NONE: return run_fwd<GATE_NONE>(tm, p, B * H, st);
-    case GATE_SCALAR: return run_fwd<GATE_SCALAR>(tm, p, B * H, st);
-    default: return run_fwd<GATE_VECTOR>(tm, p, B * H, st);
+    case GATE_NONE: return run_fwd<GATE_NONE>(tm, p, seqs * H, st);
+    case GATE_SCALAR: return run_fwd<GATE_SCALAR>(tm, p, seqs * H, st);
+    default: return run_fwd<GATE_VECTOR>(tm, p, seqs * H, st);
   }
 }
 

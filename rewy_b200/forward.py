@@ -36,13 +36,14 @@ def _bf(x):
 
 @torch.no_grad()
 def chunk_forward(op, q, k, v, g=None, beta=None, b=None, w=None, scale=None, initial_state=None,
-                  output_final_state=True, g_is_cumsum=False, state_v_first=False, check_status=False):
+                  output_final_state=True, g_is_cumsum=False, state_v_first=False, check_status=False, cu_seqlens=None):
     """CUDA forward.  Returns dict(o, final_state, g_cumsum, Aqk, Akk, w, u, qg, kg, v_new, h).
 
     q,k,v BF16 [B,T,H,128]; g per-step natural-log gate ([B,T,H] for 'gdn', [B,T,H,128] for 'kda'/'gdn2', None for
     'delta') or, with ``g_is_cumsum``, already the chunk-local cumulative gate in log2 units; beta [B,T,H] or
     (b [B,T,H,128], w [B,T,H,128]) for 'gdn2'; ``state_v_first``: initial and final state are [B,H,V,K];
-    ``check_status`` synchronises and raises if a kernel gave up on a bounded wait."""
+    ``check_status`` synchronises and raises if a kernel gave up on a bounded wait; ``cu_seqlens`` (int tensor
+    [sequences + 1], lengths multiples of 64, batch of 1): packed sequences, states are [sequences,H,128,128]."""
     from . import _capi, elementwise
     if not q.is_cuda:
         raise RuntimeError("rewy_b200 chunk_forward needs CUDA tensors (there is no CPU fallback); "
@@ -72,7 +73,11 @@ def chunk_forward(op, q, k, v, g=None, beta=None, b=None, w=None, scale=None, in
         a64 = lambda: torch.empty(B, T, H, 64, dtype=torch.bfloat16, device=dev)
         out = dict(o=big(), Aqk=a64(), Akk=a64(), w=big(), u=big(), qg=big(), kg=big(), v_new=big(),
                    h=torch.empty(B, T // CHUNK, H, 128, 128, dtype=torch.bfloat16, device=dev))
-        final = torch.empty(B, H, 128, 128, dtype=torch.float32, device=dev) if output_final_state else None
+        cu = None if cu_seqlens is None else cu_seqlens.to(device=dev, dtype=torch.int32).contiguous()
+        if cu is not None and B != 1:
+            raise ValueError("chunk_forward: packed sequences (cu_seqlens) need a batch of 1")
+        nseq = B if cu is None else cu.numel() - 1
+        final = torch.empty(nseq, H, 128, 128, dtype=torch.float32, device=dev) if output_final_state else None
         ctrl = torch.empty(2, dtype=torch.int32, device=dev)
         a = _capi.FwdArgs()
         a.family, a.B, a.T, a.H, a.state_v_first, a.scale = _capi.FAMILY_ID[op], B, T, H, int(bool(state_v_first)), float(scale)
@@ -83,6 +88,8 @@ def chunk_forward(op, q, k, v, g=None, beta=None, b=None, w=None, scale=None, in
         for name, t in out.items():
             setattr(a, name, _capi.ptr(t))
         a.final_state, a.ctrl = _capi.ptr(final), _capi.ptr(ctrl)
+        if cu is not None:
+            a.cu_seqlens, a.num_seqs = _capi.ptr(cu), nseq
         _capi.check(lib.rewy_chunk_fwd(a, _capi.current_stream(dev)), "rewy_chunk_fwd")
         if check_status:
             _capi.check(lib.rewy_device_status(_capi.ptr(ctrl), _capi.current_stream(dev)), "device status (forward)")

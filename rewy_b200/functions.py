@@ -25,7 +25,8 @@ def _cumulative_gate(g, A_log=None, dt_bias=None):
 class ChunkKDAFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
-                use_gate_in_kernel, use_beta_sigmoid_in_kernel, allow_neg_eigval, disable_recompute, state_v_first):
+                use_gate_in_kernel, use_beta_sigmoid_in_kernel, allow_neg_eigval, disable_recompute, state_v_first,
+                cu_seqlens):
         q_rstd = k_rstd = None
         if use_qk_l2norm_in_kernel:
             q, q_rstd = _ew.l2norm_fwd(q)
@@ -37,11 +38,12 @@ class ChunkKDAFunction(torch.autograd.Function):
         # one pass; otherwise g is the per-step natural-log decay
         g_cumsum = _cumulative_gate(g, A_log if use_gate_in_kernel else None, dt_bias if use_gate_in_kernel else None)
         f = chunk_forward("kda", q, k, v, g=g_cumsum, beta=beta, scale=scale, initial_state=initial_state,
-                          output_final_state=output_final_state, g_is_cumsum=True, state_v_first=state_v_first)
+                          output_final_state=output_final_state, g_is_cumsum=True, state_v_first=state_v_first,
+                          cu_seqlens=cu_seqlens)
         keep = (lambda x: x) if disable_recompute else (lambda x: None)
         ctx.save_for_backward(q, q_rstd, k, k_rstd, v, g_cumsum, g, beta_raw, beta, A_log, dt_bias, f["Aqk"], f["Akk"],
                               keep(f["w"]), keep(f["u"]), keep(f["qg"]), keep(f["kg"]), keep(f["v_new"]),
-                              keep(f["h"]), initial_state)
+                              keep(f["h"]), initial_state, cu_seqlens)
         ctx.scale, ctx.disable_recompute = scale, disable_recompute
         ctx.use_qk_l2norm_in_kernel, ctx.use_beta_sigmoid_in_kernel = use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel
         ctx.use_gate_in_kernel, ctx.allow_neg_eigval, ctx.state_v_first = use_gate_in_kernel, allow_neg_eigval, state_v_first
@@ -50,10 +52,10 @@ class ChunkKDAFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, dht):
         (q, q_rstd, k, k_rstd, v, g_cumsum, g_input, beta_raw, beta, A_log, dt_bias, Aqk, Akk, w, u, qg, kg, v_new, h,
-         initial_state) = ctx.saved_tensors
+         initial_state, cu_seqlens) = ctx.saved_tensors
         dq, dk, dv, db, dg, dh0, _, _ = _bwd.kda_backward(
             q=q, k=k, v=v, beta=beta, Aqk=Aqk, Akk=Akk, scale=ctx.scale, initial_state=initial_state, do=do, dht=dht,
-            g=g_cumsum, state_v_first=ctx.state_v_first, disable_recompute=ctx.disable_recompute, w=w, u=u, qg=qg, kg=kg,
+            g=g_cumsum, state_v_first=ctx.state_v_first, cu_seqlens=cu_seqlens, disable_recompute=ctx.disable_recompute, w=w, u=u, qg=qg, kg=kg,
             v_new=v_new, h=h, out_dtype=torch.float32 if ctx.use_qk_l2norm_in_kernel else torch.bfloat16)
         dA = dbias = None
         if ctx.use_gate_in_kernel:
@@ -66,23 +68,25 @@ class ChunkKDAFunction(torch.autograd.Function):
         if ctx.use_beta_sigmoid_in_kernel:
             db = _ew.beta_sigmoid_bwd(beta_raw, db, 2.0 if ctx.allow_neg_eigval else 1.0)
         return (dq.to(q), dk.to(k), dv.to(v), dg.to(g_input), db.to(beta_raw), dA, dbias, None, dh0, None, None, None,
-                None, None, None, None)
+                None, None, None, None, None)
 
 
 class ChunkGDN2Function(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, b, w, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
-                disable_recompute, state_v_first):
+                disable_recompute, state_v_first, cu_seqlens):
         q_rstd = k_rstd = None
         if use_qk_l2norm_in_kernel:
             q, q_rstd = _ew.l2norm_fwd(q)
             k, k_rstd = _ew.l2norm_fwd(k)
         g_cumsum = _cumulative_gate(g)
         f = chunk_forward("gdn2", q, k, v, g=g_cumsum, b=b, w=w, scale=scale, initial_state=initial_state,
-                          output_final_state=output_final_state, g_is_cumsum=True, state_v_first=state_v_first)
+                          output_final_state=output_final_state, g_is_cumsum=True, state_v_first=state_v_first,
+                          cu_seqlens=cu_seqlens)
         keep = (lambda x: x) if disable_recompute else (lambda x: None)
         ctx.save_for_backward(q, q_rstd, k, k_rstd, v, g_cumsum, g, b, w, f["Aqk"], f["Akk"], keep(f["w"]),
-                              keep(f["u"]), keep(f["qg"]), keep(f["kg"]), keep(f["v_new"]), keep(f["h"]), initial_state)
+                              keep(f["u"]), keep(f["qg"]), keep(f["kg"]), keep(f["v_new"]), keep(f["h"]), initial_state,
+                              cu_seqlens)
         ctx.scale, ctx.disable_recompute, ctx.use_qk_l2norm_in_kernel = scale, disable_recompute, use_qk_l2norm_in_kernel
         ctx.state_v_first = state_v_first
         return f["o"].type_as(q), f["final_state"]
@@ -90,23 +94,23 @@ class ChunkGDN2Function(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, dht):
         (q, q_rstd, k, k_rstd, v, g_cumsum, g_input, b, w, Aqk, Akk, w_wy, u_wy, qg, kg, v_new, h,
-         initial_state) = ctx.saved_tensors
+         initial_state, cu_seqlens) = ctx.saved_tensors
         dq, dk, dv, db, dw, dg, dh0, _, _ = _bwd.gdn2_backward(
             q=q, k=k, v=v, b=b, w_gate=w, Aqk=Aqk, Akk=Akk, scale=ctx.scale, initial_state=initial_state, do=do,
-            dht=dht, g=g_cumsum, state_v_first=ctx.state_v_first, w_wy=w_wy, u_wy=u_wy, qg=qg, kg=kg, v_new=v_new, h=h,
+            dht=dht, g=g_cumsum, state_v_first=ctx.state_v_first, cu_seqlens=cu_seqlens, w_wy=w_wy, u_wy=u_wy, qg=qg, kg=kg, v_new=v_new, h=h,
             disable_recompute=ctx.disable_recompute,
             out_dtype=torch.float32 if ctx.use_qk_l2norm_in_kernel else torch.bfloat16)
         if ctx.use_qk_l2norm_in_kernel:
             dq = _ew.l2norm_bwd(q, q_rstd, dq)
             dk = _ew.l2norm_bwd(k, k_rstd, dk)
         return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg.to(g_input.dtype), db.to(b.dtype), dw.to(w.dtype),
-                None, dh0, None, None, None, None)
+                None, dh0, None, None, None, None, None)
 
 
 class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel,
-                use_beta_sigmoid_in_kernel, allow_neg_eigval, state_v_first):
+                use_beta_sigmoid_in_kernel, allow_neg_eigval, state_v_first, cu_seqlens):
         q_rstd = k_rstd = None
         if use_qk_l2norm_in_kernel:
             q, q_rstd = _ew.l2norm_fwd(q)
@@ -115,8 +119,8 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
         if use_beta_sigmoid_in_kernel:
             beta = _ew.beta_sigmoid_fwd(beta_raw, 2.0 if allow_neg_eigval else 1.0)
         f = chunk_forward("gdn", q, k, v, g=g, beta=beta, scale=scale, initial_state=initial_state,
-                          output_final_state=output_final_state, state_v_first=state_v_first)
-        ctx.save_for_backward(q, q_rstd, k, k_rstd, v, f["g_cumsum"], g, beta_raw, beta, f["Akk"], initial_state)
+                          output_final_state=output_final_state, state_v_first=state_v_first, cu_seqlens=cu_seqlens)
+        ctx.save_for_backward(q, q_rstd, k, k_rstd, v, f["g_cumsum"], g, beta_raw, beta, f["Akk"], initial_state, cu_seqlens)
         ctx.scale, ctx.use_qk_l2norm_in_kernel = scale, use_qk_l2norm_in_kernel
         ctx.use_beta_sigmoid_in_kernel, ctx.allow_neg_eigval = use_beta_sigmoid_in_kernel, allow_neg_eigval
         ctx.state_v_first = state_v_first
@@ -124,42 +128,50 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, do, dht):
-        q, q_rstd, k, k_rstd, v, g, g_input, beta_raw, beta, A, initial_state = ctx.saved_tensors
+        q, q_rstd, k, k_rstd, v, g, g_input, beta_raw, beta, A, initial_state, cu_seqlens = ctx.saved_tensors
         dq, dk, dv, db, dg, dh0, _, _ = _bwd.gdn_backward(
             q=q, k=k, v=v, g=g, beta=beta, A=A, scale=ctx.scale, initial_state=initial_state, do=do, dht=dht,
-            state_v_first=ctx.state_v_first,
+            state_v_first=ctx.state_v_first, cu_seqlens=cu_seqlens,
             out_dtype=torch.float32 if ctx.use_qk_l2norm_in_kernel else torch.bfloat16)
         if ctx.use_qk_l2norm_in_kernel:
             dq = _ew.l2norm_bwd(q, q_rstd, dq)
             dk = _ew.l2norm_bwd(k, k_rstd, dk)
         if ctx.use_beta_sigmoid_in_kernel:
             db = _ew.beta_sigmoid_bwd(beta_raw, db, 2.0 if ctx.allow_neg_eigval else 1.0)
-        return (dq.to(q), dk.to(k), dv.to(v), dg.to(g_input), db.to(beta_raw), None, dh0, None, None, None, None, None)
+        return (dq.to(q), dk.to(k), dv.to(v), dg.to(g_input), db.to(beta_raw), None, dh0, None, None, None, None, None,
+                None)
 
 
 class ChunkDeltaRuleFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, beta, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel):
+    def forward(ctx, q, k, v, beta, scale, initial_state, output_final_state, use_qk_l2norm_in_kernel, cu_seqlens):
         q_rstd = k_rstd = None
         if use_qk_l2norm_in_kernel:
             q, q_rstd = _ew.l2norm_fwd(q)
             k, k_rstd = _ew.l2norm_fwd(k)
         f = chunk_forward("delta", q, k, v, beta=beta, scale=scale, initial_state=initial_state,
-                          output_final_state=output_final_state)
-        ctx.save_for_backward(q, q_rstd, k, k_rstd, v, beta, f["Akk"], initial_state)
+                          output_final_state=output_final_state, cu_seqlens=cu_seqlens)
+        ctx.save_for_backward(q, q_rstd, k, k_rstd, v, beta, f["Akk"], initial_state, cu_seqlens)
         ctx.scale, ctx.use_qk_l2norm_in_kernel = scale, use_qk_l2norm_in_kernel
         return f["o"].to(q.dtype), f["final_state"]
 
     @staticmethod
     def backward(ctx, do, dht):
-        q, q_rstd, k, k_rstd, v, beta, A, initial_state = ctx.saved_tensors
+        q, q_rstd, k, k_rstd, v, beta, A, initial_state, cu_seqlens = ctx.saved_tensors
         dq, dk, dv, db, dh0 = _bwd.delta_backward(
             q=q, k=k, v=v, beta=beta, A=A, scale=ctx.scale, initial_state=initial_state, do=do, dht=dht,
+            cu_seqlens=cu_seqlens,
             out_dtype=torch.float32 if ctx.use_qk_l2norm_in_kernel else torch.bfloat16)
         if ctx.use_qk_l2norm_in_kernel:
             dq = _ew.l2norm_bwd(q, q_rstd, dq)
             dk = _ew.l2norm_bwd(k, k_rstd, dk)
-        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), db.to(beta.dtype), None, dh0, None, None
+        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), db.to(beta.dtype), None, dh0, None, None, None
+
+
+def _packed(cu_seqlens, q):
+    """cu_seqlens as an int32 device tensor (the dispatch layer has already checked that every length is a multiple
+    of 64), or None."""
+    return None if cu_seqlens is None else cu_seqlens.to(device=q.device, dtype=torch.int32).contiguous()
 
 
 def _common_checks(q, k, v, initial_state):
@@ -191,7 +203,7 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
         scale = k.shape[-1] ** -0.5
     return ChunkKDAFunction.apply(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state,
                                   use_qk_l2norm_in_kernel, use_gate_in_kernel, use_beta_sigmoid_in_kernel, allow_neg_eigval,
-                                  disable_recompute, state_v_first)
+                                  disable_recompute, state_v_first, _packed(cu_seqlens, q))
 
 
 @torch.compiler.disable
@@ -204,7 +216,7 @@ def chunk_gdn2(q, k, v, g, b, w, scale=None, initial_state=None, output_final_st
     if scale is None:
         scale = k.shape[-1] ** -0.5
     return ChunkGDN2Function.apply(q, k, v, g, b, w, scale, initial_state, output_final_state,
-                                   use_qk_l2norm_in_kernel, disable_recompute, state_v_first)
+                                   use_qk_l2norm_in_kernel, disable_recompute, state_v_first, _packed(cu_seqlens, q))
 
 
 @torch.compiler.disable
@@ -218,7 +230,7 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
         scale = k.shape[-1] ** -0.5
     return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state,
                                              use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel, allow_neg_eigval,
-                                             state_v_first)
+                                             state_v_first, _packed(cu_seqlens, q))
 
 
 @torch.compiler.disable
@@ -229,4 +241,4 @@ def chunk_delta_rule(q, k, v, beta, scale=None, initial_state=None, output_final
     if scale is None:
         scale = k.shape[-1] ** -0.5
     return ChunkDeltaRuleFunction.apply(q, k, v, beta, scale, initial_state, output_final_state,
-                                        use_qk_l2norm_in_kernel)
+                                        use_qk_l2norm_in_kernel, _packed(cu_seqlens, q))

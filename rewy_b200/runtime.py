@@ -106,8 +106,16 @@ def rejection_reason(op, arguments, device_types=("cuda",)):
         return "sequence length must be a positive multiple of 64"
     if arguments.get("chunk_size", 64) != 64:
         return "release envelope requires chunk_size=64"
-    if arguments.get("cu_seqlens") is not None:
-        return "packed/variable sequences are not release-validated"
+    cu = arguments.get("cu_seqlens")
+    if cu is not None:
+        # packed sequences: accepted when no chunk straddles two sequences (the reference's release envelope rejects
+        # them all: "packed/variable sequences are not release-validated")
+        host = arguments.get("cu_seqlens_cpu")
+        host = cu.detach().cpu() if host is None else host
+        lengths = host[1:] - host[:-1]
+        if q.shape[0] != 1 or host.numel() < 2 or int(host[0]) != 0 or int(host[-1]) != k.shape[1] \
+                or bool((lengths <= 0).any()) or bool((lengths % 64 != 0).any()):
+            return "packed sequences need a batch of 1 and lengths that are positive multiples of 64"
     if arguments.get("cp_context") is not None:
         return "context parallelism is not release-validated"
     if arguments.get("safe_gate", False):

@@ -473,6 +473,50 @@ def test_custom_op_passes_opcheck():
     ws = torch.empty(_capi.workspace_bytes(_capi.KDA, _capi.RECOMPUTE, 1, 128, 2), dtype=torch.uint8, device=DEV)
     args = (_capi.KDA, _capi.RECOMPUTE, True, 0, False, 128 ** -0.5, xs["q"], xs["k"], xs["v"], xs["do"], saved["Akk"], ws,
             saved["g_cumsum"], xs["beta"].float(), None, None, saved["Aqk"], xs["initial_state"], xs["dht"],
-            None, None, None, None, None)
+            None, None, None, None, None, None)
     torch.library.opcheck(torch.ops.rewy_b200.family_bwd.default, args,
                           test_utils=("test_schema", "test_faketensor"))
+
+
+@pytest.mark.parametrize("op,policy_saved", [("kda", True), ("kda", False), ("gdn", False)])
+def test_family_backward_replays_from_a_cuda_graph(op, policy_saved):
+    """The whole backward is capturable (no host synchronisation, no shape-dependent host reads, fixed workspace):
+    captured once after a warm-up call, replayed on new contents of the same buffers, it reproduces the eager results
+    bit for bit.  The reference times its operators the same way (research/operators/delta_algebra_20261024/common.py:28-61)."""
+    from rewy_b200 import backward as bw
+    xs = _inputs(op, B=2, T=256, H=2, seed=31)
+    saved = forward_saved(op, xs)
+    B, T, H, _ = xs["k"].shape
+    fam = _capi.FAMILY_ID[op]
+    ws = torch.empty(_capi.workspace_bytes(fam, _capi.SAVED if policy_saved else _capi.RECOMPUTE, B, T, H),
+                     dtype=torch.uint8, device=DEV)
+    do_buf = xs["do"].clone()
+
+    def call():
+        common = dict(q=xs["q"], k=xs["k"], v=xs["v"], scale=128 ** -0.5, initial_state=xs["initial_state"], do=do_buf,
+                      dht=xs["dht"], out_dtype=torch.bfloat16, workspace=ws)
+        if op == "kda":
+            return bw.kda_backward(beta=xs["beta"], Aqk=saved["Aqk"], Akk=saved["Akk"], g=saved["g_cumsum"],
+                                   disable_recompute=policy_saved, w=saved["w"], u=saved["u"], qg=saved["qg"],
+                                   kg=saved["kg"], v_new=saved["v_new"], h=saved["h"], **common)
+        return bw.gdn_backward(g=saved["g_cumsum"], beta=xs["beta"], A=saved["Akk"], **common)
+
+    side = torch.cuda.Stream(device=DEV)
+    side.wait_stream(torch.cuda.current_stream(DEV))
+    with torch.cuda.stream(side):
+        call()                                        # warm-up outside the capture (first-use set-up of the kernels)
+    torch.cuda.current_stream(DEV).wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = call()
+    do_new = (xs["do"].float() * -0.5 + 0.25).to(torch.bfloat16)
+    do_buf.copy_(do_new)
+    graph.replay()
+    torch.cuda.synchronize()
+    replayed = [t.clone() for t in outs if t is not None]
+    eager = [t for t in call() if t is not None]
+    torch.cuda.synchronize()
+    assert _capi.load().rewy_device_status(_capi.ptr(ws), _capi.current_stream(torch.device(DEV))) == 0
+    for a, b in zip(replayed, eager):
+        assert torch.isfinite(a.float()).all() and torch.equal(a, b)

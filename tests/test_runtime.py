@@ -58,7 +58,7 @@ def test_assert_used_reports_missing_backward():
     (lambda a: a.update(q=a["q"].float()), "BF16"),
     (lambda a: a.update(q=a["q"][:, :65], k=a["k"][:, :65], v=a["v"][:, :65]), "multiple of 64"),
     (lambda a: a.update(chunk_size=32), "chunk_size=64"),
-    (lambda a: a.update(cu_seqlens=torch.tensor([0, 128])), "packed/variable"),
+    (lambda a: a.update(cu_seqlens=torch.tensor([0, 100, 128])), "packed sequences need"),
     (lambda a: a.update(scale=0.5), "custom scale"),
     (lambda a: a.update(safe_gate=True), "safe_gate"),
     (lambda a: a.update(v=a["v"][..., :64]), "K=V=128"),
@@ -83,6 +83,19 @@ def test_fused_gate_and_value_first_states_follow_the_reference_envelope():
     assert rejection_reason("gdn", args, device_types=("cpu",)) == "GDN fused gate is not release-validated"
     assert rejection_reason("gdn2", args, device_types=("cpu",)) == "GDN2 fused gate is not release-validated"
     assert rejection_reason("gdn", dict(q=t, k=t, v=t, state_v_first=True), device_types=("cpu",)) is None
+
+
+def test_packed_sequences_are_accepted_when_no_chunk_straddles_two_sequences():
+    from rewy_b200.runtime import rejection_reason
+    t = torch.zeros(1, 256, 2, 128, dtype=torch.bfloat16)
+    ok = dict(q=t, k=t, v=t, cu_seqlens=torch.tensor([0, 64, 256]))
+    assert rejection_reason("kda", ok, device_types=("cpu",)) is None
+    assert rejection_reason("delta", dict(ok, cu_seqlens_cpu=torch.tensor([0, 128, 256])), device_types=("cpu",)) is None
+    for bad in ([0, 64, 200], [0, 256, 256], [64, 256], [0, 128]):
+        assert "packed sequences need" in rejection_reason("kda", dict(ok, cu_seqlens=torch.tensor(bad)), device_types=("cpu",))
+    two = torch.zeros(2, 256, 2, 128, dtype=torch.bfloat16)
+    assert "packed sequences need" in rejection_reason("kda", dict(q=two, k=two, v=two, cu_seqlens=torch.tensor([0, 256])),
+                                                       device_types=("cpu",))
 
 
 def test_rejection_on_cpu_tensors_is_device():
@@ -275,10 +288,10 @@ def test_custom_op_is_registered_with_a_shape_only_implementation():
     g = m(B, T, H, 128, dt=torch.float32)
     h0 = m(B, H, 128, 128, dt=torch.float32)
     r = backward._family_bwd_fake(_capi.KDA, _capi.RECOMPUTE, False, 0, False, 1.0, big, big, big, big, a64, ws, g,
-                                  m(B, T, H, dt=torch.float32), None, None, a64, h0, h0, None, None, None, None, None)
+                                  m(B, T, H, dt=torch.float32), None, None, a64, h0, h0, None, None, None, None, None, None)
     assert [tuple(x.shape) for x in r] == [(B, T, H, 128)] * 4 + [(B, T, H), (0,), (0,), (B, H, 128, 128)]
     assert r[0].dtype == torch.bfloat16 and r[3].dtype == torch.float32
     r = backward._family_bwd_fake(_capi.GDN2, _capi.SAVED, True, 0, True, 1.0, big, big, big, big, a64, ws, g, None, big, big,
-                                  a64, None, None, big, big, big, big, m(B, T // 64, H, 128, 128))
+                                  a64, None, None, big, big, big, big, m(B, T // 64, H, 128, 128), None)
     assert [tuple(x.shape) for x in r] == [(B, T, H, 128)] * 4 + [(0,)] + [(B, T, H, 128)] * 2 + [(0,)]
     assert r[0].dtype == torch.float32 and r[5].dtype == torch.float32
