@@ -21,7 +21,7 @@ EXPORTS = (
     "rewy_stage_prepare", "rewy_stage_fwd_scan", "rewy_stage_bwd_scan", "rewy_stage_chunk_adjoint",
     "rewy_stage_timing_enable", "rewy_stage_timing_read", "rewy_selftest_tensor_core", "rewy_selftest_bounded_wait",
     "rewy_device_status", "rewy_wide_chunk_count", "rewy_set_chunk_variant", "rewy_set_scan_variant",
-    "rewy_set_prepare_variant",
+    "rewy_set_prepare_variant", "rewy_set_scan_overlap",
     "rewy_stage_chunk_adjoint_static", "rewy_static_device_status",
     "rewy_l2norm_fwd", "rewy_l2norm_bwd", "rewy_beta_sigmoid_fwd", "rewy_beta_sigmoid_bwd", "rewy_gate_cumsum_fwd",
     "rewy_gate_act_bwd", "rewy_chunk_fwd", "rewy_scalar_gate_cumsum_fwd",
@@ -115,6 +115,8 @@ def load():
     lib.rewy_static_device_status.restype = c_int
     lib.rewy_set_scan_variant.argtypes = [c_int]
     lib.rewy_set_scan_variant.restype = c_int
+    lib.rewy_set_scan_overlap.argtypes = [c_int]
+    lib.rewy_set_scan_overlap.restype = c_int
     lib.rewy_set_prepare_variant.argtypes = [c_int]
     lib.rewy_set_prepare_variant.restype = c_int
     lib.rewy_set_chunk_variant.argtypes = [c_int]

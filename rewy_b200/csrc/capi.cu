@@ -168,6 +168,30 @@ cudaError_t run_chunk_adjoint(const RewyBwdArgs& a, const RewyStageBuffers& s, c
   return launch_chunk_adjoint_tc(a, s, static_cast<int*>(s.ctrl), st);
 }
 
+// Side stream and the two events of the fork/join around the forward scan: one set per host thread and device, created
+// at first use and kept for the life of the thread (host-side handles only, no device memory).  Per-thread sets keep
+// two host threads that drive the same device from waiting on each other's events.
+struct ForkJoin {
+  cudaStream_t side = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  bool ready = false, failed = false;
+};
+std::atomic<int> g_overlap_scans{1};  // 1: forward scan on a side stream, concurrent with the reverse scan
+thread_local ForkJoin g_fork_join[64];
+
+ForkJoin* fork_join_for_current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  ForkJoin& f = g_fork_join[dev];
+  if (!f.ready && !f.failed) {
+    f.failed = cudaStreamCreateWithFlags(&f.side, cudaStreamNonBlocking) != cudaSuccess ||
+               cudaEventCreateWithFlags(&f.fork, cudaEventDisableTiming) != cudaSuccess ||
+               cudaEventCreateWithFlags(&f.join, cudaEventDisableTiming) != cudaSuccess;
+    f.ready = !f.failed;
+  }
+  return f.ready ? &f : nullptr;
+}
+
 int check_cuda(cudaError_t e, const char* stage) {
   if (e == cudaSuccess) return REWY_OK;
   snprintf(g_error, sizeof(g_error), "%s: %s", stage, cudaGetErrorString(e));
@@ -206,10 +230,29 @@ int run_family(const RewyBwdArgs* a, int family, cudaStream_t st) {
   if (p.prepare) {
     if ((rc = check_cuda(run_prepare(*a, s, st), "prepare")) != REWY_OK) return rc;
     timing_mark(set, 1, st);
-    if ((rc = check_cuda(run_fwd_scan(*a, s, st), "forward state scan")) != REWY_OK) return rc;
+    // The forward scan (h, v_new: read by the chunk stage) and the reverse scan (reads qg, kg, w of the prepare stage
+    // only) do not depend on each other: the forward scan goes to a side stream and joins before the chunk stage.  One
+    // CTA of each fits an SM together (shared memory and TMEM), so two latency-bound chains share the machine.
+    ForkJoin* fj = g_overlap_scans.load(std::memory_order_relaxed) ? fork_join_for_current_device() : nullptr;
+    if (fj != nullptr) {
+      cudaError_t e = cudaEventRecord(fj->fork, st);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(fj->side, fj->fork, 0);
+      if (e == cudaSuccess) e = run_fwd_scan(*a, s, fj->side);
+      if (e == cudaSuccess) e = cudaEventRecord(fj->join, fj->side);
+      if ((rc = check_cuda(e, "forward state scan (side stream)")) != REWY_OK) return rc;
+      timing_mark(set, 2, st);
+      e = run_bwd_scan(*a, s, st);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(st, fj->join, 0);
+      if ((rc = check_cuda(e, "reverse state scan")) != REWY_OK) return rc;
+    } else {
+      if ((rc = check_cuda(run_fwd_scan(*a, s, st), "forward state scan")) != REWY_OK) return rc;
+      timing_mark(set, 2, st);
+      if ((rc = check_cuda(run_bwd_scan(*a, s, st), "reverse state scan")) != REWY_OK) return rc;
+    }
+  } else {
+    timing_mark(set, 2, st);
+    if ((rc = check_cuda(run_bwd_scan(*a, s, st), "reverse state scan")) != REWY_OK) return rc;
   }
-  timing_mark(set, 2, st);
-  if ((rc = check_cuda(run_bwd_scan(*a, s, st), "reverse state scan")) != REWY_OK) return rc;
   timing_mark(set, 3, st);
   if ((rc = check_cuda(run_chunk_adjoint(*a, s, st), "chunk adjoint")) != REWY_OK) return rc;
   timing_mark(set, 4, st);
@@ -353,6 +396,11 @@ int rewy_stage_timing_read(float* ms_sum, int* calls) {
 int rewy_set_scan_variant(int variant) {
   if (variant != 0 && variant != 1) return fail(REWY_ERR_UNSUPPORTED, "scan variant must be 0 or 1%s");
   g_scan_variant.store(variant, std::memory_order_relaxed);
+  return REWY_OK;
+}
+
+int rewy_set_scan_overlap(int enable) {
+  g_overlap_scans.store(enable != 0, std::memory_order_relaxed);
   return REWY_OK;
 }
 

@@ -520,3 +520,23 @@ def test_family_backward_replays_from_a_cuda_graph(op, policy_saved):
     assert _capi.load().rewy_device_status(_capi.ptr(ws), _capi.current_stream(torch.device(DEV))) == 0
     for a, b in zip(replayed, eager):
         assert torch.isfinite(a.float()).all() and torch.equal(a, b)
+
+
+@pytest.mark.parametrize("op", OPS)
+def test_concurrent_scans_give_the_same_gradients_as_sequential_ones(op):
+    """Recompute policy: the forward scan on the library's side stream (default) against every stage on the caller's
+    stream; the two scans share no tensor, so the results are bitwise equal."""
+    xs = _inputs(op, B=2, T=512, H=4, seed=77)
+    saved = forward_saved(op, xs)
+    lib = _capi.load()
+    try:
+        assert lib.rewy_set_scan_overlap(0) == 0
+        seq = _family_call(op, xs, saved, False)
+    finally:
+        lib.rewy_set_scan_overlap(1)
+    par = _family_call(op, xs, saved, False)
+    par2 = _family_call(op, xs, saved, False)
+    torch.cuda.synchronize()
+    for n, t in seq.items():
+        if torch.is_tensor(t):
+            assert torch.equal(t, par[n]) and torch.equal(t, par2[n]), (op, n)
