@@ -259,7 +259,7 @@ int rewy_set_chunk_variant(int variant);
  * word; without it the stage function uses the warp-MMA kernel), 1 warp-MMA kernel. */
 int rewy_set_scan_variant(int variant);
 /* Under the recompute policy (and always for the scalar families) the forward state scan and the reverse state scan are
- * independent; by default (1) a whole-family call enqueues the forward scan on a side stream of the library (one
+ * independent; by default (1) a whole-family call with at most 148 (sequence, head) pairs enqueues the forward scan on a side stream of the library (one
  * non-blocking stream and two events per host thread and device, created at the first such call) that forks from and joins the
  * caller's stream through events, so the two scans run concurrently and the call stays capturable in a CUDA graph.
  * 0 keeps every stage on the caller's stream.  Process-wide; no counterpart in the reference. */

@@ -233,7 +233,10 @@ int run_family(const RewyBwdArgs* a, int family, cudaStream_t st) {
     // The forward scan (h, v_new: read by the chunk stage) and the reverse scan (reads qg, kg, w of the prepare stage
     // only) do not depend on each other: the forward scan goes to a side stream and joins before the chunk stage.  One
     // CTA of each fits an SM together (shared memory and TMEM), so two latency-bound chains share the machine.
-    ForkJoin* fj = g_overlap_scans.load(std::memory_order_relaxed) ? fork_join_for_current_device() : nullptr;
+    // Worth it while both kernels together leave SMs idle (at most one CTA per SM each); at larger sizes both are bound
+    // by HBM and running them together gains nothing.
+    const long long scan_ctas = (long long)(a->cu_seqlens != nullptr ? a->num_seqs : a->B) * a->H;
+    ForkJoin* fj = g_overlap_scans.load(std::memory_order_relaxed) && scan_ctas <= 148 ? fork_join_for_current_device() : nullptr;
     if (fj != nullptr) {
       cudaError_t e = cudaEventRecord(fj->fork, st);
       if (e == cudaSuccess) e = cudaStreamWaitEvent(fj->side, fj->fork, 0);

@@ -4,7 +4,8 @@
 //   w = Akk (b k gamma), u = Akk (w_gate v), qg = q gamma, kg = k 2^(g_last - g)
 //   and, for the scalar-gate / ungated families, Aqk = scale tril((q k^T) 2^(g_i - g_j)).
 // Persistent CTAs walk over chunks (head fastest); two CTAs share an SM and hide each other's waits.  Per chunk:
-//   * one elected thread requests the k, v, q, Akk (and gate) tiles by TMA;
+//   * one elected thread requests the k, v, q, Akk (and gate) tiles by TMA (GDN2: the key gate lands in the tile that
+//     becomes kg; the value gate is read with plain 16-byte loads, which keeps the plan at 105 KB);
 //   * scalar families: q k^T runs first on the tiles as they landed (M=128 with only lanes 0..63 meaningful);
 //   * every thread turns 16-byte pieces of the k / v / q tiles IN PLACE into E = b k gamma, Z = w_gate v and qg (the
 //     tiles keep the 128-byte-swizzled layout TMA wrote, which is what the products and the tile stores read), and
@@ -21,6 +22,7 @@ using namespace tc;
 
 struct PrepParams {
   const float *g, *beta;
+  const bf16* wg;  // GDN2 value gate, read with plain 16-byte loads
   bf16* Aqk;
   int* err;
   int T, H, NT, total_chunks;
@@ -32,18 +34,16 @@ struct PS {
   static constexpr uint32_t KT = 0;                // k tile, 2 panels [64 t][64 k]; becomes E in place        16 KB
   static constexpr uint32_t VT = KT + 16384;       // v tile; becomes Z in place                               16 KB
   static constexpr uint32_t QT = VT + 16384;       // q tile; becomes qg in place                              16 KB
-  static constexpr uint32_t KGT = QT + 16384;      // kg tile, same layout                                     16 KB
+  static constexpr uint32_t KGT = QT + 16384;      // kg tile, same layout; GDN2: the key gate tile lands here 16 KB
+                                                   // first (each thread reads its piece of it before writing kg there)
   static constexpr uint32_t AK = KGT + 16384;      // Akk [64 i][64 j]                                         8 KB
   static constexpr uint32_t GT = AK + 8192;        // vector gate: 4 panels [64 t][32 k] FP32                  32 KB
   static constexpr uint32_t WO = GT;               // dense [64 t][128 k] BF16 output tiles of w and u take the gate
   static constexpr uint32_t UO = GT + 16384;       // tile once every thread has its factors
-  static constexpr uint32_t BGT = GT + 32768;      // GDN2: key gate tile                                      16 KB
-  static constexpr uint32_t WGT = BGT + 16384;     // GDN2: value gate tile                                    16 KB
-  static constexpr uint32_t ROWS = WGT + 16384;    // float[64] beta rows, float[64] scalar gate rows
+  static constexpr uint32_t ROWS = GT + 32768;     // float[64] beta rows, float[64] scalar gate rows
   static constexpr uint32_t BARS = ROWS + 512;
   static constexpr uint32_t TMEM = BARS + 64;
   static constexpr uint32_t TOTAL = TMEM + 64;
-  static constexpr uint32_t TOTAL_NO_VB = BGT + 512 + 64 + 64;  // without the two GDN2 gate tiles
 };
 constexpr uint32_t TM_W = 0, TM_U = 64, TM_AQK = 128;
 enum { PB_LOAD = 0, PB_AQK, PB_MMA, PB_COUNT };
@@ -66,16 +66,15 @@ __global__ void __launch_bounds__(TPB, 2)
 prepare_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                   const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmAkk,
                   const __grid_constant__ CUtensorMap tmG, const __grid_constant__ CUtensorMap tmBG,
-                  const __grid_constant__ CUtensorMap tmWG, const __grid_constant__ CUtensorMap tmQg,
+                  const __grid_constant__ CUtensorMap tmQg,
                   const __grid_constant__ CUtensorMap tmKg, const __grid_constant__ CUtensorMap tmW,
                   const __grid_constant__ CUtensorMap tmU, const PrepParams p) {
   extern __shared__ __align__(1024) unsigned char raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
-  constexpr uint32_t ROWS = VB ? PS::ROWS : PS::BGT;  // the plan without the GDN2 tiles ends earlier
-  float* sBeta = reinterpret_cast<float*>(sm + ROWS);
+  float* sBeta = reinterpret_cast<float*>(sm + PS::ROWS);
   float* sGs = sBeta + C;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + ROWS + 512);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + ROWS + 512 + 64);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + PS::BARS);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + PS::TMEM);
   const uint32_t sb = smem_u32(sm);
   const int tid = threadIdx.x, warp = tid >> 5;
   const int ch = tid & 127, half = tid >> 7;
@@ -88,7 +87,7 @@ prepare_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmQ); prefetch_tmap(&tmAkk);
     prefetch_tmap(&tmQg); prefetch_tmap(&tmKg); prefetch_tmap(&tmW); prefetch_tmap(&tmU);
     if (GATE == GATE_VECTOR) prefetch_tmap(&tmG);
-    if (VB) { prefetch_tmap(&tmBG); prefetch_tmap(&tmWG); }
+    if (VB) prefetch_tmap(&tmBG);
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, 256);
@@ -119,16 +118,13 @@ prepare_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 
     if (warp == 0) {
       if (leader) {
-        mbar_expect_tx(&bars[PB_LOAD], 3 * 16384 + 8192 + (GATE == GATE_VECTOR ? 32768 : 0) + (VB ? 2 * 16384 : 0));
+        mbar_expect_tx(&bars[PB_LOAD], 3 * 16384 + 8192 + (GATE == GATE_VECTOR ? 32768 : 0) + (VB ? 16384 : 0));
         tma_load_3d(sm + PS::KT, &tmK, h * 128, row0, 0, &bars[PB_LOAD]);
         tma_load_3d(sm + PS::VT, &tmV, h * 128, row0, 0, &bars[PB_LOAD]);
         tma_load_3d(sm + PS::QT, &tmQ, h * 128, row0, 0, &bars[PB_LOAD]);
         tma_load_2d(sm + PS::AK, &tmAkk, h * 64, row0, &bars[PB_LOAD]);
         if (GATE == GATE_VECTOR) tma_load_3d(sm + PS::GT, &tmG, h * 128, row0, 0, &bars[PB_LOAD]);
-        if (VB) {
-          tma_load_3d(sm + PS::BGT, &tmBG, h * 128, row0, 0, &bars[PB_LOAD]);
-          tma_load_3d(sm + PS::WGT, &tmWG, h * 128, row0, 0, &bars[PB_LOAD]);
-        }
+        if (VB) tma_load_3d(sm + PS::KGT, &tmBG, h * 128, row0, 0, &bars[PB_LOAD]);
       }
       __syncwarp();
     }
@@ -216,8 +212,8 @@ prepare_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         uint4 br = make_uint4(0, 0, 0, 0), wr = br;
         const float bs = VB ? 0.f : sBeta[r];
         if (VB) {
-          br = *reinterpret_cast<const uint4*>(sm + PS::BGT + off);
-          wr = *reinterpret_cast<const uint4*>(sm + PS::WGT + off);
+          br = *reinterpret_cast<const uint4*>(sm + PS::KGT + off);
+          wr = *reinterpret_cast<const uint4*>(p.wg + ((size_t)(row0 + r) * H + h) * 128 + c16 * 8);
         }
         const uint32_t* ku = reinterpret_cast<const uint32_t*>(&kr);
         const uint32_t* qu = reinterpret_cast<const uint32_t*>(&qr);
@@ -311,8 +307,7 @@ prepare_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   if (warp == 0) tmem_dealloc(tb, 256);
 }
 
-constexpr size_t PREP_TC_SMEM_VB = PS::TOTAL + 1024;
-constexpr size_t PREP_TC_SMEM = PS::TOTAL_NO_VB + 1024;
+constexpr size_t PREP_TC_SMEM = PS::TOTAL + 1024;
 static_assert(2 * (PREP_TC_SMEM + 1024) <= 233472, "two prepare CTAs must fit one SM");
 
 int sm_count_prepare() {
@@ -327,14 +322,12 @@ int sm_count_prepare() {
 
 template <int GATE, bool VB>
 cudaError_t run(const CUtensorMap* tm, const PrepParams& p, cudaStream_t st) {
-  const size_t smem = VB ? PREP_TC_SMEM_VB : PREP_TC_SMEM;
+  const size_t smem = PREP_TC_SMEM;
   cudaError_t e = ensure_dynamic_smem<prepare_tc_kernel<GATE, VB>>(smem);
   if (e != cudaSuccess) return e;
-  const int per_sm = VB ? 1 : 2;
-  const int cap = sm_count_prepare() * per_sm;
+  const int cap = sm_count_prepare() * 2;  // two CTAs per SM
   const int grid = p.total_chunks < cap ? p.total_chunks : cap;
-  prepare_tc_kernel<GATE, VB><<<grid, TPB, smem, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9],
-                                                      tm[10], p);
+  prepare_tc_kernel<GATE, VB><<<grid, TPB, smem, st>>>(tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[7], tm[8], tm[9], tm[10], p);
   count_launch();
   return cudaGetLastError();
 }
@@ -357,12 +350,10 @@ cudaError_t launch_prepare_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, i
             encode_tmap_2d(&tm[10], s.u, 2, cols, rows, pitch, 128, 64, false);
   tm[4] = tm[5] = tm[6] = tm[0];  // never dereferenced unless the family has the tensor
   if (ok && vector) ok = encode_tmap_panels(&tm[4], a.g, 4, cols, rows, (uint64_t)H * 512, 64, 4);
-  if (ok && vb)
-    ok = encode_tmap_panels(&tm[5], a.b_gate, 2, cols, rows, pitch, 64, 2) &&
-         encode_tmap_panels(&tm[6], a.w_gate, 2, cols, rows, pitch, 64, 2);
+  if (ok && vb) ok = encode_tmap_panels(&tm[5], a.b_gate, 2, cols, rows, pitch, 64, 2);
   if (!ok) return cudaErrorInvalidValue;
   PrepParams p;
-  p.g = a.g; p.beta = a.beta; p.Aqk = (bf16*)s.Aqk; p.err = err;
+  p.g = a.g; p.beta = a.beta; p.wg = (const bf16*)a.w_gate; p.Aqk = (bf16*)s.Aqk; p.err = err;
   p.T = T; p.H = H; p.NT = NT; p.total_chunks = B * H * NT; p.scale = a.scale;
   switch (a.family) {
     case REWY_DELTA: return run<GATE_NONE, false>(tm, p, st);
