@@ -264,8 +264,9 @@ int rewy_set_scan_variant(int variant);
  * caller's stream through events, so the two scans run concurrently and the call stays capturable in a CUDA graph.
  * 0 keeps every stage on the caller's stream.  Process-wide; no counterpart in the reference. */
 int rewy_set_scan_overlap(int enable);
-/* Same for the prepare stage: 0 (default) TMA + tcgen05 kernel (needs RewyStageBuffers.ctrl for its status word; without
- * it the stage function uses the warp-MMA kernel), 1 warp-MMA kernel. */
+/* Same for the prepare stage: 0 (default) the faster kernel per family as measured on B200 (TMA + tcgen05 for DeltaNet,
+ * GDN and KDA, warp-MMA for GDN2), 1 warp-MMA kernel, 2 TMA + tcgen05 kernel.  The tcgen05 kernel needs
+ * RewyStageBuffers.ctrl for its status word; without it the stage function uses the warp-MMA kernel. */
 int rewy_set_prepare_variant(int variant);
 
 /* Self-test of the tensor-core plumbing (no counterpart in the reference): one CTA pushes every shared-memory

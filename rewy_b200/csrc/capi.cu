@@ -130,10 +130,15 @@ void timing_mark(int set, int idx, cudaStream_t st) {
   g_timing.have[set][idx] = true;
 }
 
-std::atomic<int> g_prepare_variant{0};  // 0 = TMA + tcgen05 kernel, 1 = warp-MMA kernel
+std::atomic<int> g_prepare_variant{0};  // 0 = by measurement, 1 = warp-MMA kernel, 2 = TMA + tcgen05 kernel
 
+// Default choice, by measurement on B200: the TMA + tcgen05 kernel for DeltaNet, GDN and KDA (0.83 ms against 0.91 ms at
+// KDA B=8 T=8192 H=32); for GDN2, whose chunk reads seven operand tiles, the warp-MMA kernel with four CTAs per SM
+// keeps more loads in flight and is faster (4.2 ms against 5.3 ms at B=8 T=32768 H=32).
 cudaError_t run_prepare(const RewyBwdArgs& a, const RewyStageBuffers& s, cudaStream_t st) {
-  if (g_prepare_variant.load(std::memory_order_relaxed) == 1 || s.ctrl == nullptr) return launch_prepare(a, s, st);
+  const int variant = g_prepare_variant.load(std::memory_order_relaxed);
+  const bool warp = variant == 1 || s.ctrl == nullptr || (variant == 0 && a.family == REWY_GDN2);
+  if (warp) return launch_prepare(a, s, st);
   return launch_prepare_tc(a, s, static_cast<int*>(s.ctrl), st);
 }
 
@@ -408,7 +413,7 @@ int rewy_set_scan_overlap(int enable) {
 }
 
 int rewy_set_prepare_variant(int variant) {
-  if (variant != 0 && variant != 1) return fail(REWY_ERR_UNSUPPORTED, "prepare variant must be 0 or 1%s");
+  if (variant < 0 || variant > 2) return fail(REWY_ERR_UNSUPPORTED, "prepare variant must be 0, 1 or 2%s");
   g_prepare_variant.store(variant, std::memory_order_relaxed);
   return REWY_OK;
 }

@@ -66,7 +66,7 @@ def test_stage_prepare(op, variant):
     ctrl = torch.zeros(8, dtype=torch.int32, device=DEV)
     lib = _capi.load()
     try:
-        assert lib.rewy_set_prepare_variant(1 if variant == "warp_mma" else 0) == 0
+        assert lib.rewy_set_prepare_variant(1 if variant == "warp_mma" else 2) == 0
         before = lib.rewy_kernel_launch_count()
         call_stage("rewy_stage_prepare", a, stage_buffers(w=w, u=u, qg=qg, kg=kg, Aqk=aqk, ctrl=ctrl), DEV)
         assert lib.rewy_kernel_launch_count() == before + 1
