@@ -179,6 +179,8 @@ typedef struct RewyFwdArgs {
   int32_t num_seqs;
 } RewyFwdArgs;
 int rewy_chunk_fwd(const RewyFwdArgs* args, rewy_stream_t stream);
+/* Output kernel of the forward: 0 (default) TMA + tcgen05, 1 warp-MMA (cross-check).  Process-wide. */
+int rewy_set_forward_variant(int variant);
 /* Chunk-local cumulative sum in log2 units of a scalar per-head gate x [B,T,H] (BF16 or FP32), FLA chunk_local_cumsum
  * as used by chunk_gated_delta_rule_fwd (_compat/gdn.py:52-69). */
 int rewy_scalar_gate_cumsum_fwd(const void* x, int x_is_f32, float* g_cumsum, int32_t B, int32_t T, int32_t H,

@@ -24,7 +24,7 @@ EXPORTS = (
     "rewy_set_prepare_variant", "rewy_set_scan_overlap",
     "rewy_stage_chunk_adjoint_static", "rewy_static_device_status",
     "rewy_l2norm_fwd", "rewy_l2norm_bwd", "rewy_beta_sigmoid_fwd", "rewy_beta_sigmoid_bwd", "rewy_gate_cumsum_fwd",
-    "rewy_gate_act_bwd", "rewy_chunk_fwd", "rewy_scalar_gate_cumsum_fwd",
+    "rewy_gate_act_bwd", "rewy_chunk_fwd", "rewy_scalar_gate_cumsum_fwd", "rewy_set_forward_variant",
     "rewy_last_error", "rewy_version", "rewy_kernel_launch_count",
 )
 
@@ -115,6 +115,8 @@ def load():
     lib.rewy_static_device_status.restype = c_int
     lib.rewy_set_scan_variant.argtypes = [c_int]
     lib.rewy_set_scan_variant.restype = c_int
+    lib.rewy_set_forward_variant.argtypes = [c_int]
+    lib.rewy_set_forward_variant.restype = c_int
     lib.rewy_set_scan_overlap.argtypes = [c_int]
     lib.rewy_set_scan_overlap.restype = c_int
     lib.rewy_set_prepare_variant.argtypes = [c_int]

@@ -10,7 +10,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "csrc" / "build"
 LIB = PKG / "librewy_b200.so"
-SOURCES = ("capi.cu", "prepare.cu", "prepare_tc.cu", "state_scan.cu", "state_scan_tc.cu", "chunk_adjoint.cu", "chunk_adjoint_tc.cu", "tc_selftest.cu", "wrappers.cu", "chunk_fwd.cu")
+SOURCES = ("capi.cu", "prepare.cu", "prepare_tc.cu", "state_scan.cu", "state_scan_tc.cu", "chunk_adjoint.cu", "chunk_adjoint_tc.cu", "tc_selftest.cu", "wrappers.cu", "chunk_fwd.cu", "chunk_output_tc.cu")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "--expt-extended-lambda", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

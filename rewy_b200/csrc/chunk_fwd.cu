@@ -3,7 +3,8 @@
 //   chunk_fwd_local_kernel   one CTA per chunk: Akk = (I + tril(E Y^T, -1))^-1, Aqk = scale tril(Qg Y^T),
 //                            w = Akk E, u = Akk Z, qg, kg          (E = b k gamma, Y = k / gamma, Z = w v)
 //   fwd_scan_tc_kernel       (state_scan_tc.cu) h[n], v_new, final state
-//   chunk_output_kernel      one CTA per chunk: o = scale qg h[n] + Aqk v_new
+//   chunk_output_tc_kernel   (chunk_output_tc.cu, tcgen05) o = scale qg h[n] + Aqk v_new; chunk_output_kernel here is its
+//                            warp-MMA cross-check (rewy_set_forward_variant(1))
 // Replaces FLA's chunk_kda_fwd / chunk_gdn2_fwd / chunk_gated_delta_rule_fwd / chunk_delta_rule_fwd as the reference
 // binds them (src/fast_delta_rule/_compat/kda.py:89-113, gdn2.py:94-117, gdn.py:33-125, delta.py).
 //
@@ -14,6 +15,7 @@
 // use centred factors (they would leave the FP32 range): its two matrices are summed pair by pair on the CUDA cores,
 // sum_k q_ik k_jk 2^(G_ik - G_jk), like the exact pairwise path of the backward.  The unit lower-triangular inverse is
 // plain FP32 forward substitution, one thread per column with the column held in registers.
+#include <atomic>
 #include <cstdio>
 #include "warp_mma.cuh"
 
@@ -341,6 +343,8 @@ cudaError_t run_local(const FwdLocalParams& p, int B, cudaStream_t st) {
 
 bool bad16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; }
 
+std::atomic<int> g_forward_variant{0};  // output kernel: 0 = TMA + tcgen05, 1 = warp-MMA (cross-check)
+
 }  // namespace
 }  // namespace rewy
 
@@ -391,7 +395,9 @@ extern "C" int rewy_chunk_fwd(const RewyFwdArgs* a, rewy_stream_t stream) {
     sb.w = a->w; sb.u = a->u; sb.kg = a->kg; sb.h = a->h; sb.v_new = a->v_new;
     e = launch_fwd_scan_tc(ba, sb, static_cast<int*>(a->ctrl), st, a->final_state);
   }
-  if (e == cudaSuccess) {
+  if (e == cudaSuccess && g_forward_variant.load(std::memory_order_relaxed) == 0) {
+    e = launch_chunk_output_tc(*a, static_cast<int*>(a->ctrl), st);
+  } else if (e == cudaSuccess) {
     e = ensure_dynamic_smem<chunk_output_kernel>(OUTPUT_SMEM);
     if (e == cudaSuccess) {
       dim3 grid(a->T / C, a->B * a->H);
@@ -406,6 +412,12 @@ extern "C" int rewy_chunk_fwd(const RewyFwdArgs* a, rewy_stream_t stream) {
     snprintf(msg, sizeof(msg), "chunk forward: %s", cudaGetErrorString(e));
     return report_error(REWY_ERR_LAUNCH, msg);
   }
+  return REWY_OK;
+}
+
+extern "C" int rewy_set_forward_variant(int variant) {
+  if (variant != 0 && variant != 1) return report_error(REWY_ERR_UNSUPPORTED, "forward variant must be 0 or 1");
+  g_forward_variant.store(variant, std::memory_order_relaxed);
   return REWY_OK;
 }
 

@@ -32,6 +32,7 @@ cudaError_t launch_bwd_scan_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, 
 // followed by the warp-MMA kernel on the listed wide-span chunks; or the warp-MMA kernel on every chunk.
 cudaError_t launch_chunk_adjoint_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, int* ctrl, cudaStream_t st);
 cudaError_t launch_chunk_adjoint_warp(const RewyBwdArgs& a, const RewyStageBuffers& s, const int* list, cudaStream_t st);
+cudaError_t launch_chunk_output_tc(const RewyFwdArgs& a, int* err, cudaStream_t st);  // forward output, TMA + tcgen05
 void count_launch(int n = 1);
 int report_error(int code, const char* text);  // stores the text rewy_last_error() returns; gives back `code`
 // shape envelope + presence and 16-byte alignment of every pointer of a chunk-stage call (REWY_OK or an error code)

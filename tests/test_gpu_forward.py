@@ -59,6 +59,22 @@ def test_cuda_forward_matches_the_oracle_and_the_torch_statement(op, state):
     assert not bad, f"CUDA forward and torch statement disagree: {bad}"
 
 
+def test_output_kernel_variants_agree():
+    """The TMA + tcgen05 output kernel against its warp-MMA cross-check (same operands, FP32 accumulation)."""
+    from rewy_b200 import _capi
+    lib = _capi.load()
+    xs = make_inputs("gdn2", 2, 512, 3, seed=12, device=DEV)
+    tc = chunk_forward("gdn2", check_status=True, **_kw("gdn2", xs))
+    try:
+        assert lib.rewy_set_forward_variant(1) == 0
+        warp = chunk_forward("gdn2", check_status=True, **_kw("gdn2", xs))
+    finally:
+        lib.rewy_set_forward_variant(0)
+    assert torch.isfinite(tc["o"].float()).all()
+    assert nrmse(warp["o"], tc["o"]) < 1e-3, nrmse(warp["o"], tc["o"])
+    assert torch.equal(warp["h"], tc["h"]) and torch.equal(warp["v_new"], tc["v_new"])
+
+
 def test_cuda_forward_value_first_states_and_no_final_state():
     xs = make_inputs("kda", 1, 192, 3, seed=9, device=DEV)
     plain = chunk_forward("kda", check_status=True, **_kw("kda", xs))

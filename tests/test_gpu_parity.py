@@ -30,6 +30,7 @@ def _inputs(op, B=1, T=256, H=2, seed=42, **kw):
 
 
 def _report(errs, tol):
+    print("NRMSE", {n: float(f"{e:.3g}") for n, e in errs.items()}, "limit", tol)
     bad = {n: e for n, e in errs.items() if not (e <= (tol[n] if isinstance(tol, dict) else tol))}
     assert not bad, f"NRMSE above tolerance: {bad}; all: {errs}"
 
