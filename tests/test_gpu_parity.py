@@ -3,7 +3,9 @@ the FP64 CPU oracle on the same seeded inputs.
 
 Tolerances (normalised RMSE = ||got-ref||/||ref||):
   2e-3  for every gradient of the whole-family backward against the FP64 closed-form backward fed with the
-        same (BF16) saved tensors — the bound the operator is specified to;
+        same (BF16) saved tensors — the bound the operator is specified to — including the cases that run the exact
+        pairwise path on huge gate spans; 3e-3 only where dq/dk are compared after rounding to BF16 on a tiny problem
+        (the rounding floor itself is measured at the benchmark shapes in test_gpu_shapes.py);
   8e-3 / 2e-2 (gate, beta and vector-gate gradients) for the public autograd path against the FP64 token
         recurrence on the raw inputs — the reference's own acceptance limits
         (src/fast_delta_rule/validation.py:68-71).
@@ -117,9 +119,9 @@ def test_stage_reverse_scan(op):
     call_stage("rewy_stage_bwd_scan", a, stage_buffers(qg=saved["qg"], kg=saved["kg"], w=saved["w"], Aqk=saved["Aqk"],
                                                        dh=dh, dR=dR, dR_lo=dR_lo, ctrl=ctrl), DEV)
     assert ctrl[0].item() == 0, f"device status word {ctrl[0].item()}: a bounded wait gave up"
-    # dh is stored in BF16 (inter-stage contract), dR as a BF16 hi/lo pair
-    _report(dict(dh=nrmse(ref["dh"], dh), dR=nrmse(ref["dR"], dR.float() + dR_lo.float()),
-                 dh0=nrmse(ref["dh0"], dh0)), 3e-3)
+    # dh is stored in BF16 (inter-stage contract): compared in that dtype; dR is a BF16 hi/lo pair
+    _report(dict(dh=nrmse(ref["dh"].to(torch.bfloat16), dh), dR=nrmse(ref["dR"], dR.float() + dR_lo.float()),
+                 dh0=nrmse(ref["dh0"], dh0)), TOL)
 
 
 def _split(x):
@@ -261,7 +263,7 @@ def test_kda_edge_cases(case):
     for n, t in out.items():
         if torch.is_tensor(t):
             assert torch.isfinite(t.float()).all(), f"{n} not finite"
-    _report(errs, 4e-3 if case in ("strong_gate", "mixed_tiles") else TOL)
+    _report(errs, TOL)   # the pairwise path of strong_gate / mixed_tiles included (measured: dk 1.2e-3, dg 1.2e-3)
 
 
 @pytest.mark.parametrize("op", ("gdn2", "gdn"))
@@ -272,7 +274,7 @@ def test_strong_gate_pairwise_path(op):
     ref = oracle_backward(op, xs, saved)
     out = _family_call(op, xs, saved, op == "gdn2")
     errs = _grad_errs(op, ref, out)
-    _report(errs, 4e-3)
+    _report(errs, TOL)
 
 
 @pytest.mark.parametrize("rising", (False, True))
@@ -296,7 +298,7 @@ def test_scalar_gate_strong_decay_keeps_the_tensor_core_path(rising):
     out = dict(dq=r[0], dk=r[1], dv=r[2], dbeta=r[3], dg=r[4], dh0=r[5])
     count = lib.rewy_wide_chunk_count(_capi.ptr(ws), _capi.current_stream(torch.device(DEV)))
     assert count == (1 if rising else 0), count
-    _report(_grad_errs("gdn", ref, out), 4e-3)
+    _report(_grad_errs("gdn", ref, out), TOL)
 
 
 @pytest.mark.parametrize("op", OPS)
