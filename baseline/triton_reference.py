@@ -219,6 +219,11 @@ def main():
     if hasattr(reference_bwd, "_fdr_intra"):
         out["reference_intra_fallback_calls"] = reference_bwd._fdr_intra.fallback_calls
     out["fla_original"] = time_arm(fla_bwd, "FLA stock backward", False)
+    # the forward the reference runs is FLA's own, unchanged (src/fast_delta_rule/_compat/kda.py:89-113)
+    from fla.ops.kda import chunk as fla_chunk
+    kw = dict(q=xs["q"], k=xs["k"], v=xs["v"], g=xs["g"], beta=xs["beta"], scale=128 ** -0.5,
+              initial_state=xs["initial_state"], output_final_state=False, disable_recompute=saved)
+    out["fla_forward"] = time_arm(fla_chunk.chunk_kda_fwd, "FLA forward", False)
     print(json.dumps(out), flush=True)
     return 0
 

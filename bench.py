@@ -458,6 +458,31 @@ def main():
                        "call, pinned host inputs copied H2D and gradients copied D2H every step on three streams "
                        "(copy in, backward, copy out overlap)"}
 
+    # the forward that produces the saved set (not part of the metric: the reference's forward is FLA's, unchanged)
+    forward = None
+    if world == 1:
+        from rewy_b200.forward import chunk_forward
+        x = prob.xs
+
+        def fwd():
+            return chunk_forward(prob.op, x["q"], x["k"], x["v"], g=x.get("g"), beta=x.get("beta"), b=x.get("b"),
+                                 w=x.get("w"), initial_state=x.get("initial_state"), output_final_state=False)
+        try:
+            for _ in range(3):
+                fwd()
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record()
+            for _ in range(min(K, 10)):
+                fwd()
+            f1.record()
+            torch.cuda.synchronize()
+            fms = f0.elapsed_time(f1) / min(K, 10)
+            forward = {"ms_per_step": fms, "tokens_per_s": tokens / (fms * 1e-3),
+                       "note": "rewy_chunk_fwd incl. the gate cumsum and the allocation of the saved set by torch"}
+        except Exception as exc:  # e.g. out of memory beside the resident problem: report, keep the headline
+            forward = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+        torch.cuda.empty_cache()
+
     e2e = e2e_other = None
     if not args.no_e2e and prob.op == "kda":
         e2e = measure_e2e(head_saved)
@@ -531,7 +556,7 @@ def main():
                        "outputs": "dq,dk,dv (and GDN2's db,dw) BF16; dg,dbeta FP32"},
             "policies": policies, "token_heads_per_s": value * n_heads,
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "e2e_other_policy": e2e_other, "clocks": clocks,
-            "gpu_launches": launches, "families": families, "triton_baseline": triton_baseline,
+            "gpu_launches": launches, "forward": forward, "families": families, "triton_baseline": triton_baseline,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -49,20 +49,44 @@ __device__ __forceinline__ void split_store8(bf16* hi, bf16* lo, const float (&x
   *reinterpret_cast<uint4*>(lo) = make_uint4(l[0], l[1], l[2], l[3]);
 }
 
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&x)[8]) {
+  const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const float2 f = unpack_bf16(u[j]);
+    x[2 * j] = f.x;
+    x[2 * j + 1] = f.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
+  return make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+}
+__device__ __forceinline__ void load_gate8(const float* g, float (&x)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(g), b = *reinterpret_cast<const float4*>(g + 4);
+  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+
+// Shared memory holds four operand tiles only, so that two CTAs share an SM: the element-wise operands are built in
+// three passes over the chunk's inputs (the second and third read them again, from L2), each pass reusing the tiles
+// of the one before.
 template <int GATE, bool VECTOR_BETA>
-__global__ void __launch_bounds__(256) chunk_fwd_local_kernel(const FwdLocalParams p) {
+__global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sA = reinterpret_cast<bf16*>(smem_raw);            // [64][72]   Akk (BF16) once inverted
-  bf16* sE = sA + C * LD64;                                // [64][136]  b*k*gamma, later w
-  bf16* sZ = sE + C * LD128;                               // [64][136]  w_gate*v, later u
-  float* sL = reinterpret_cast<float*>(sZ + C * LD128);    // [64][68]   strictly lower part of E Y^T
+  float* sL = reinterpret_cast<float*>(sA + C * LD64);     // [64][68]   strictly lower part of E Y^T
   float* sG = sL + C * LDL;                                // [64]       scalar gate rows
   float* sGl = sG + C;                                     // [128]      last gate row of the chunk (vector gate)
   float* sCen = sGl + 128;                                 // [128]      per-channel centre of the gate (vector gate)
   float* sBeta = sCen + 128;                               // [64]       scalar beta rows
-  bf16* sT = reinterpret_cast<bf16*>(sBeta + C);           // operand tiles of the two A products, [64][136] each:
-  // vector gate: Qc hi, Qc lo, Ec hi, Ec lo, Yc hi, Yc lo;  scalar gate / none: q, k
+  bf16* sT = reinterpret_cast<bf16*>(sBeta + C);           // four tiles [64][136]:
+  //   vector gate, pass 1: Qc hi, Qc lo, Yc hi, Yc lo;  pass 2: Ec hi, Ec lo over the first two
+  //   scalar gate / none:  q, k
+  //   wide-span chunk:     q, k, and the FP32 gate rows [64][132] over the last two
+  //   last pass, all:      E = b k gamma and Z = w v in the last two (-> w, u)
   constexpr int TILE = C * LD128;
+  static_assert((size_t)C * LDG * sizeof(float) <= 2 * (size_t)TILE * sizeof(bf16), "gate rows fit two tiles");
+  bf16* sE = sT + 2 * TILE;
+  bf16* sZ = sT + 3 * TILE;
 
   const int n = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
   const int T = p.T, H = p.H;
@@ -91,144 +115,159 @@ __global__ void __launch_bounds__(256) chunk_fwd_local_kernel(const FwdLocalPara
   }
   // wide gate span somewhere in the chunk: no centred factors, exact pairwise sums instead (vector gate only)
   const bool wide = __syncthreads_or(wide_here ? 1 : 0) != 0;
-  float* sGf = reinterpret_cast<float*>(sT + 3 * TILE);  // [64][132] FP32 gate tile of a wide chunk
-
-  // element-wise operands, 8 columns (16 bytes of BF16) per thread-iteration
-  for (int i = tid; i < C * 16; i += blockDim.x) {
-    const int r = i >> 4, c = (i & 15) * 8;
-    const size_t go = base128 + (size_t)r * ldt + c;
-    const uint4 kr = *reinterpret_cast<const uint4*>(p.k + go);
-    const uint4 qr = *reinterpret_cast<const uint4*>(p.q + go);
-    const uint4 vr = *reinterpret_cast<const uint4*>(p.v + go);
-    float gg[8];
-    if (GATE == GATE_VECTOR) {
-      const float4 ga = *reinterpret_cast<const float4*>(p.g + go), gb = *reinterpret_cast<const float4*>(p.g + go + 4);
-      gg[0] = ga.x; gg[1] = ga.y; gg[2] = ga.z; gg[3] = ga.w; gg[4] = gb.x; gg[5] = gb.y; gg[6] = gb.z; gg[7] = gb.w;
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; j++) gg[j] = GATE == GATE_SCALAR ? sG[r] : 0.f;
-    }
-    uint4 br = make_uint4(0, 0, 0, 0), wr = br;
-    const float bs = VECTOR_BETA ? 0.f : sBeta[r];
-    if (VECTOR_BETA) {
-      br = *reinterpret_cast<const uint4*>(p.bg + go);
-      wr = *reinterpret_cast<const uint4*>(p.wg + go);
-    }
-    const uint32_t* ku = reinterpret_cast<const uint32_t*>(&kr);
-    const uint32_t* qu = reinterpret_cast<const uint32_t*>(&qr);
-    const uint32_t* vu = reinterpret_cast<const uint32_t*>(&vr);
-    const uint32_t* bu = reinterpret_cast<const uint32_t*>(&br);
-    const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wr);
-    float ev[8], zv[8], qv[8], kv[8];  // E = b k gamma, Z = w v, qg, kg (rounded to BF16 below)
-    float qc[8], ec[8], yc[8];          // centred operands of the A products (vector gate)
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-      const float2 kk2 = unpack_bf16(ku[j >> 1]), qq2 = unpack_bf16(qu[j >> 1]), vv2 = unpack_bf16(vu[j >> 1]);
-      const float kk = (j & 1) ? kk2.y : kk2.x, qq = (j & 1) ? qq2.y : qq2.x, vv = (j & 1) ? vv2.y : vv2.x;
-      float bb = bs, ww = bs;
-      if (VECTOR_BETA) {
-        const float2 b2 = unpack_bf16(bu[j >> 1]), w2 = unpack_bf16(wu[j >> 1]);
-        bb = (j & 1) ? b2.y : b2.x;
-        ww = (j & 1) ? w2.y : w2.x;
-      }
-      const float gj = gg[j];
-      const float gam = GATE == GATE_NONE ? 1.f : exp2f(gj);
-      const float glast = GATE == GATE_VECTOR ? sGl[c + j] : (GATE == GATE_SCALAR ? sG[C - 1] : 0.f);
-      ev[j] = bb * kk * gam;
-      zv[j] = vv * ww;
-      qv[j] = qq * gam;
-      kv[j] = kk * (GATE == GATE_NONE ? 1.f : exp2f(glast - gj));
-      if (GATE == GATE_VECTOR && !wide) {
-        const float al = exp2f(gj - sCen[c + j]);
-        qc[j] = qq * al;
-        ec[j] = bb * kk * al;
-        yc[j] = kk * __frcp_rn(al);
-      }
-    }
-    uint32_t eo[4], zo[4], qo[4], ko[4];
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-      eo[j] = pack_bf16(ev[2 * j], ev[2 * j + 1]);
-      zo[j] = pack_bf16(zv[2 * j], zv[2 * j + 1]);
-      qo[j] = pack_bf16(qv[2 * j], qv[2 * j + 1]);
-      ko[j] = pack_bf16(kv[2 * j], kv[2 * j + 1]);
-    }
-    *reinterpret_cast<uint4*>(sE + r * LD128 + c) = make_uint4(eo[0], eo[1], eo[2], eo[3]);
-    *reinterpret_cast<uint4*>(sZ + r * LD128 + c) = make_uint4(zo[0], zo[1], zo[2], zo[3]);
-    *reinterpret_cast<uint4*>(p.qg + go) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
-    *reinterpret_cast<uint4*>(p.kg + go) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
-    if (GATE == GATE_VECTOR && !wide) {
-      split_store8(sT + 0 * TILE + r * LD128 + c, sT + 1 * TILE + r * LD128 + c, qc);
-      split_store8(sT + 2 * TILE + r * LD128 + c, sT + 3 * TILE + r * LD128 + c, ec);
-      split_store8(sT + 4 * TILE + r * LD128 + c, sT + 5 * TILE + r * LD128 + c, yc);
-    } else {
-      *reinterpret_cast<uint4*>(sT + 0 * TILE + r * LD128 + c) = qr;
-      *reinterpret_cast<uint4*>(sT + 1 * TILE + r * LD128 + c) = kr;
-      if (GATE == GATE_VECTOR) {  // wide chunk: raw key gate and gate rows for the pairwise sums
-        if (VECTOR_BETA) *reinterpret_cast<uint4*>(sT + 2 * TILE + r * LD128 + c) = br;
-        *reinterpret_cast<float4*>(sGf + r * LDG + c) = make_float4(gg[0], gg[1], gg[2], gg[3]);
-        *reinterpret_cast<float4*>(sGf + r * LDG + c + 4) = make_float4(gg[4], gg[5], gg[6], gg[7]);
-      }
-    }
-  }
-  __syncthreads();
+  float* sGf = reinterpret_cast<float*>(sT + 2 * TILE);  // [64][132] FP32 gate rows of a wide chunk
 
   // ---- the two A products: Qc Yc^T (-> Aqk) and Ec Yc^T (-> strictly lower part of I + L) -------------------------
-  if (GATE == GATE_VECTOR && wide) {
-    // exact pairwise sums, thread = (row i, every fourth column j)
-    const bf16 *sQr = sT, *sKr = sT + TILE, *sBr = sT + 2 * TILE;
-    const int i = tid >> 2;
-    const float beta_i = VECTOR_BETA ? 0.f : sBeta[i];
-    for (int j = tid & 3; j < C; j += 4) {
-      float aq = 0.f, ak = 0.f;
-      if (j <= i) {
-        for (int kk = 0; kk < 128; kk++) {
-          const float f = exp2f(sGf[i * LDG + kk] - sGf[j * LDG + kk]) * bf2f(sKr[j * LD128 + kk]);
-          aq = fmaf(bf2f(sQr[i * LD128 + kk]), f, aq);
-          const float bi = VECTOR_BETA ? bf2f(sBr[i * LD128 + kk]) : beta_i;
-          ak = fmaf(bi * bf2f(sKr[i * LD128 + kk]), f, ak);
-        }
+  if (GATE == GATE_VECTOR && !wide) {
+    // pass 1: Qc = q alpha and Yc = k / alpha as BF16 hi/lo pairs (alpha = 2^(G - centre))
+    for (int i = tid; i < C * 16; i += blockDim.x) {
+      const int r = i >> 4, c = (i & 15) * 8;
+      const size_t go = base128 + (size_t)r * ldt + c;
+      float kk[8], qq[8], gg[8], qc[8], yc[8];
+      unpack8(*reinterpret_cast<const uint4*>(p.k + go), kk);
+      unpack8(*reinterpret_cast<const uint4*>(p.q + go), qq);
+      load_gate8(p.g + go, gg);
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const float al = exp2f(gg[j] - sCen[c + j]);
+        qc[j] = qq[j] * al;
+        yc[j] = kk[j] * __frcp_rn(al);
       }
-      p.Aqk[base64 + (size_t)i * H * 64 + j] = f2bf(p.scale * aq);
-      sL[i * LDL + j] = j < i ? ak : 0.f;
+      split_store8(sT + 0 * TILE + r * LD128 + c, sT + 1 * TILE + r * LD128 + c, qc);
+      split_store8(sT + 2 * TILE + r * LD128 + c, sT + 3 * TILE + r * LD128 + c, yc);
+    }
+    __syncthreads();
+    const Operand<false> Yh{sT + 2 * TILE, LD128}, Yl{sT + 3 * TILE, LD128};
+    {
+      const Operand<false> Qh{sT + 0 * TILE, LD128}, Ql{sT + 1 * TILE, LD128};
+      Tile<64, 64, 2, 4> aq;
+      aq.zero();
+      aq.mma<128>(Qh, Yh); aq.mma<128>(Ql, Yh); aq.mma<128>(Qh, Yl);
+      aq.for_each_pair([&](int r, int c, float& x0, float& x1) {
+        const float y0 = c <= r ? x0 * p.scale : 0.f, y1 = c + 1 <= r ? x1 * p.scale : 0.f;
+        *reinterpret_cast<uint32_t*>(p.Aqk + base64 + (size_t)r * H * 64 + c) = pack_bf16(y0, y1);
+      });
+    }
+    __syncthreads();  // every warp has read Qc
+    // pass 2: Ec = b k alpha over the Qc tiles
+    for (int i = tid; i < C * 16; i += blockDim.x) {
+      const int r = i >> 4, c = (i & 15) * 8;
+      const size_t go = base128 + (size_t)r * ldt + c;
+      float kk[8], gg[8], bb[8], ec[8];
+      unpack8(*reinterpret_cast<const uint4*>(p.k + go), kk);
+      load_gate8(p.g + go, gg);
+      if (VECTOR_BETA) unpack8(*reinterpret_cast<const uint4*>(p.bg + go), bb);
+      const float bs = VECTOR_BETA ? 0.f : sBeta[r];
+#pragma unroll
+      for (int j = 0; j < 8; j++) ec[j] = (VECTOR_BETA ? bb[j] : bs) * kk[j] * exp2f(gg[j] - sCen[c + j]);
+      split_store8(sT + 0 * TILE + r * LD128 + c, sT + 1 * TILE + r * LD128 + c, ec);
+    }
+    __syncthreads();
+    {
+      const Operand<false> Eh{sT + 0 * TILE, LD128}, El{sT + 1 * TILE, LD128};
+      Tile<64, 64, 2, 4> ak;
+      ak.zero();
+      ak.mma<128>(Eh, Yh); ak.mma<128>(El, Yh); ak.mma<128>(Eh, Yl);
+      ak.for_each_pair([&](int r, int c, float& x0, float& x1) {
+        sL[r * LDL + c] = c < r ? x0 : 0.f;
+        sL[r * LDL + c + 1] = c + 1 < r ? x1 : 0.f;
+      });
     }
   } else {
-    Tile<64, 64, 2, 4> aq, ak;
-    aq.zero();
-    ak.zero();
+    // raw q and k tiles (and, for a wide-span chunk, the gate rows)
+    for (int i = tid; i < C * 16; i += blockDim.x) {
+      const int r = i >> 4, c = (i & 15) * 8;
+      const size_t go = base128 + (size_t)r * ldt + c;
+      *reinterpret_cast<uint4*>(sT + 0 * TILE + r * LD128 + c) = *reinterpret_cast<const uint4*>(p.q + go);
+      *reinterpret_cast<uint4*>(sT + 1 * TILE + r * LD128 + c) = *reinterpret_cast<const uint4*>(p.k + go);
+      if (GATE == GATE_VECTOR) {
+        *reinterpret_cast<float4*>(sGf + r * LDG + c) = *reinterpret_cast<const float4*>(p.g + go);
+        *reinterpret_cast<float4*>(sGf + r * LDG + c + 4) = *reinterpret_cast<const float4*>(p.g + go + 4);
+      }
+    }
+    __syncthreads();
     if (GATE == GATE_VECTOR) {
-      const Operand<false> Qh{sT + 0 * TILE, LD128}, Ql{sT + 1 * TILE, LD128}, Eh{sT + 2 * TILE, LD128},
-          El{sT + 3 * TILE, LD128}, Yh{sT + 4 * TILE, LD128}, Yl{sT + 5 * TILE, LD128};
-      aq.mma<128>(Qh, Yh); aq.mma<128>(Ql, Yh); aq.mma<128>(Qh, Yl);
-      ak.mma<128>(Eh, Yh); ak.mma<128>(El, Yh); ak.mma<128>(Eh, Yl);
+      // exact pairwise sums, thread = (row i, every fourth column j)
+      const bf16 *sQr = sT, *sKr = sT + TILE;
+      const int i = tid >> 2;
+      const float beta_i = VECTOR_BETA ? 0.f : sBeta[i];
+      const bf16* bgi = p.bg + base128 + (size_t)i * ldt;  // key gate row of token i (vector beta)
+      for (int j = tid & 3; j < C; j += 4) {
+        float aq = 0.f, ak = 0.f;
+        if (j <= i) {
+          for (int kk = 0; kk < 128; kk++) {
+            const float f = exp2f(sGf[i * LDG + kk] - sGf[j * LDG + kk]) * bf2f(sKr[j * LD128 + kk]);
+            aq = fmaf(bf2f(sQr[i * LD128 + kk]), f, aq);
+            const float bi = VECTOR_BETA ? bf2f(bgi[kk]) : beta_i;
+            ak = fmaf(bi * bf2f(sKr[i * LD128 + kk]), f, ak);
+          }
+        }
+        p.Aqk[base64 + (size_t)i * H * 64 + j] = f2bf(p.scale * aq);
+        sL[i * LDL + j] = j < i ? ak : 0.f;
+      }
     } else {
       const Operand<false> Q{sT + 0 * TILE, LD128}, K{sT + 1 * TILE, LD128};
+      Tile<64, 64, 2, 4> aq, ak;
+      aq.zero();
+      ak.zero();
       aq.mma<128>(Q, K);
       ak.mma<128>(K, K);
-    }
-    aq.for_each_pair([&](int r, int c, float& x0, float& x1) {
-      float f0 = p.scale, f1 = p.scale;
-      if (GATE == GATE_SCALAR) {
-        f0 *= exp2f(sG[r] - sG[c <= r ? c : r]);
-        f1 *= exp2f(sG[r] - sG[c + 1 <= r ? c + 1 : r]);
-      }
-      const float y0 = c <= r ? x0 * f0 : 0.f, y1 = c + 1 <= r ? x1 * f1 : 0.f;
-      *reinterpret_cast<uint32_t*>(p.Aqk + base64 + (size_t)r * H * 64 + c) = pack_bf16(y0, y1);
-    });
-    ak.for_each_pair([&](int r, int c, float& x0, float& x1) {
-      float f0 = 1.f, f1 = 1.f;
-      if (GATE != GATE_VECTOR) {  // exact k k^T: beta and the pairwise gate factor go on afterwards
-        f0 = f1 = VECTOR_BETA ? 1.f : sBeta[r];
+      aq.for_each_pair([&](int r, int c, float& x0, float& x1) {
+        float f0 = p.scale, f1 = p.scale;
+        if (GATE == GATE_SCALAR) {
+          f0 *= exp2f(sG[r] - sG[c <= r ? c : r]);
+          f1 *= exp2f(sG[r] - sG[c + 1 <= r ? c + 1 : r]);
+        }
+        const float y0 = c <= r ? x0 * f0 : 0.f, y1 = c + 1 <= r ? x1 * f1 : 0.f;
+        *reinterpret_cast<uint32_t*>(p.Aqk + base64 + (size_t)r * H * 64 + c) = pack_bf16(y0, y1);
+      });
+      ak.for_each_pair([&](int r, int c, float& x0, float& x1) {
+        // exact k k^T: beta and the pairwise gate factor go on afterwards
+        float f0 = VECTOR_BETA ? 1.f : sBeta[r], f1 = f0;
         if (GATE == GATE_SCALAR) {
           f0 *= exp2f(sG[r] - sG[c < r ? c : r]);
           f1 *= exp2f(sG[r] - sG[c + 1 < r ? c + 1 : r]);
         }
-      }
-      sL[r * LDL + c] = c < r ? x0 * f0 : 0.f;
-      sL[r * LDL + c + 1] = c + 1 < r ? x1 * f1 : 0.f;
-    });
+        sL[r * LDL + c] = c < r ? x0 * f0 : 0.f;
+        sL[r * LDL + c + 1] = c + 1 < r ? x1 * f1 : 0.f;
+      });
+    }
   }
   __syncthreads();
+
+  // ---- last pass, by the threads that do not invert: E = b k gamma and Z = w v into the last two tiles, qg and kg
+  //      straight to global memory -----------------------------------------------------------------------------------
+  if (tid >= C) {
+    for (int i = tid - C; i < C * 16; i += 256 - C) {
+      const int r = i >> 4, c = (i & 15) * 8;
+      const size_t go = base128 + (size_t)r * ldt + c;
+      float kk[8], qq[8], vv[8], gg[8], bb[8], ww[8];
+      unpack8(*reinterpret_cast<const uint4*>(p.k + go), kk);
+      unpack8(*reinterpret_cast<const uint4*>(p.q + go), qq);
+      unpack8(*reinterpret_cast<const uint4*>(p.v + go), vv);
+      if (GATE == GATE_VECTOR) load_gate8(p.g + go, gg);
+      if (VECTOR_BETA) {
+        unpack8(*reinterpret_cast<const uint4*>(p.bg + go), bb);
+        unpack8(*reinterpret_cast<const uint4*>(p.wg + go), ww);
+      }
+      const float bs = VECTOR_BETA ? 0.f : sBeta[r];
+      float ev[8], zv[8], qv[8], kv[8];  // E = b k gamma, Z = w v, qg, kg (rounded to BF16 below)
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const float gj = GATE == GATE_VECTOR ? gg[j] : (GATE == GATE_SCALAR ? sG[r] : 0.f);
+        const float gam = GATE == GATE_NONE ? 1.f : exp2f(gj);
+        const float glast = GATE == GATE_VECTOR ? sGl[c + j] : (GATE == GATE_SCALAR ? sG[C - 1] : 0.f);
+        ev[j] = (VECTOR_BETA ? bb[j] : bs) * kk[j] * gam;
+        zv[j] = vv[j] * (VECTOR_BETA ? ww[j] : bs);
+        qv[j] = qq[j] * gam;
+        kv[j] = kk[j] * (GATE == GATE_NONE ? 1.f : exp2f(glast - gj));
+      }
+      *reinterpret_cast<uint4*>(sE + r * LD128 + c) = pack8(ev);
+      *reinterpret_cast<uint4*>(sZ + r * LD128 + c) = pack8(zv);
+      *reinterpret_cast<uint4*>(p.qg + go) = pack8(qv);
+      *reinterpret_cast<uint4*>(p.kg + go) = pack8(kv);
+    }
+  }
 
   // ---- Akk = (I + L)^-1: thread c solves column c by forward substitution (x[j] = 0 for j < c comes out by itself) ----
   if (tid < C) {
@@ -275,11 +314,9 @@ __global__ void __launch_bounds__(256) chunk_fwd_local_kernel(const FwdLocalPara
   }
 }
 
-constexpr size_t FWD_LOCAL_SMEM_FIXED = (size_t)(C * LD64 + 2 * C * LD128) * sizeof(bf16) +
-                                        (size_t)(C * LDL + C + 128 + 128 + C) * sizeof(float);
-constexpr size_t FWD_LOCAL_SMEM_VECTOR = FWD_LOCAL_SMEM_FIXED + (size_t)6 * C * LD128 * sizeof(bf16);
-constexpr size_t FWD_LOCAL_SMEM_SCALAR = FWD_LOCAL_SMEM_FIXED + (size_t)2 * C * LD128 * sizeof(bf16);
-static_assert(FWD_LOCAL_SMEM_VECTOR <= 232448, "shared memory plan of the forward chunk kernel exceeds 227 KB");
+constexpr size_t FWD_LOCAL_SMEM = (size_t)(C * LD64 + 4 * C * LD128) * sizeof(bf16) +
+                                  (size_t)(C * LDL + C + 128 + 128 + C) * sizeof(float);
+static_assert(2 * (FWD_LOCAL_SMEM + 1024) <= 233472, "two forward chunk CTAs must fit one SM");
 
 // o = scale * qg h[n] + Aqk v_new for one chunk.
 __global__ void __launch_bounds__(256) chunk_output_kernel(const bf16* __restrict__ qg, const bf16* __restrict__ Aqk,
@@ -332,7 +369,7 @@ __global__ void __launch_bounds__(128) scalar_gate_cumsum_kernel(const void* __r
 template <int GATE, bool VB>
 cudaError_t run_local(const FwdLocalParams& p, int B, cudaStream_t st) {
   auto kern = chunk_fwd_local_kernel<GATE, VB>;
-  const size_t smem = GATE == GATE_VECTOR ? FWD_LOCAL_SMEM_VECTOR : FWD_LOCAL_SMEM_SCALAR;
+  const size_t smem = FWD_LOCAL_SMEM;
   cudaError_t e = ensure_dynamic_smem<chunk_fwd_local_kernel<GATE, VB>>(smem);
   if (e != cudaSuccess) return e;
   dim3 grid(p.T / C, B * p.H);
