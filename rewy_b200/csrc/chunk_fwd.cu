@@ -49,6 +49,17 @@ __device__ __forceinline__ void split_store8(bf16* hi, bf16* lo, const float (&x
   *reinterpret_cast<uint4*>(lo) = make_uint4(l[0], l[1], l[2], l[3]);
 }
 
+// 2^x and 1/x in one instruction each (2 ulp / 1 ulp); results below the normal range flush to zero
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void unpack8(const uint4& raw, float (&x)[8]) {
   const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw);
 #pragma unroll
@@ -103,8 +114,8 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalP
   if (GATE == GATE_VECTOR && tid < 128) {
     // per-channel range of the cumulative gate over the chunk -> centre; the last row is the chunk decay
     float lo = INFINITY, hi = -INFINITY, last = 0.f;
-#pragma unroll 8
-    for (int t = 0; t < C; t++) {
+#pragma unroll
+    for (int t = 0; t < C; t++) {  // all 64 loads in flight at once
       last = p.g[base128 + (size_t)t * ldt + tid];
       lo = fminf(lo, last);
       hi = fmaxf(hi, last);
@@ -120,7 +131,8 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalP
   // ---- the two A products: Qc Yc^T (-> Aqk) and Ec Yc^T (-> strictly lower part of I + L) -------------------------
   if (GATE == GATE_VECTOR && !wide) {
     // pass 1: Qc = q alpha and Yc = k / alpha as BF16 hi/lo pairs (alpha = 2^(G - centre))
-    for (int i = tid; i < C * 16; i += blockDim.x) {
+#pragma unroll
+    for (int i = tid; i < C * 16; i += 256) {
       const int r = i >> 4, c = (i & 15) * 8;
       const size_t go = base128 + (size_t)r * ldt + c;
       float kk[8], qq[8], gg[8], qc[8], yc[8];
@@ -129,9 +141,9 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalP
       load_gate8(p.g + go, gg);
 #pragma unroll
       for (int j = 0; j < 8; j++) {
-        const float al = exp2f(gg[j] - sCen[c + j]);
+        const float al = ex2(gg[j] - sCen[c + j]);  // |exponent| < 40: no flush
         qc[j] = qq[j] * al;
-        yc[j] = kk[j] * __frcp_rn(al);
+        yc[j] = kk[j] * rcp(al);
       }
       split_store8(sT + 0 * TILE + r * LD128 + c, sT + 1 * TILE + r * LD128 + c, qc);
       split_store8(sT + 2 * TILE + r * LD128 + c, sT + 3 * TILE + r * LD128 + c, yc);
@@ -150,7 +162,8 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalP
     }
     __syncthreads();  // every warp has read Qc
     // pass 2: Ec = b k alpha over the Qc tiles
-    for (int i = tid; i < C * 16; i += blockDim.x) {
+#pragma unroll
+    for (int i = tid; i < C * 16; i += 256) {
       const int r = i >> 4, c = (i & 15) * 8;
       const size_t go = base128 + (size_t)r * ldt + c;
       float kk[8], gg[8], bb[8], ec[8];
@@ -159,7 +172,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalP
       if (VECTOR_BETA) unpack8(*reinterpret_cast<const uint4*>(p.bg + go), bb);
       const float bs = VECTOR_BETA ? 0.f : sBeta[r];
 #pragma unroll
-      for (int j = 0; j < 8; j++) ec[j] = (VECTOR_BETA ? bb[j] : bs) * kk[j] * exp2f(gg[j] - sCen[c + j]);
+      for (int j = 0; j < 8; j++) ec[j] = (VECTOR_BETA ? bb[j] : bs) * kk[j] * ex2(gg[j] - sCen[c + j]);
       split_store8(sT + 0 * TILE + r * LD128 + c, sT + 1 * TILE + r * LD128 + c, ec);
     }
     __syncthreads();
@@ -175,7 +188,8 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalP
     }
   } else {
     // raw q and k tiles (and, for a wide-span chunk, the gate rows)
-    for (int i = tid; i < C * 16; i += blockDim.x) {
+#pragma unroll
+    for (int i = tid; i < C * 16; i += 256) {
       const int r = i >> 4, c = (i & 15) * 8;
       const size_t go = base128 + (size_t)r * ldt + c;
       *reinterpret_cast<uint4*>(sT + 0 * TILE + r * LD128 + c) = *reinterpret_cast<const uint4*>(p.q + go);
@@ -238,6 +252,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalP
   // ---- last pass, by the threads that do not invert: E = b k gamma and Z = w v into the last two tiles, qg and kg
   //      straight to global memory -----------------------------------------------------------------------------------
   if (tid >= C) {
+#pragma unroll 2
     for (int i = tid - C; i < C * 16; i += 256 - C) {
       const int r = i >> 4, c = (i & 15) * 8;
       const size_t go = base128 + (size_t)r * ldt + c;
