@@ -1,5 +1,5 @@
 // Blackwell (sm_100a) plumbing used by the tensor-core stages: mbarriers with bounded waits, TMA tile
-// loads (no multicast anywhere), tcgen05 MMA with TMEM accumulators, shared-memory matrix descriptors.
+// loads (every CTA fetches its own tiles), tcgen05 MMA with TMEM accumulators, shared-memory matrix descriptors.
 #pragma once
 #include <cuda.h>
 #include <cstring>
