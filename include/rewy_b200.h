@@ -28,6 +28,11 @@ extern "C" {
 
 typedef struct CUstream_st* rewy_stream_t; /* a cudaStream_t */
 
+/* Envelope: T a positive multiple of 64, B*H (or num_seqs*H) <= 65535, and B*T*H at most this many token-heads
+ * (tile coordinates are 32-bit: the rows of the [B,NT,H,128,128] state tensors are 2*B*T*H).  Larger problems are
+ * REWY_ERR_SHAPE; 180 GB of device memory hold far fewer. */
+#define REWY_MAX_TOKEN_HEADS (1LL << 29)
+
 enum {
   REWY_OK = 0,
   REWY_ERR_NULL = 1,       /* a required pointer is NULL */

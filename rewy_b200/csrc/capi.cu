@@ -90,6 +90,8 @@ int validate_common(const RewyBwdArgs* a, int family) {
   }
   if (a->T < C || a->T % C != 0) return fail(REWY_ERR_SHAPE, "T must be a positive multiple of 64 (got %s%lld)", "", a->T);
   if ((long long)a->B * a->H > 65535) return fail(REWY_ERR_SHAPE, "B*H exceeds the grid limit 65535%s");
+  if ((long long)a->B * a->T * a->H > REWY_MAX_TOKEN_HEADS)
+    return fail(REWY_ERR_SHAPE, "B*T*H exceeds 2^29 token-heads (32-bit tile coordinates)%s");
   REQUIRE_PTR(q); REQUIRE_PTR(k); REQUIRE_PTR(v); REQUIRE_PTR(Akk); REQUIRE_PTR(d_o);
   REQUIRE_PTR(dq); REQUIRE_PTR(dk); REQUIRE_PTR(dv);
   OPTIONAL_PTR(h0); OPTIONAL_PTR(dht); OPTIONAL_PTR(dh0);
@@ -272,6 +274,8 @@ int validate_stage(const RewyBwdArgs* a, const RewyStageBuffers* s) {
   if (a->family < REWY_DELTA || a->family > REWY_GDN2) return fail(REWY_ERR_UNSUPPORTED, "unknown family%s");
   if (a->B <= 0 || a->H <= 0 || a->T < C || a->T % C != 0) return fail(REWY_ERR_SHAPE, "bad B/T/H%s");
   if ((long long)a->B * a->H > 65535) return fail(REWY_ERR_SHAPE, "B*H exceeds the grid limit 65535%s");
+  if ((long long)a->B * a->T * a->H > REWY_MAX_TOKEN_HEADS)
+    return fail(REWY_ERR_SHAPE, "B*T*H exceeds 2^29 token-heads (32-bit tile coordinates)%s");
   if (a->cu_seqlens != nullptr && (a->B != 1 || a->num_seqs <= 0 || (long long)a->num_seqs * a->H > 65535))
     return fail(REWY_ERR_SHAPE, "packed sequences need B = 1 and 0 < num_seqs*H <= 65535%s");
   return REWY_OK;

@@ -413,6 +413,8 @@ extern "C" int rewy_chunk_fwd(const RewyFwdArgs* a, rewy_stream_t stream) {
   if (a->family < REWY_DELTA || a->family > REWY_GDN2) return report_error(REWY_ERR_UNSUPPORTED, "unknown family");
   if (a->B <= 0 || a->H <= 0 || a->T < C || a->T % C != 0) return report_error(REWY_ERR_SHAPE, "bad B/T/H");
   if ((long long)a->B * a->H > 65535) return report_error(REWY_ERR_SHAPE, "B*H exceeds the grid limit 65535");
+  if ((long long)a->B * a->T * a->H > REWY_MAX_TOKEN_HEADS)
+    return report_error(REWY_ERR_SHAPE, "B*T*H exceeds 2^29 token-heads (32-bit tile coordinates)");
   if (a->state_v_first != 0 && a->state_v_first != 1) return report_error(REWY_ERR_UNSUPPORTED, "state_v_first must be 0 or 1");
   if (a->cu_seqlens != nullptr && (a->B != 1 || a->num_seqs <= 0 || (long long)a->num_seqs * a->H > 65535))
     return report_error(REWY_ERR_SHAPE, "packed sequences need B = 1 and 0 < num_seqs*H <= 65535");

@@ -156,6 +156,15 @@ def test_argument_validation_without_a_gpu():
     a.T = 128
     assert lib.rewy_kda_bwd(a, None) == 1 and b"'q'" in lib.rewy_last_error()
     assert lib.rewy_gdn_bwd(a, None) == 7
+    # maximum size: 2^29 token-heads is the last accepted problem (then the first missing pointer is reported)
+    a.B, a.T, a.H = 64, 1 << 17, 64
+    assert lib.rewy_kda_bwd(a, None) == 1
+    a.T = (1 << 17) + 64
+    assert lib.rewy_kda_bwd(a, None) == 2 and b"2^29" in lib.rewy_last_error()
+    f = _capi.FwdArgs()
+    f.family, f.B, f.T, f.H = _capi.KDA, 64, (1 << 17) + 64, 64
+    assert lib.rewy_chunk_fwd(f, None) == 2 and b"2^29" in lib.rewy_last_error()
+    a.B, a.T, a.H = 1, 128, 1
     assert lib.rewy_bwd_workspace_bytes(_capi.KDA, _capi.SAVED, 1, 128, 1) == 256 + 128 * (512 + 2 * 256)
     assert lib.rewy_bwd_workspace_bytes(_capi.GDN, _capi.RECOMPUTE, 1, 128, 1) == 256 + 128 * (512 + 2 * 256 + 5 * 256 + 512 + 128)
 
