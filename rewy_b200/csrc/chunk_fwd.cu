@@ -1,6 +1,6 @@
 // Forward pass of the four families: what the autograd forward needs besides the backward's own stages.
 //
-//   chunk_fwd_local_kernel   one CTA per chunk: Akk = (I + tril(E Y^T, -1))^-1, Aqk = scale tril(Qg Y^T),
+//   chunk_fwd_local_kernel   one CTA per chunk, three per SM: Akk = (I + tril(E Y^T, -1))^-1, Aqk = scale tril(Qg Y^T),
 //                            w = Akk E, u = Akk Z, qg, kg          (E = b k gamma, Y = k / gamma, Z = w v)
 //   fwd_scan_tc_kernel       (state_scan_tc.cu) h[n], v_new, final state
 //   chunk_output_tc_kernel   (chunk_output_tc.cu, tcgen05) o = scale qg h[n] + Aqk v_new; chunk_output_kernel here is its
@@ -10,7 +10,7 @@
 //
 // The two 64x64x128 products that build the A matrices use centred gate factors (alpha = 2^(G - c), zeta = 1/alpha with
 // c the per-channel mid-point of G over the chunk) and BF16 hi/lo operand pairs in three passes (about 16 mantissa
-// bits), accumulated in FP32 by warp-level MMA; scalar gates apply their pairwise factor 2^(G_i - G_j) to the exact
+// bits), accumulated in FP32 by warp-level MMA (operands by ldmatrix); scalar gates apply their pairwise factor 2^(G_i - G_j) to the exact
 // q k^T and k k^T products instead.  A chunk whose cumulative gate spans 80 log2 units or more in some channel does not
 // use centred factors (they would leave the FP32 range): its two matrices are summed pair by pair on the CUDA cores,
 // sum_k q_ik k_jk 2^(G_ik - G_jk), like the exact pairwise path of the backward.  The unit lower-triangular inverse is
@@ -77,27 +77,33 @@ __device__ __forceinline__ void load_gate8(const float* g, float (&x)[8]) {
   x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
 }
 
-// Shared memory holds four operand tiles only, so that two CTAs share an SM: the element-wise operands are built in
-// three passes over the chunk's inputs (the second and third read them again, from L2), each pass reusing the tiles
-// of the one before.
+// Shared memory holds four operand tiles and nothing else of size, so that three CTAs share an SM: the element-wise
+// operands are built in three passes over the chunk's inputs (the second and third read them again, from L2), each
+// pass reusing the tiles of the one before, and the FP32 matrix I + L and the inverse take the first two tiles once
+// the products that read them are complete.
 template <int GATE, bool VECTOR_BETA>
-__global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalParams p) {
+__global__ void __launch_bounds__(256, 3) chunk_fwd_local_kernel(const FwdLocalParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* sA = reinterpret_cast<bf16*>(smem_raw);            // [64][72]   Akk (BF16) once inverted
-  float* sL = reinterpret_cast<float*>(sA + C * LD64);     // [64][68]   strictly lower part of E Y^T
-  float* sG = sL + C * LDL;                                // [64]       scalar gate rows
+  constexpr int TILE = C * LD128;
+  bf16* sT = reinterpret_cast<bf16*>(smem_raw);            // four tiles [64][136]:
+  //   vector gate, pass 1: Qc hi, Qc lo, Yc hi, Yc lo;  pass 2: Ec hi, Ec lo over the first two
+  //   scalar gate / none:  q, k in the last two
+  //   wide-span chunk:     k in the second, the FP32 gate rows [64][132] over the last two (q and the key gate are
+  //                        read from global memory)
+  //   after the A products: I + L (FP32 [64][68]) in the first, Akk (BF16 [64][72]) in the second
+  //   last pass, all:      E = b k gamma and Z = w v in the last two (-> w, u)
+  static_assert((size_t)C * LDG * sizeof(float) <= 2 * (size_t)TILE * sizeof(bf16), "gate rows fit two tiles");
+  static_assert((size_t)C * LDL * sizeof(float) <= (size_t)TILE * sizeof(bf16), "I + L fits one tile");
+  static_assert(LD64 <= LD128, "Akk fits one tile");
+  float* sL = reinterpret_cast<float*>(sT);                // [64][68]   strictly lower part of E Y^T
+  bf16* sA = sT + TILE;                                    // [64][72]   Akk (BF16) once inverted
+  bf16* sE = sT + 2 * TILE;
+  bf16* sZ = sT + 3 * TILE;
+  bf16* sStage = sE;                                       // [64][72]   Aqk between its product and its row-wise store
+  float* sG = reinterpret_cast<float*>(sT + 4 * TILE);     // [64]       scalar gate rows
   float* sGl = sG + C;                                     // [128]      last gate row of the chunk (vector gate)
   float* sCen = sGl + 128;                                 // [128]      per-channel centre of the gate (vector gate)
   float* sBeta = sCen + 128;                               // [64]       scalar beta rows
-  bf16* sT = reinterpret_cast<bf16*>(sBeta + C);           // four tiles [64][136]:
-  //   vector gate, pass 1: Qc hi, Qc lo, Yc hi, Yc lo;  pass 2: Ec hi, Ec lo over the first two
-  //   scalar gate / none:  q, k
-  //   wide-span chunk:     q, k, and the FP32 gate rows [64][132] over the last two
-  //   last pass, all:      E = b k gamma and Z = w v in the last two (-> w, u)
-  constexpr int TILE = C * LD128;
-  static_assert((size_t)C * LDG * sizeof(float) <= 2 * (size_t)TILE * sizeof(bf16), "gate rows fit two tiles");
-  bf16* sE = sT + 2 * TILE;
-  bf16* sZ = sT + 3 * TILE;
 
   const int n = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
   const int T = p.T, H = p.H;
@@ -149,15 +155,18 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalP
       split_store8(sT + 2 * TILE + r * LD128 + c, sT + 3 * TILE + r * LD128 + c, yc);
     }
     __syncthreads();
-    const Operand<false> Yh{sT + 2 * TILE, LD128}, Yl{sT + 3 * TILE, LD128};
+    const LdmOperand<false> Yh{sT + 2 * TILE, LD128}, Yl{sT + 3 * TILE, LD128};
+    uint32_t aqp[8];  // this thread's part of Aqk (scaled, masked, BF16 pairs): staged for a row-wise store further down
     {
-      const Operand<false> Qh{sT + 0 * TILE, LD128}, Ql{sT + 1 * TILE, LD128};
+      const LdmOperand<false> Qh{sT + 0 * TILE, LD128}, Ql{sT + 1 * TILE, LD128};
       Tile<64, 64, 2, 4> aq;
+      static_assert(Tile<64, 64, 2, 4>::REGS == 16, "eight column pairs per thread");
       aq.zero();
       aq.mma<128>(Qh, Yh); aq.mma<128>(Ql, Yh); aq.mma<128>(Qh, Yl);
+      int n8 = 0;
       aq.for_each_pair([&](int r, int c, float& x0, float& x1) {
         const float y0 = c <= r ? x0 * p.scale : 0.f, y1 = c + 1 <= r ? x1 * p.scale : 0.f;
-        *reinterpret_cast<uint32_t*>(p.Aqk + base64 + (size_t)r * H * 64 + c) = pack_bf16(y0, y1);
+        aqp[n8++] = pack_bf16(y0, y1);
       });
     }
     __syncthreads();  // every warp has read Qc
@@ -177,41 +186,47 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalP
     }
     __syncthreads();
     {
-      const Operand<false> Eh{sT + 0 * TILE, LD128}, El{sT + 1 * TILE, LD128};
+      const LdmOperand<false> Eh{sT + 0 * TILE, LD128}, El{sT + 1 * TILE, LD128};
       Tile<64, 64, 2, 4> ak;
       ak.zero();
       ak.mma<128>(Eh, Yh); ak.mma<128>(El, Yh); ak.mma<128>(Eh, Yl);
+      __syncthreads();  // every warp has read Ec and Yc: I + L and the Aqk tile take their places
+      int n8 = 0;
       ak.for_each_pair([&](int r, int c, float& x0, float& x1) {
         sL[r * LDL + c] = c < r ? x0 : 0.f;
         sL[r * LDL + c + 1] = c + 1 < r ? x1 : 0.f;
+        *reinterpret_cast<uint32_t*>(sStage + r * LD64 + c) = aqp[n8++];
       });
     }
   } else {
-    // raw q and k tiles (and, for a wide-span chunk, the gate rows)
+    // raw q and k tiles (scalar gate / none), or k and the gate rows of a wide-span chunk
+    bf16* sQr = sT + 2 * TILE;
+    bf16* sKr = GATE == GATE_VECTOR ? sT + TILE : sT + 3 * TILE;
 #pragma unroll
     for (int i = tid; i < C * 16; i += 256) {
       const int r = i >> 4, c = (i & 15) * 8;
       const size_t go = base128 + (size_t)r * ldt + c;
-      *reinterpret_cast<uint4*>(sT + 0 * TILE + r * LD128 + c) = *reinterpret_cast<const uint4*>(p.q + go);
-      *reinterpret_cast<uint4*>(sT + 1 * TILE + r * LD128 + c) = *reinterpret_cast<const uint4*>(p.k + go);
+      *reinterpret_cast<uint4*>(sKr + r * LD128 + c) = *reinterpret_cast<const uint4*>(p.k + go);
       if (GATE == GATE_VECTOR) {
         *reinterpret_cast<float4*>(sGf + r * LDG + c) = *reinterpret_cast<const float4*>(p.g + go);
         *reinterpret_cast<float4*>(sGf + r * LDG + c + 4) = *reinterpret_cast<const float4*>(p.g + go + 4);
+      } else {
+        *reinterpret_cast<uint4*>(sQr + r * LD128 + c) = *reinterpret_cast<const uint4*>(p.q + go);
       }
     }
     __syncthreads();
     if (GATE == GATE_VECTOR) {
       // exact pairwise sums, thread = (row i, every fourth column j)
-      const bf16 *sQr = sT, *sKr = sT + TILE;
       const int i = tid >> 2;
       const float beta_i = VECTOR_BETA ? 0.f : sBeta[i];
+      const bf16* qi = p.q + base128 + (size_t)i * ldt;    // query row of token i
       const bf16* bgi = p.bg + base128 + (size_t)i * ldt;  // key gate row of token i (vector beta)
       for (int j = tid & 3; j < C; j += 4) {
         float aq = 0.f, ak = 0.f;
         if (j <= i) {
           for (int kk = 0; kk < 128; kk++) {
             const float f = exp2f(sGf[i * LDG + kk] - sGf[j * LDG + kk]) * bf2f(sKr[j * LD128 + kk]);
-            aq = fmaf(bf2f(sQr[i * LD128 + kk]), f, aq);
+            aq = fmaf(bf2f(qi[kk]), f, aq);
             const float bi = VECTOR_BETA ? bf2f(bgi[kk]) : beta_i;
             ak = fmaf(bi * bf2f(sKr[i * LD128 + kk]), f, ak);
           }
@@ -220,12 +235,13 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalP
         sL[i * LDL + j] = j < i ? ak : 0.f;
       }
     } else {
-      const Operand<false> Q{sT + 0 * TILE, LD128}, K{sT + 1 * TILE, LD128};
+      const LdmOperand<false> Q{sQr, LD128}, K{sKr, LD128};
       Tile<64, 64, 2, 4> aq, ak;
       aq.zero();
       ak.zero();
       aq.mma<128>(Q, K);
       ak.mma<128>(K, K);
+      __syncthreads();  // every warp has read q and k: the Aqk tile takes the place of q
       aq.for_each_pair([&](int r, int c, float& x0, float& x1) {
         float f0 = p.scale, f1 = p.scale;
         if (GATE == GATE_SCALAR) {
@@ -233,7 +249,7 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalP
           f1 *= exp2f(sG[r] - sG[c + 1 <= r ? c + 1 : r]);
         }
         const float y0 = c <= r ? x0 * f0 : 0.f, y1 = c + 1 <= r ? x1 * f1 : 0.f;
-        *reinterpret_cast<uint32_t*>(p.Aqk + base64 + (size_t)r * H * 64 + c) = pack_bf16(y0, y1);
+        *reinterpret_cast<uint32_t*>(sStage + r * LD64 + c) = pack_bf16(y0, y1);
       });
       ak.for_each_pair([&](int r, int c, float& x0, float& x1) {
         // exact k k^T: beta and the pairwise gate factor go on afterwards
@@ -252,6 +268,14 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalP
   // ---- last pass, by the threads that do not invert: E = b k gamma and Z = w v into the last two tiles, qg and kg
   //      straight to global memory -----------------------------------------------------------------------------------
   if (tid >= C) {
+    if (!(GATE == GATE_VECTOR && wide)) {
+      // Aqk leaves in 16-byte pieces of whole rows; the tile is overwritten by this pass, so its 192 threads meet first
+      for (int i = tid - C; i < C * 8; i += 256 - C) {
+        const int r = i >> 3, c = (i & 7) * 8;
+        *reinterpret_cast<uint4*>(p.Aqk + base64 + (size_t)r * H * 64 + c) = *reinterpret_cast<const uint4*>(sStage + r * LD64 + c);
+      }
+      asm volatile("bar.sync 1, 192;" ::: "memory");
+    }
 #pragma unroll 2
     for (int i = tid - C; i < C * 16; i += 256 - C) {
       const int r = i >> 4, c = (i & 15) * 8;
@@ -312,13 +336,13 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalP
   {
     Tile<64, 128, 2, 4> acc;
     acc.zero();
-    acc.mma<64>(Operand<false>{sA, LD64}, Operand<true>{sE, LD128});
+    acc.mma<64>(LdmOperand<false>{sA, LD64}, LdmOperand<true>{sE, LD128});
     __syncthreads();
     acc.for_each_pair([&](int r, int c, float& x0, float& x1) {
       *reinterpret_cast<uint32_t*>(sE + r * LD128 + c) = pack_bf16(x0, x1);
     });
     acc.zero();
-    acc.mma<64>(Operand<false>{sA, LD64}, Operand<true>{sZ, LD128});
+    acc.mma<64>(LdmOperand<false>{sA, LD64}, LdmOperand<true>{sZ, LD128});
     __syncthreads();
     acc.for_each_pair([&](int r, int c, float& x0, float& x1) {
       *reinterpret_cast<uint32_t*>(sZ + r * LD128 + c) = pack_bf16(x0, x1);
@@ -329,9 +353,8 @@ __global__ void __launch_bounds__(256, 2) chunk_fwd_local_kernel(const FwdLocalP
   }
 }
 
-constexpr size_t FWD_LOCAL_SMEM = (size_t)(C * LD64 + 4 * C * LD128) * sizeof(bf16) +
-                                  (size_t)(C * LDL + C + 128 + 128 + C) * sizeof(float);
-static_assert(2 * (FWD_LOCAL_SMEM + 1024) <= 233472, "two forward chunk CTAs must fit one SM");
+constexpr size_t FWD_LOCAL_SMEM = (size_t)(4 * C * LD128) * sizeof(bf16) + (size_t)(C + 128 + 128 + C) * sizeof(float);
+static_assert(3 * (FWD_LOCAL_SMEM + 1024) <= 233472, "three forward chunk CTAs must fit one SM");
 
 // o = scale * qg h[n] + Aqk v_new for one chunk.
 __global__ void __launch_bounds__(256) chunk_output_kernel(const bf16* __restrict__ qg, const bf16* __restrict__ Aqk,

@@ -108,13 +108,13 @@ __global__ void __launch_bounds__(256) prepare_kernel(
     // w and u go back through the operand tiles they were computed from, so that they leave in 16-byte rows
     Tile<64, 128, 2, 4> acc;
     acc.zero();
-    acc.mma<64>(Operand<false>{sA, LD64}, Operand<true>{sE, LD128});
+    acc.mma<64>(LdmOperand<false>{sA, LD64}, LdmOperand<true>{sE, LD128});
     __syncthreads();  // every warp has read the b*k*gamma tile
     acc.for_each_pair([&](int r, int c, float& x0, float& x1) {
       *reinterpret_cast<uint32_t*>(sE + r * LD128 + c) = pack_bf16(x0, x1);
     });
     acc.zero();
-    acc.mma<64>(Operand<false>{sA, LD64}, Operand<true>{sZ, LD128});
+    acc.mma<64>(LdmOperand<false>{sA, LD64}, LdmOperand<true>{sZ, LD128});
     __syncthreads();
     acc.for_each_pair([&](int r, int c, float& x0, float& x1) {
       *reinterpret_cast<uint32_t*>(sZ + r * LD128 + c) = pack_bf16(x0, x1);
@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(256) prepare_kernel(
   if (Aqk_out != nullptr) {
     Tile<64, 64, 2, 4> acc;
     acc.zero();
-    acc.mma<128>(Operand<false>{sQ, LD128}, Operand<false>{sK, LD128});
+    acc.mma<128>(LdmOperand<false>{sQ, LD128}, LdmOperand<false>{sK, LD128});
     acc.for_each_pair([&](int r, int c, float& x0, float& x1) {
       float f0 = scale, f1 = scale;
       if (GATE == GATE_SCALAR) {

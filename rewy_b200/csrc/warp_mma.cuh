@@ -11,6 +11,7 @@ namespace rewy {
 // NEG flips the sign of every element as it is fetched.
 template <bool TRANS, bool NEG = false>
 struct Operand {
+  static constexpr bool LDM = false;
   const bf16* p;
   int ld;
   __device__ __forceinline__ uint32_t pair(int mn, int k) const {  // elements (mn,k) and (mn,k+1)
@@ -26,6 +27,28 @@ struct Operand {
     return u;
   }
 };
+
+// The same view, fetched with ldmatrix: four 8x8 BF16 matrices per instruction instead of one 32-bit (or two 16-bit)
+// shared-memory loads per fragment register.  Requires p 16-byte aligned and ld a multiple of 8 elements.
+template <bool TRANS, bool NEG = false>
+struct LdmOperand {
+  static constexpr bool LDM = true;
+  static constexpr bool TRANSPOSED = TRANS;
+  static constexpr bool NEGATE = NEG;
+  const bf16* p;
+  int ld;
+};
+
+template <bool TRANS>
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const bf16* at) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(at));
+  if (TRANS)
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+  else
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
   asm volatile(
@@ -60,8 +83,61 @@ struct Tile {
   }
   __device__ __forceinline__ static int col(int j, int e) { return n0() + j * 8 + ((threadIdx.x & 3) << 1) + (e & 1); }
 
+  // ldmatrix operands.  Lane l of a warp supplies the address of one 8-element row of one of the four matrices of
+  // an instruction (matrix l>>3, row l&7):
+  //   A, m16 x k16:  a0 (m 0-7, k 0-7), a1 (m 8-15, k 0-7), a2 (m 0-7, k 8-15), a3 (m 8-15, k 8-15)
+  //   B, two n8 x k16 fragments:  b[j][0] (k 0-7), b[j][1] (k 8-15), b[j+1][0], b[j+1][1]
+  // A transposed view is stored [k][mn] and read with .trans, which hands every thread the same elements.
+  template <int KD, class OA, class OB>
+  __device__ __forceinline__ void mma_ldm(const OA& A, const OB& B) {
+    static_assert(TN % 2 == 0, "B fragments are fetched two at a time");
+    const int l = threadIdx.x & 31;
+    const int rm = m0(), rn = n0();
+    const bf16* pa = OA::TRANSPOSED ? A.p + ((l & 7) + (l >> 4) * 8) * A.ld + rm + ((l >> 3) & 1) * 8
+                                    : A.p + (rm + (l & 7) + ((l >> 3) & 1) * 8) * A.ld + (l >> 4) * 8;
+    const bf16* pb = OB::TRANSPOSED ? B.p + ((l & 7) + ((l >> 3) & 1) * 8) * B.ld + rn + (l >> 4) * 8
+                                    : B.p + (rn + (l & 7) + (l >> 4) * 8) * B.ld + ((l >> 3) & 1) * 8;
+    const int a_i = OA::TRANSPOSED ? 16 : 16 * A.ld, a_k = OA::TRANSPOSED ? A.ld : 1;
+    const int b_j = OB::TRANSPOSED ? 16 : 16 * B.ld, b_k = OB::TRANSPOSED ? B.ld : 1;
+#pragma unroll 2
+    for (int k0 = 0; k0 < KD; k0 += 16) {
+      uint32_t a[TM][4], b[TN][2];
+#pragma unroll
+      for (int i = 0; i < TM; i++) {
+        ldmatrix_x4<OA::TRANSPOSED>(a[i], pa + i * a_i + k0 * a_k);
+        if (OA::NEGATE) {
+#pragma unroll
+          for (int e = 0; e < 4; e++) a[i][e] ^= 0x80008000u;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < TN; j += 2) {
+        uint32_t r[4];
+        ldmatrix_x4<OB::TRANSPOSED>(r, pb + (j >> 1) * b_j + k0 * b_k);
+        if (OB::NEGATE) {
+#pragma unroll
+          for (int e = 0; e < 4; e++) r[e] ^= 0x80008000u;
+        }
+        b[j][0] = r[0]; b[j][1] = r[1]; b[j + 1][0] = r[2]; b[j + 1][1] = r[3];
+      }
+#pragma unroll
+      for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < TN; j++) mma_16816(acc[i][j], a[i], b[j]);
+    }
+  }
+
   template <int KD, class OA, class OB>
   __device__ __forceinline__ void mma(const OA& A, const OB& B) {
+    if constexpr (OA::LDM && OB::LDM) {
+      mma_ldm<KD>(A, B);
+    } else {
+      mma_lds<KD>(A, B);
+    }
+  }
+
+  template <int KD, class OA, class OB>
+  __device__ __forceinline__ void mma_lds(const OA& A, const OB& B) {
     const int g = (threadIdx.x & 31) >> 2, t = threadIdx.x & 3;
     const int rm = m0(), rn = n0();
 #pragma unroll 2
