@@ -112,7 +112,9 @@ def intra_fixtures(ref):
 
 
 if __name__ == "__main__":
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: python make_golden.py <checkout of the reference (flashserve/ReWY)>")
+    ref = Path(sys.argv[1])
     recurrence_fixtures(ref)
     closed_form_fixture(ref)
     intra_fixtures(ref)
