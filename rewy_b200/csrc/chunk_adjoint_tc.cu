@@ -896,12 +896,19 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     }
     if (GATE == GATE_SCALAR) {
       __syncthreads();
-      if (tid == 0 && alive) {
-        float r = sDb[0] + sDb[1] + sDb[2] + sDb[3];
-        for (int t = C - 1; t >= 0; --t) {
-          r += sDgs[t];
-          p.dg[base1 + (size_t)t * H] = r;
+      if (warp == 0 && alive) {
+        // reverse cumulative sum over the 64 tokens by one warp: lane l owns tokens 2l and 2l+1
+        const float v0 = sDgs[2 * lane], v1 = sDgs[2 * lane + 1];
+        float acc = v0 + v1;  // becomes the sum over this lane and every lane above it
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const float up = __shfl_down_sync(0xffffffffu, acc, d);
+          if (lane + d < 32) acc += up;
         }
+        const float end = sDb[0] + sDb[1] + sDb[2] + sDb[3];  // the chunk-end term sits on the last token
+        const float r1 = end + (acc - v0);                    // tokens 2l+1 .. 63
+        p.dg[base1 + (size_t)(2 * lane + 1) * H] = r1;
+        p.dg[base1 + (size_t)(2 * lane) * H] = r1 + v0;
       }
     }
     ph ^= used;
