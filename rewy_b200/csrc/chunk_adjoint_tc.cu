@@ -488,7 +488,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       uint4 hi, lo;
       split8(y, hi, lo);
       tmem_st4(tlane + TM_Y + ch * 4, hi);
-      tmem_st4(tlane + TM_Y + 32 + ch * 4, lo);
+      if (GATE == GATE_VECTOR) tmem_st4(tlane + TM_Y + 32 + ch * 4, lo);
     }
     tmem_st_wait();
 
@@ -661,7 +661,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
         mma_kmajor<8>(tb + TM_X1, dl(Smem::HS, 16), 16384, dl(Smem::DOP, 16), 16384, ID_KK128, false);
         // [X2 | X4] = Yc^T [dAqk ; dAkk]^T, hi/lo split in three passes, Yc^T from tensor memory
         mma_ts4(tb + TM_X2, tb + TM_Y, dl(Smem::HHI, 16), 32, ID_KK128, false);
-        mma_ts4(tb + TM_X2, tb + TM_Y + 32, dl(Smem::HHI, 16), 32, ID_KK128, true);
+        if (GATE == GATE_VECTOR)  // without a vector gate Yc = k is exact in BF16: its lo part is zero
+          mma_ts4(tb + TM_X2, tb + TM_Y + 32, dl(Smem::HHI, 16), 32, ID_KK128, true);
         mma_ts4(tb + TM_X2, tb + TM_Y, dl(Smem::HLO, 16), 32, ID_KK128, true);
         mma_commit(&bars[BAR_Q]);  // X1 and X2 complete: dq can be finished while the rest still runs
       }
@@ -690,7 +691,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
       uint4 hi, lo;
       split8(x, hi, lo);
       tmem_st4(tlane + TM_QC + (wg * (HALF / 8) + t8) * 4, hi);
-      tmem_st4(tlane + TM_QC + 32 + (wg * (HALF / 8) + t8) * 4, lo);
+      if (GATE == GATE_VECTOR) tmem_st4(tlane + TM_QC + 32 + (wg * (HALF / 8) + t8) * 4, lo);
     }
     tmem_st_wait();
     tc_fence_before_sync();
@@ -722,7 +723,8 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
           // this runs after it
           mma_kmajor<8>(tb + TM_X5, dl(Smem::DHT, 16), 16384, dl(Smem::R, 16), 8192, ID_KK, false);
           mma_ts4(tb + TM_X6, tb + TM_QC, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
-          mma_ts4(tb + TM_X6, tb + TM_QC + 32, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
+          if (GATE == GATE_VECTOR)  // likewise Qc = q
+            mma_ts4(tb + TM_X6, tb + TM_QC + 32, dl(Smem::HHI, 8192), 2048, ID_KMN, true);
           mma_ts4(tb + TM_X6, tb + TM_QC, dl(Smem::HLO, 8192), 2048, ID_KMN, true);
           mma_commit(&bars[BAR_C3]);
         }
