@@ -235,7 +235,14 @@ int run_family(const RewyBwdArgs* a, int family, cudaStream_t st) {
   if ((rc = check_cuda(clear_status(s.ctrl, st), "status word")) != REWY_OK) return rc;
   timing_mark(set, 0, st);
   if (p.prepare) {
+    // Without a gate qg = q and kg = k: the prepare stage writes neither and the scans read the inputs themselves
+    const bool gateless = a->family == REWY_DELTA;
+    if (gateless) s.qg = s.kg = nullptr;
     if ((rc = check_cuda(run_prepare(*a, s, st), "prepare")) != REWY_OK) return rc;
+    if (gateless) {
+      s.qg = const_cast<void*>(a->q);
+      s.kg = const_cast<void*>(a->k);
+    }
     timing_mark(set, 1, st);
     // The forward scan (h, v_new: read by the chunk stage) and the reverse scan (reads qg, kg, w of the prepare stage
     // only) do not depend on each other: the forward scan goes to a side stream and joins before the chunk stage.  One

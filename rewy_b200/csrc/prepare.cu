@@ -95,8 +95,10 @@ __global__ void __launch_bounds__(256) prepare_kernel(
     }
     *reinterpret_cast<uint4*>(sE + r * LD128 + c) = make_uint4(eo[0], eo[1], eo[2], eo[3]);
     *reinterpret_cast<uint4*>(sZ + r * LD128 + c) = make_uint4(zo[0], zo[1], zo[2], zo[3]);
-    *reinterpret_cast<uint4*>(qg_out + go) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
-    *reinterpret_cast<uint4*>(kg_out + go) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
+    if (qg_out != nullptr) {  // nullptr: a family without a gate, whose scans read q and k themselves
+      *reinterpret_cast<uint4*>(qg_out + go) = make_uint4(qo[0], qo[1], qo[2], qo[3]);
+      *reinterpret_cast<uint4*>(kg_out + go) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
+    }
     if (Aqk_out != nullptr) {
       *reinterpret_cast<uint4*>(sQ + r * LD128 + c) = qr;
       *reinterpret_cast<uint4*>(sK + r * LD128 + c) = kr;

@@ -26,6 +26,7 @@ struct PrepParams {
   bf16* Aqk;
   int* err;
   int T, H, NT, total_chunks;
+  int write_qk;  // 0: qg and kg are not stored (a family without a gate, whose scans read q and k themselves)
   float scale;
 };
 
@@ -258,9 +259,11 @@ prepare_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         for (int ks = 0; ks < 4; ks++)
           mma_f16_lo(tb + TM_U, dl(PS::VT + ks * 2048, 8192), dl(PS::AK + ks * 32, 16), ID_WU, ks > 0);
         mma_commit(&bars[PB_MMA]);
-        tma_store_3d(&tmQg, sm + PS::QT, h * 128, row0, 0);
-        tma_store_3d(&tmKg, sm + PS::KGT, h * 128, row0, 0);
-        tma_store_commit();
+        if (p.write_qk) {
+          tma_store_3d(&tmQg, sm + PS::QT, h * 128, row0, 0);
+          tma_store_3d(&tmKg, sm + PS::KGT, h * 128, row0, 0);
+          tma_store_commit();
+        }
       }
       __syncwarp();
     }
@@ -344,17 +347,20 @@ cudaError_t launch_prepare_tc(const RewyBwdArgs& a, const RewyStageBuffers& s, i
             encode_tmap_panels(&tm[1], a.v, 2, cols, rows, pitch, 64, 2) &&
             encode_tmap_panels(&tm[2], a.q, 2, cols, rows, pitch, 64, 2) &&
             encode_tmap_2d(&tm[3], a.Akk, 2, (uint64_t)H * 64, rows, (uint64_t)H * 128, 64, 64) &&
-            encode_tmap_panels(&tm[7], s.qg, 2, cols, rows, pitch, 64, 2) &&
-            encode_tmap_panels(&tm[8], s.kg, 2, cols, rows, pitch, 64, 2) &&
             encode_tmap_2d(&tm[9], s.w, 2, cols, rows, pitch, 128, 64, false) &&
             encode_tmap_2d(&tm[10], s.u, 2, cols, rows, pitch, 128, 64, false);
-  tm[4] = tm[5] = tm[6] = tm[0];  // never dereferenced unless the family has the tensor
+  tm[4] = tm[5] = tm[6] = tm[7] = tm[8] = tm[0];  // never dereferenced unless the family has the tensor
+  const bool write_qk = s.qg != nullptr && s.kg != nullptr;
+  if (ok && write_qk)
+    ok = encode_tmap_panels(&tm[7], s.qg, 2, cols, rows, pitch, 64, 2) &&
+         encode_tmap_panels(&tm[8], s.kg, 2, cols, rows, pitch, 64, 2);
   if (ok && vector) ok = encode_tmap_panels(&tm[4], a.g, 4, cols, rows, (uint64_t)H * 512, 64, 4);
   if (ok && vb) ok = encode_tmap_panels(&tm[5], a.b_gate, 2, cols, rows, pitch, 64, 2);
   if (!ok) return cudaErrorInvalidValue;
   PrepParams p;
   p.g = a.g; p.beta = a.beta; p.wg = (const bf16*)a.w_gate; p.Aqk = (bf16*)s.Aqk; p.err = err;
   p.T = T; p.H = H; p.NT = NT; p.total_chunks = B * H * NT; p.scale = a.scale;
+  p.write_qk = write_qk ? 1 : 0;
   switch (a.family) {
     case REWY_DELTA: return run<GATE_NONE, false>(tm, p, st);
     case REWY_GDN: return run<GATE_SCALAR, false>(tm, p, st);
