@@ -15,19 +15,20 @@ __version__ = "0.1.0"
 
 
 def enable(backend="optimized", *, strict=True, ops=None, integrations=()):
-    """Select the CUDA backward for the given operators.  ``integrations=("fla",)`` also registers the four
-    operators in flash-linear-attention's backend registry when the installed FLA has one (see
-    ``rewy_b200.integrations``); an FLA without that registry, or an unknown name, raises."""
+    """Select the CUDA backward for the given operators.  ``integrations`` names what else should reach them without
+    source edits (``rewy_b200.integrations``): "fla" replaces flash-linear-attention's public operator aliases,
+    "qwen3_5" and "gdn2" bind the two model files the reference binds.  An unknown name raises."""
     from .runtime import configure
     from . import _capi
-    for name in integrations:
-        if name != "fla":
-            raise ValueError(f"Unknown integration: {name}")
+    unknown = [name for name in integrations if name not in ("fla", "qwen3_5", "gdn2")]
+    if unknown:
+        raise ValueError(f"Unknown integration: {unknown[0]}")
     if backend == "optimized":
         _capi.load()  # fail here, loudly, if the CUDA library has not been built
-    if "fla" in integrations:
-        from .integrations import install
-        install()
+    if integrations:
+        from .integrations import INTEGRATIONS
+        for name in integrations:
+            INTEGRATIONS[name]()
     configure(backend, strict=strict, ops=ops)
 
 

@@ -8,6 +8,11 @@ public aliases ``fla.ops.<family>.<name>`` and ``fla.ops.<family>.chunk.<name>``
 layer modules that are already imported) by the dispatching entry of ``rewy_b200.runtime.operator``.  The
 original functions are captured first, so the "original" backend and non-strict forwarding still reach FLA's
 own implementation.  Families the installed FLA does not have are skipped and reported.
+
+Model bindings (the reference's src/fast_delta_rule/integrations/models.py:5-15): ``bind_qwen3_5`` points the chunked
+gated delta rule of transformers' Qwen3.5 modelling file at the ``gdn`` operator, ``bind_gdn2`` does the same for the
+``chunk_gdn2`` of the GDN2 authors' ``lit_gpt.gdn2`` layer.  Both change exactly one attribute of one module and
+refuse a module that does not have it; ``uninstall()`` puts every patched attribute back.
 """
 import importlib
 import sys
@@ -44,6 +49,33 @@ def install():
                 setattr(module, name, entry)
     _installed = {"patched": sorted(originals), "skipped": skipped}
     return _installed
+
+
+def _bind(module_path, attribute, op, what):
+    try:
+        module = importlib.import_module(module_path)
+    except Exception as exc:
+        raise RuntimeError(f"rewy_b200 integration {what!r}: {module_path} is not importable: {exc}") from exc
+    if not hasattr(module, attribute):
+        raise RuntimeError(f"rewy_b200 integration {what!r}: {module_path} has no {attribute}")
+    from .runtime import operator
+    entry = operator(op)
+    if getattr(module, attribute) is not entry:
+        _patched.append((module, attribute, getattr(module, attribute)))
+        setattr(module, attribute, entry)
+
+
+def bind_qwen3_5():
+    """transformers' Qwen3.5: layers built after this call run the ``gdn`` operator for their chunked delta rule."""
+    _bind("transformers.models.qwen3_5.modeling_qwen3_5", "torch_chunk_gated_delta_rule", "gdn", "qwen3_5")
+
+
+def bind_gdn2():
+    """The GDN2 authors' layer (their project must be importable as ``lit_gpt``)."""
+    _bind("lit_gpt.gdn2", "chunk_gdn2", "gdn2", "gdn2")
+
+
+INTEGRATIONS = {"fla": install, "qwen3_5": bind_qwen3_5, "gdn2": bind_gdn2}
 
 
 def uninstall():

@@ -279,6 +279,73 @@ def test_fla_integration_patches_and_restores_public_aliases():
     assert mod.chunk_kda is before
 
 
+def test_model_bindings_change_one_attribute_and_are_restored():
+    """The two model bindings of the reference (integrations/models.py:5-15): one attribute of one module each."""
+    import sys
+    import types
+    import rewy_b200 as fdr
+    from rewy_b200 import integrations, runtime
+    pkg, layer = types.ModuleType("lit_gpt"), types.ModuleType("lit_gpt.gdn2")
+    theirs = lambda *a, **k: None
+    layer.chunk_gdn2 = theirs
+    pkg.gdn2 = layer
+    sys.modules["lit_gpt"], sys.modules["lit_gpt.gdn2"] = pkg, layer
+    try:
+        fdr.enable("original", integrations=("gdn2",))
+        assert layer.chunk_gdn2 is runtime.operator("gdn2")
+        integrations.uninstall()
+        assert layer.chunk_gdn2 is theirs
+        del layer.chunk_gdn2
+        with pytest.raises(RuntimeError, match="has no chunk_gdn2"):
+            fdr.enable("original", integrations=("gdn2",))
+    finally:
+        integrations.uninstall()
+        fdr.disable()
+        del sys.modules["lit_gpt"], sys.modules["lit_gpt.gdn2"]
+    with pytest.raises(RuntimeError, match="not importable"):
+        fdr.enable("original", integrations=("gdn2",))
+    fdr.disable()
+    qwen = pytest.importorskip("transformers.models.qwen3_5.modeling_qwen3_5")
+    before = qwen.torch_chunk_gated_delta_rule
+    try:
+        fdr.enable("original", integrations=("qwen3_5",))
+        assert qwen.torch_chunk_gated_delta_rule is runtime.operator("gdn")
+    finally:
+        integrations.uninstall()
+        fdr.disable()
+    assert qwen.torch_chunk_gated_delta_rule is before
+
+
+def test_launcher_runs_a_script_and_writes_the_dispatch_report(tmp_path):
+    """`python -m rewy_b200 run`: the script runs unmodified with its own argv, the report is written, and an optimized
+    run without any optimized backward is an error unless it is declared forward-only (reference: cli.py:70-95)."""
+    import json
+    import sys
+    pytest.importorskip("fla")
+    from rewy_b200 import disable, integrations, launcher
+    script = tmp_path / "train.py"
+    script.write_text("import sys, pathlib\npathlib.Path(sys.argv[1]).write_text(' '.join(sys.argv[1:]))\n")
+    marker, report = tmp_path / "ran.txt", tmp_path / "out" / "report.json"
+    argv_before = sys.argv[:]
+    try:
+        assert launcher.main(["run", "--backend", "original", "--report", str(report), str(script), str(marker), "--lr", "3"]) == 0
+        assert marker.read_text() == f"{marker} --lr 3" and sys.argv == argv_before
+        got = json.loads(report.read_text())
+        assert got["backend"] == "original" and got["counts"] == {} and "count_boundary" in got
+        with pytest.raises(RuntimeError, match="No optimized backward ran"):
+            launcher.main(["run", "--report", str(report), str(script), str(marker)])
+        assert json.loads(report.read_text())["backend"] == "optimized"     # written even when the run is refused
+        assert launcher.main(["run", "--allow-no-backward", str(script), str(marker)]) == 0
+        failing = tmp_path / "fail.py"
+        failing.write_text("raise SystemExit(3)\n")
+        with pytest.raises(SystemExit):
+            launcher.main(["run", "--backend", "original", str(failing)])
+    finally:
+        integrations.uninstall()
+        disable()
+    assert set(launcher.doctor()) >= {"python", "torch", "library", "cuda_available"}
+
+
 def test_unknown_integration_is_rejected():
     import rewy_b200 as fdr
     with pytest.raises(ValueError, match="Unknown integration"):
