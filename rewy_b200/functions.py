@@ -174,6 +174,45 @@ def _packed(cu_seqlens, q):
     return None if cu_seqlens is None else cu_seqlens.to(device=q.device, dtype=torch.int32).contiguous()
 
 
+class _Ragged:
+    """Lengths that are not multiples of the chunk: every sequence is extended to the next multiple of 64 by neutral
+    tokens (q = k = v = 0, no decay), which change neither the state nor any real token's output, and the results are
+    cut back.  The padding and the cut are ordinary differentiable tensor operations around the autograd function, so
+    the gradients of the real tokens come out by themselves.  FLA handles such lengths by bounds checks inside its
+    kernels (the reference's release envelope rejects them: src/fast_delta_rule/runtime.py:87-88)."""
+
+    def __init__(self, T, device, cu_seqlens=None, cu_seqlens_cpu=None):
+        self.T, self.index, self.cu = T, None, None
+        if cu_seqlens is None:
+            self.total = -(-T // 64) * 64
+            self.needed = self.total != T
+            return
+        host = (cu_seqlens if cu_seqlens_cpu is None else cu_seqlens_cpu).detach().cpu().to(torch.int64)
+        lengths = host[1:] - host[:-1]
+        padded = (lengths + 63) // 64 * 64
+        self.needed = bool((padded != lengths).any())
+        if not self.needed:
+            return
+        starts = torch.cumsum(padded, 0) - padded
+        self.total = int(padded.sum())
+        self.index = torch.cat([torch.arange(int(n)) + int(s) for n, s in zip(lengths, starts)]).to(device)
+        self.cu = torch.cat([starts, starts[-1:] + padded[-1:]]).to(device=device, dtype=torch.int32)
+
+    def pad(self, x, fill=0.0):
+        """x [B, T, ...] -> [B, padded T, ...]"""
+        if x is None or not self.needed:
+            return x
+        if self.index is None:
+            tail = x.new_full((x.shape[0], self.total - self.T) + tuple(x.shape[2:]), fill)
+            return torch.cat([x, tail], 1)
+        return x.new_full((x.shape[0], self.total) + tuple(x.shape[2:]), fill).index_copy(1, self.index, x)
+
+    def cut(self, o):
+        if not self.needed:
+            return o
+        return o[:, :self.T] if self.index is None else o.index_select(1, self.index)
+
+
 def _common_checks(q, k, v, initial_state):
     if q.shape != k.shape:
         raise ValueError(f"q and k must have the same shape, got q={tuple(q.shape)} vs k={tuple(k.shape)}")
@@ -201,9 +240,15 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
             raise ValueError("rewy_b200 chunk_kda: the lower_bound gate law belongs to safe_gate, which is not supported")
     if scale is None:
         scale = k.shape[-1] ** -0.5
-    return ChunkKDAFunction.apply(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state,
-                                  use_qk_l2norm_in_kernel, use_gate_in_kernel, use_beta_sigmoid_in_kernel, allow_neg_eigval,
-                                  disable_recompute, state_v_first, _packed(cu_seqlens, q))
+    rg = _Ragged(q.shape[1], q.device, cu_seqlens, cu_seqlens_cpu)
+    if rg.needed:
+        # a raw gate input goes through -exp(A_log) softplus(g + dt_bias): a very negative value gives decay 0
+        q, k, v, beta, g = rg.pad(q), rg.pad(k), rg.pad(v), rg.pad(beta), rg.pad(g, -1e4 if use_gate_in_kernel else 0.0)
+        cu_seqlens = rg.cu
+    o, final_state = ChunkKDAFunction.apply(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state,
+                                            use_qk_l2norm_in_kernel, use_gate_in_kernel, use_beta_sigmoid_in_kernel,
+                                            allow_neg_eigval, disable_recompute, state_v_first, _packed(cu_seqlens, q))
+    return rg.cut(o), final_state
 
 
 @torch.compiler.disable
@@ -215,8 +260,14 @@ def chunk_gdn2(q, k, v, g, b, w, scale=None, initial_state=None, output_final_st
     _common_checks(q, k, v, initial_state)
     if scale is None:
         scale = k.shape[-1] ** -0.5
-    return ChunkGDN2Function.apply(q, k, v, g, b, w, scale, initial_state, output_final_state,
-                                   use_qk_l2norm_in_kernel, disable_recompute, state_v_first, _packed(cu_seqlens, q))
+    rg = _Ragged(q.shape[1], q.device, cu_seqlens, cu_seqlens_cpu)
+    if rg.needed:
+        q, k, v, g, b, w = (rg.pad(x) for x in (q, k, v, g, b, w))
+        cu_seqlens = rg.cu
+    o, final_state = ChunkGDN2Function.apply(q, k, v, g, b, w, scale, initial_state, output_final_state,
+                                             use_qk_l2norm_in_kernel, disable_recompute, state_v_first,
+                                             _packed(cu_seqlens, q))
+    return rg.cut(o), final_state
 
 
 @torch.compiler.disable
@@ -228,9 +279,14 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
     _common_checks(q, k, v, initial_state)
     if scale is None:
         scale = k.shape[-1] ** -0.5
-    return ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state,
-                                             use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel, allow_neg_eigval,
-                                             state_v_first, _packed(cu_seqlens, q))
+    rg = _Ragged(q.shape[1], q.device, cu_seqlens, cu_seqlens_cpu)
+    if rg.needed:
+        q, k, v, g, beta = (rg.pad(x) for x in (q, k, v, g, beta))
+        cu_seqlens = rg.cu
+    o, final_state = ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state,
+                                                       use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel,
+                                                       allow_neg_eigval, state_v_first, _packed(cu_seqlens, q))
+    return rg.cut(o), final_state
 
 
 @torch.compiler.disable
@@ -240,5 +296,10 @@ def chunk_delta_rule(q, k, v, beta, scale=None, initial_state=None, output_final
     _common_checks(q, k, v, initial_state)
     if scale is None:
         scale = k.shape[-1] ** -0.5
-    return ChunkDeltaRuleFunction.apply(q, k, v, beta, scale, initial_state, output_final_state,
-                                        use_qk_l2norm_in_kernel, _packed(cu_seqlens, q))
+    rg = _Ragged(q.shape[1], q.device, cu_seqlens, cu_seqlens_cpu)
+    if rg.needed:
+        q, k, v, beta = (rg.pad(x) for x in (q, k, v, beta))
+        cu_seqlens = rg.cu
+    o, final_state = ChunkDeltaRuleFunction.apply(q, k, v, beta, scale, initial_state, output_final_state,
+                                                  use_qk_l2norm_in_kernel, _packed(cu_seqlens, q))
+    return rg.cut(o), final_state

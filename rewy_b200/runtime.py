@@ -102,20 +102,20 @@ def rejection_reason(op, arguments, device_types=("cuda",)):
         return "release envelope requires K=V=128"
     if q.shape != k.shape or k.shape[:3] != v.shape[:3]:
         return "grouped heads or unequal q/k/v shapes"
-    if k.shape[1] < 64 or k.shape[1] % 64:
-        return "sequence length must be a positive multiple of 64"
+    if k.shape[1] < 1:
+        return "sequence length must be positive"  # other lengths: the operators pad to the chunk with neutral tokens
     if arguments.get("chunk_size", 64) != 64:
         return "release envelope requires chunk_size=64"
     cu = arguments.get("cu_seqlens")
     if cu is not None:
-        # packed sequences: accepted when no chunk straddles two sequences (the reference's release envelope rejects
-        # them all: "packed/variable sequences are not release-validated")
+        # packed sequences are accepted (the reference's release envelope rejects them all: "packed/variable sequences
+        # are not release-validated"); lengths that are not multiples of 64 are padded by the operators
         host = arguments.get("cu_seqlens_cpu")
         host = cu.detach().cpu() if host is None else host
         lengths = host[1:] - host[:-1]
         if q.shape[0] != 1 or host.numel() < 2 or int(host[0]) != 0 or int(host[-1]) != k.shape[1] \
-                or bool((lengths <= 0).any()) or bool((lengths % 64 != 0).any()):
-            return "packed sequences need a batch of 1 and lengths that are positive multiples of 64"
+                or bool((lengths <= 0).any()):
+            return "packed sequences need a batch of 1 and positive lengths that add up to the token count"
     if arguments.get("cp_context") is not None:
         return "context parallelism is not release-validated"
     if arguments.get("safe_gate", False):

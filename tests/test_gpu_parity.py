@@ -425,8 +425,8 @@ def test_rejections_and_error_codes():
     import rewy_b200 as fdr
     xs = _inputs("kda", T=128, H=1)
     with fdr.use_backend("optimized"):
-        with pytest.raises(RuntimeError, match="multiple of 64"):
-            fdr.chunk_kda(xs["q"][:, :65], xs["k"][:, :65], xs["v"][:, :65], xs["g"][:, :65], xs["beta"][:, :65])
+        with pytest.raises(RuntimeError, match="custom scale"):
+            fdr.chunk_kda(xs["q"], xs["k"], xs["v"], xs["g"], xs["beta"], scale=0.5)
     saved = forward_saved("kda", xs)
     a, keep = base_args("kda", xs, saved)
     lib = _capi.load()

@@ -56,9 +56,9 @@ def test_assert_used_reports_missing_backward():
 
 @pytest.mark.parametrize("mutate,reason", [
     (lambda a: a.update(q=a["q"].float()), "BF16"),
-    (lambda a: a.update(q=a["q"][:, :65], k=a["k"][:, :65], v=a["v"][:, :65]), "multiple of 64"),
+    (lambda a: a.update(q=a["q"][:, :0], k=a["k"][:, :0], v=a["v"][:, :0]), "must be positive"),
     (lambda a: a.update(chunk_size=32), "chunk_size=64"),
-    (lambda a: a.update(cu_seqlens=torch.tensor([0, 100, 128])), "packed sequences need"),
+    (lambda a: a.update(cu_seqlens=torch.tensor([0, 100, 120])), "packed sequences need"),
     (lambda a: a.update(scale=0.5), "custom scale"),
     (lambda a: a.update(safe_gate=True), "safe_gate"),
     (lambda a: a.update(v=a["v"][..., :64]), "K=V=128"),
@@ -85,17 +85,40 @@ def test_fused_gate_and_value_first_states_follow_the_reference_envelope():
     assert rejection_reason("gdn", dict(q=t, k=t, v=t, state_v_first=True), device_types=("cpu",)) is None
 
 
-def test_packed_sequences_are_accepted_when_no_chunk_straddles_two_sequences():
+def test_packed_sequences_and_ragged_lengths_are_accepted():
     from rewy_b200.runtime import rejection_reason
     t = torch.zeros(1, 256, 2, 128, dtype=torch.bfloat16)
     ok = dict(q=t, k=t, v=t, cu_seqlens=torch.tensor([0, 64, 256]))
     assert rejection_reason("kda", ok, device_types=("cpu",)) is None
     assert rejection_reason("delta", dict(ok, cu_seqlens_cpu=torch.tensor([0, 128, 256])), device_types=("cpu",)) is None
+    assert rejection_reason("kda", dict(ok, cu_seqlens=torch.tensor([0, 37, 256])), device_types=("cpu",)) is None
+    odd = torch.zeros(2, 100, 2, 128, dtype=torch.bfloat16)
+    assert rejection_reason("gdn", dict(q=odd, k=odd, v=odd), device_types=("cpu",)) is None
     for bad in ([0, 64, 200], [0, 256, 256], [64, 256], [0, 128]):
         assert "packed sequences need" in rejection_reason("kda", dict(ok, cu_seqlens=torch.tensor(bad)), device_types=("cpu",))
     two = torch.zeros(2, 256, 2, 128, dtype=torch.bfloat16)
     assert "packed sequences need" in rejection_reason("kda", dict(q=two, k=two, v=two, cu_seqlens=torch.tensor([0, 256])),
                                                        device_types=("cpu",))
+
+
+def test_ragged_lengths_are_padded_to_the_chunk_and_cut_back():
+    """Host logic of the neutral padding: indices, padded offsets, differentiable pad and cut."""
+    from rewy_b200.functions import _Ragged
+    assert not _Ragged(128, "cpu").needed
+    rg = _Ragged(100, "cpu")
+    x = torch.arange(2 * 100 * 3, dtype=torch.float32).reshape(2, 100, 3).requires_grad_()
+    y = rg.pad(x, -1.0)
+    assert y.shape == (2, 128, 3) and torch.equal(y[:, :100], x) and bool((y[:, 100:] == -1).all())
+    assert torch.equal(rg.cut(y), x)
+    assert not _Ragged(256, "cpu", torch.tensor([0, 64, 256])).needed
+    rg = _Ragged(167, "cpu", torch.tensor([0, 37, 101, 167]))          # lengths 37, 64, 66 -> 64, 64, 128
+    assert rg.needed and rg.total == 256 and rg.cu.tolist() == [0, 64, 128, 256]
+    x = torch.randn(1, 167, 2, requires_grad=True)
+    y = rg.pad(x)
+    assert torch.equal(y[0, :37], x[0, :37]) and torch.equal(y[0, 64:128], x[0, 37:101]) and torch.equal(y[0, 128:194], x[0, 101:])
+    assert bool((y[0, 37:64] == 0).all()) and bool((y[0, 194:] == 0).all())
+    (rg.cut(y) * 2).sum().backward()
+    assert torch.equal(x.grad, torch.full_like(x, 2.0))
 
 
 def test_rejection_on_cpu_tensors_is_device():
