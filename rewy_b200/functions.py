@@ -218,6 +218,16 @@ def _common_checks(q, k, v, initial_state):
         raise ValueError(f"q and k must have the same shape, got q={tuple(q.shape)} vs k={tuple(k.shape)}")
     if initial_state is not None and initial_state.dtype != torch.float32:
         raise ValueError("initial_state must be in float32.")
+    if v.shape[2] != q.shape[2] and (v.shape[2] < q.shape[2] or v.shape[2] % q.shape[2] != 0):
+        raise ValueError(f"the value heads ({v.shape[2]}) must be a multiple of the query/key heads ({q.shape[2]})")
+
+
+def _grouped(q, k, v):
+    """Grouped value heads (HV = G * H; value head hv reads query/key head hv // G, as in FLA's kernels): q and k are
+    repeated to HV heads, and autograd's backward of the repeat sums dq and dk over each group.  The kernels then see
+    equal head counts; the price is G copies of q and k."""
+    G = v.shape[2] // q.shape[2]
+    return (q, k) if G == 1 else (q.repeat_interleave(G, 2), k.repeat_interleave(G, 2))
 
 
 @torch.compiler.disable
@@ -240,6 +250,7 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
             raise ValueError("rewy_b200 chunk_kda: the lower_bound gate law belongs to safe_gate, which is not supported")
     if scale is None:
         scale = k.shape[-1] ** -0.5
+    q, k = _grouped(q, k, v)
     rg = _Ragged(q.shape[1], q.device, cu_seqlens, cu_seqlens_cpu)
     if rg.needed:
         # a raw gate input goes through -exp(A_log) softplus(g + dt_bias): a very negative value gives decay 0
@@ -260,6 +271,7 @@ def chunk_gdn2(q, k, v, g, b, w, scale=None, initial_state=None, output_final_st
     _common_checks(q, k, v, initial_state)
     if scale is None:
         scale = k.shape[-1] ** -0.5
+    q, k = _grouped(q, k, v)
     rg = _Ragged(q.shape[1], q.device, cu_seqlens, cu_seqlens_cpu)
     if rg.needed:
         q, k, v, g, b, w = (rg.pad(x) for x in (q, k, v, g, b, w))
@@ -279,6 +291,7 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
     _common_checks(q, k, v, initial_state)
     if scale is None:
         scale = k.shape[-1] ** -0.5
+    q, k = _grouped(q, k, v)
     rg = _Ragged(q.shape[1], q.device, cu_seqlens, cu_seqlens_cpu)
     if rg.needed:
         q, k, v, g, beta = (rg.pad(x) for x in (q, k, v, g, beta))
@@ -296,6 +309,7 @@ def chunk_delta_rule(q, k, v, beta, scale=None, initial_state=None, output_final
     _common_checks(q, k, v, initial_state)
     if scale is None:
         scale = k.shape[-1] ** -0.5
+    q, k = _grouped(q, k, v)
     rg = _Ragged(q.shape[1], q.device, cu_seqlens, cu_seqlens_cpu)
     if rg.needed:
         q, k, v, beta = (rg.pad(x) for x in (q, k, v, beta))

@@ -100,8 +100,8 @@ def rejection_reason(op, arguments, device_types=("cuda",)):
         return "release envelope uses BF16 q/k/v"
     if k.shape[-1] != 128 or v.shape[-1] != 128:
         return "release envelope requires K=V=128"
-    if q.shape != k.shape or k.shape[:3] != v.shape[:3]:
-        return "grouped heads or unequal q/k/v shapes"
+    if q.shape != k.shape or k.shape[:2] != v.shape[:2] or v.shape[2] < k.shape[2] or v.shape[2] % k.shape[2]:
+        return "unequal q/k/v shapes"  # grouped value heads (a multiple of the q/k heads) are accepted
     if k.shape[1] < 1:
         return "sequence length must be positive"  # other lengths: the operators pad to the chunk with neutral tokens
     if arguments.get("chunk_size", 64) != 64:

@@ -88,3 +88,21 @@ def test_padding_tokens_of_a_fused_gate_call_do_not_decay_the_state():
         o_a, fin_a = fdr.chunk_kda(xs["q"], xs["k"], xs["v"], act, xs["beta"], initial_state=xs["initial_state"],
                                    output_final_state=True)
     assert nrmse(o_a, o_f) <= 2e-3 and nrmse(fin_a, fin_f) <= 1e-3, (nrmse(o_a, o_f), nrmse(fin_a, fin_f))
+
+
+@pytest.mark.parametrize("op", ("kda", "gdn"))
+def test_grouped_value_heads_equal_the_call_with_repeated_query_and_key_heads(op):
+    """HV = 2 H: value head hv reads query/key head hv // 2 (FLA's convention); dq and dk are sums over each group."""
+    xs = make_inputs(op, 1, 128, 4, seed=21, device=DEV, gate_scale=0.1, gate="softplus")
+    ins = {n: x for n, x in operator_inputs(op, xs).items() if x is not None}
+    grouped = dict(ins, q=ins["q"][:, :, ::2].contiguous(), k=ins["k"][:, :, ::2].contiguous())
+    repeated = dict(ins, q=grouped["q"].repeat_interleave(2, 2), k=grouped["k"].repeat_interleave(2, 2))
+    o_g, fin_g, g_g = _call(op, grouped, xs["do"], xs["dht"])
+    o_r, fin_r, g_r = _call(op, repeated, xs["do"], xs["dht"])
+    assert g_g["q"].shape == grouped["q"].shape and torch.equal(o_g, o_r) and torch.equal(fin_g, fin_r)
+    for n in ins:
+        if n in ("q", "k"):
+            want = g_r[n].float().view(1, 128, 2, 2, 128).sum(3)
+            assert nrmse(want, g_g[n]) <= 4e-3, (op, n, nrmse(want, g_g[n]))     # one BF16 rounding of the sum
+        else:
+            assert torch.equal(g_g[n], g_r[n]), (op, n)
