@@ -222,6 +222,37 @@ def _common_checks(q, k, v, initial_state):
         raise ValueError(f"the value heads ({v.shape[2]}) must be a multiple of the query/key heads ({q.shape[2]})")
 
 
+class _Narrow:
+    """Head dimensions below 128: the key and value channels are filled up with zeros (exact: a zero channel adds
+    nothing to any product and its state rows stay zero) and outputs and states are cut back.  The scale keeps the
+    caller's K.  Everything here is differentiable tensor code around the autograd function."""
+
+    def __init__(self, q, v):
+        self.K, self.V = q.shape[-1], v.shape[-1]
+        if self.K > 128 or self.V > 128:
+            raise ValueError(f"head dimensions above 128 are not supported (K={self.K}, V={self.V})")
+        self.needed = self.K != 128 or self.V != 128
+
+    def key(self, x):    # [..., K] -> [..., 128]
+        return x if x is None or not self.needed else torch.nn.functional.pad(x, (0, 128 - self.K))
+
+    def value(self, x):  # [..., V] -> [..., 128]
+        return x if x is None or not self.needed else torch.nn.functional.pad(x, (0, 128 - self.V))
+
+    def state(self, h, v_first=False):  # [N,H,K,V] (or [N,H,V,K]) -> [N,H,128,128]
+        if h is None or not self.needed:
+            return h
+        last, first = (self.K, self.V) if v_first else (self.V, self.K)
+        return torch.nn.functional.pad(h, (0, 128 - last, 0, 128 - first))
+
+    def cut(self, o, final_state, v_first=False):
+        if not self.needed:
+            return o, final_state
+        if final_state is not None:
+            final_state = final_state[..., :self.V, :self.K] if v_first else final_state[..., :self.K, :self.V]
+        return o[..., :self.V], final_state
+
+
 def _grouped(q, k, v):
     """Grouped value heads (HV = G * H; value head hv reads query/key head hv // G, as in FLA's kernels): q and k are
     repeated to HV heads, and autograd's backward of the repeat sums dq and dk over each group.  The kernels then see
@@ -250,6 +281,11 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
             raise ValueError("rewy_b200 chunk_kda: the lower_bound gate law belongs to safe_gate, which is not supported")
     if scale is None:
         scale = k.shape[-1] ** -0.5
+    nw = _Narrow(q, v)
+    if nw.needed:
+        if use_gate_in_kernel:
+            raise ValueError("rewy_b200 chunk_kda: the fused gate needs K = 128 (dt_bias is laid out per channel)")
+        q, k, g, v, initial_state = nw.key(q), nw.key(k), nw.key(g), nw.value(v), nw.state(initial_state, state_v_first)
     q, k = _grouped(q, k, v)
     rg = _Ragged(q.shape[1], q.device, cu_seqlens, cu_seqlens_cpu)
     if rg.needed:
@@ -259,7 +295,7 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     o, final_state = ChunkKDAFunction.apply(q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state,
                                             use_qk_l2norm_in_kernel, use_gate_in_kernel, use_beta_sigmoid_in_kernel,
                                             allow_neg_eigval, disable_recompute, state_v_first, _packed(cu_seqlens, q))
-    return rg.cut(o), final_state
+    return nw.cut(rg.cut(o), final_state, state_v_first)
 
 
 @torch.compiler.disable
@@ -271,6 +307,10 @@ def chunk_gdn2(q, k, v, g, b, w, scale=None, initial_state=None, output_final_st
     _common_checks(q, k, v, initial_state)
     if scale is None:
         scale = k.shape[-1] ** -0.5
+    nw = _Narrow(q, v)
+    if nw.needed:
+        q, k, g, b = nw.key(q), nw.key(k), nw.key(g), nw.key(b)
+        v, w, initial_state = nw.value(v), nw.value(w), nw.state(initial_state, state_v_first)
     q, k = _grouped(q, k, v)
     rg = _Ragged(q.shape[1], q.device, cu_seqlens, cu_seqlens_cpu)
     if rg.needed:
@@ -279,7 +319,7 @@ def chunk_gdn2(q, k, v, g, b, w, scale=None, initial_state=None, output_final_st
     o, final_state = ChunkGDN2Function.apply(q, k, v, g, b, w, scale, initial_state, output_final_state,
                                              use_qk_l2norm_in_kernel, disable_recompute, state_v_first,
                                              _packed(cu_seqlens, q))
-    return rg.cut(o), final_state
+    return nw.cut(rg.cut(o), final_state, state_v_first)
 
 
 @torch.compiler.disable
@@ -291,6 +331,9 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
     _common_checks(q, k, v, initial_state)
     if scale is None:
         scale = k.shape[-1] ** -0.5
+    nw = _Narrow(q, v)
+    if nw.needed:
+        q, k, v, initial_state = nw.key(q), nw.key(k), nw.value(v), nw.state(initial_state, state_v_first)
     q, k = _grouped(q, k, v)
     rg = _Ragged(q.shape[1], q.device, cu_seqlens, cu_seqlens_cpu)
     if rg.needed:
@@ -299,7 +342,7 @@ def chunk_gated_delta_rule(q, k, v, g, beta, scale=None, initial_state=None, out
     o, final_state = ChunkGatedDeltaRuleFunction.apply(q, k, v, g, beta, scale, initial_state, output_final_state,
                                                        use_qk_l2norm_in_kernel, use_beta_sigmoid_in_kernel,
                                                        allow_neg_eigval, state_v_first, _packed(cu_seqlens, q))
-    return rg.cut(o), final_state
+    return nw.cut(rg.cut(o), final_state, state_v_first)
 
 
 @torch.compiler.disable
@@ -309,6 +352,9 @@ def chunk_delta_rule(q, k, v, beta, scale=None, initial_state=None, output_final
     _common_checks(q, k, v, initial_state)
     if scale is None:
         scale = k.shape[-1] ** -0.5
+    nw = _Narrow(q, v)
+    if nw.needed:
+        q, k, v, initial_state = nw.key(q), nw.key(k), nw.value(v), nw.state(initial_state)
     q, k = _grouped(q, k, v)
     rg = _Ragged(q.shape[1], q.device, cu_seqlens, cu_seqlens_cpu)
     if rg.needed:
@@ -316,4 +362,4 @@ def chunk_delta_rule(q, k, v, beta, scale=None, initial_state=None, output_final
         cu_seqlens = rg.cu
     o, final_state = ChunkDeltaRuleFunction.apply(q, k, v, beta, scale, initial_state, output_final_state,
                                                   use_qk_l2norm_in_kernel, _packed(cu_seqlens, q))
-    return rg.cut(o), final_state
+    return nw.cut(rg.cut(o), final_state)

@@ -98,8 +98,8 @@ def rejection_reason(op, arguments, device_types=("cuda",)):
         return "mixed devices"
     if any(x.dtype != torch.bfloat16 for x in (q, k, v)):
         return "release envelope uses BF16 q/k/v"
-    if k.shape[-1] != 128 or v.shape[-1] != 128:
-        return "release envelope requires K=V=128"
+    if k.shape[-1] > 128 or v.shape[-1] > 128:
+        return "head dimensions above K=V=128 are not supported"  # below: the operators fill up with zero channels
     if q.shape != k.shape or k.shape[:2] != v.shape[:2] or v.shape[2] < k.shape[2] or v.shape[2] % k.shape[2]:
         return "unequal q/k/v shapes"  # grouped value heads (a multiple of the q/k heads) are accepted
     if k.shape[1] < 1:
@@ -127,6 +127,8 @@ def rejection_reason(op, arguments, device_types=("cuda",)):
     scale = arguments.get("scale")
     if scale is not None and scale != k.shape[-1] ** -0.5:
         return "custom scale is not release-validated"
+    if op == "kda" and arguments.get("use_gate_in_kernel", False) and k.shape[-1] != 128:
+        return "the KDA fused gate needs K=128"
     if op == "gdn" and arguments.get("use_gate_in_kernel", False):
         return "GDN fused gate is not release-validated"
     if op == "gdn2" and arguments.get("use_gate_in_kernel", False):

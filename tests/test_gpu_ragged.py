@@ -106,3 +106,20 @@ def test_grouped_value_heads_equal_the_call_with_repeated_query_and_key_heads(op
             assert nrmse(want, g_g[n]) <= 4e-3, (op, n, nrmse(want, g_g[n]))     # one BF16 rounding of the sum
         else:
             assert torch.equal(g_g[n], g_r[n]), (op, n)
+
+
+@pytest.mark.parametrize("op", OPS)
+def test_head_dimensions_below_128_against_the_recurrence(op):
+    """K = 64, V = 96: zero channels are added for the kernels and cut from the results; the scale stays 64^-0.5."""
+    from oracle import recurrence_grads
+    xs = make_inputs(op, 1, 128, 2, K=64, V=96, seed=5, device=DEV, gate_scale=0.05, gate="softplus")
+    ins = operator_inputs(op, xs)
+    ref, o_ref, fin_ref = recurrence_grads(op, {n: (x.detach().cpu() if x is not None else None) for n, x in ins.items()},
+                                           xs["do"].cpu(), xs["dht"].cpu())
+    o, fin, grads = _call(op, ins, xs["do"], xs["dht"])
+    assert o.shape[-1] == 96 and fin.shape[-2:] == (64, 96)
+    errs = {n: nrmse(ref[n], g) for n, g in grads.items()}
+    errs["o"], errs["final_state"] = nrmse(o_ref, o), nrmse(fin_ref, fin)
+    print("NRMSE", op, {n: float(f"{e:.3g}") for n, e in errs.items()})
+    for n, e in errs.items():
+        assert e <= (0.02 if n in ("g", "beta", "b", "w") else 0.008), (op, n, e)

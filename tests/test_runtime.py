@@ -61,7 +61,8 @@ def test_assert_used_reports_missing_backward():
     (lambda a: a.update(cu_seqlens=torch.tensor([0, 100, 120])), "packed sequences need"),
     (lambda a: a.update(scale=0.5), "custom scale"),
     (lambda a: a.update(safe_gate=True), "safe_gate"),
-    (lambda a: a.update(v=a["v"][..., :64]), "K=V=128"),
+    (lambda a: a.update(v=torch.zeros(1, 128, 2, 256, dtype=torch.bfloat16)), "above K=V=128"),
+    (lambda a: a.update(q=a["q"][..., :64], k=a["k"][..., :64], use_gate_in_kernel=True), "fused gate needs K=128"),
     (lambda a: a.update(v=a["v"][:, :, :1]), "unequal q/k/v"),
     (lambda a: a.update(v=a["v"][:, :64]), "unequal q/k/v"),
 ])
@@ -96,6 +97,8 @@ def test_packed_sequences_and_ragged_lengths_are_accepted():
     assert rejection_reason("kda", dict(ok, cu_seqlens=torch.tensor([0, 37, 256])), device_types=("cpu",)) is None
     four = torch.zeros(1, 256, 4, 128, dtype=torch.bfloat16)           # grouped value heads: HV = 2 H
     assert rejection_reason("kda", dict(q=t, k=t, v=four), device_types=("cpu",)) is None
+    narrow = torch.zeros(1, 256, 2, 64, dtype=torch.bfloat16)         # K = 64 keys, V = 128 values
+    assert rejection_reason("gdn", dict(q=narrow, k=narrow, v=t), device_types=("cpu",)) is None
     odd = torch.zeros(2, 100, 2, 128, dtype=torch.bfloat16)
     assert rejection_reason("gdn", dict(q=odd, k=odd, v=odd), device_types=("cpu",)) is None
     for bad in ([0, 64, 200], [0, 256, 256], [64, 256], [0, 128]):
