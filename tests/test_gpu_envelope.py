@@ -1,11 +1,12 @@
-"""Sequence lengths that are not multiples of the 64-token chunk, for a fixed batch and for packed sequences.
+"""Envelope extensions handled in the operators, around the autograd functions (rewy_b200/functions.py):
+lengths that are not multiples of the 64-token chunk (fixed batch and packed; neutral padding tokens), grouped value
+heads (q and k repeated per group) and head dimensions below 128 (zero channels).
 
-The operators extend every sequence to the next chunk boundary with neutral tokens (q = k = v = 0, no decay) and cut
-the result back (rewy_b200/functions.py, _Ragged).  Checked here: forward outputs, final states and every gradient
-against the FP64 token recurrence with the reference's own acceptance limits (validation.py:40-45,68-71), a packed
-ragged batch against its sequences run one at a time, and that the padding tokens of a fused-gate call leave the
-final state alone.  FLA covers such lengths by bounds checks in its kernels; the reference's release envelope rejects
-them (src/fast_delta_rule/runtime.py:87-88).
+Checked: forward outputs, final states and every gradient against the FP64 token recurrence with the reference's own
+acceptance limits (validation.py:40-45,68-71); a packed ragged batch against its sequences run one at a time; the
+padding tokens of a fused-gate call leave the final state alone; a grouped call equals the call with repeated heads.
+FLA covers these cases inside its kernels; the reference's release envelope rejects them
+(src/fast_delta_rule/runtime.py:84-88).
 """
 import pytest
 import torch
