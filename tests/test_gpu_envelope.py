@@ -124,3 +124,19 @@ def test_head_dimensions_below_128_against_the_recurrence(op):
     print("NRMSE", op, {n: float(f"{e:.3g}") for n, e in errs.items()})
     for n, e in errs.items():
         assert e <= (0.02 if n in ("g", "beta", "b", "w") else 0.008), (op, n, e)
+
+
+@pytest.mark.parametrize("op", ("kda", "delta"))
+def test_non_contiguous_inputs_give_the_contiguous_result(op):
+    """The reference's accelerator test passes a non-contiguous q (tests/test_accelerator.py:41)."""
+    xs = make_inputs(op, 2, 128, 2, seed=9, device=DEV, gate_scale=0.1, gate="softplus")
+    ins = {n: x for n, x in operator_inputs(op, xs).items() if x is not None}
+    strided = dict(ins)
+    strided["q"] = torch.stack([ins["q"], ins["q"]], -1)[..., 0]                 # channel stride 2
+    strided["v"] = ins["v"].transpose(1, 2).contiguous().transpose(1, 2)          # head-major storage
+    assert not strided["q"].is_contiguous() and not strided["v"].is_contiguous()
+    o, fin, g = _call(op, ins, xs["do"], xs["dht"])
+    o2, fin2, g2 = _call(op, strided, xs["do"].transpose(1, 2).contiguous().transpose(1, 2), xs["dht"])
+    assert torch.equal(o, o2) and torch.equal(fin, fin2)
+    for n in g:
+        assert torch.equal(g[n], g2[n]), (op, n)
