@@ -66,8 +66,18 @@ def _bind(module_path, attribute, op, what):
 
 
 def bind_qwen3_5():
-    """transformers' Qwen3.5: layers built after this call run the ``gdn`` operator for their chunked delta rule."""
-    _bind("transformers.models.qwen3_5.modeling_qwen3_5", "torch_chunk_gated_delta_rule", "gdn", "qwen3_5")
+    """transformers' Qwen3.5: layers built after this call run the ``gdn`` operator for their chunked delta rule.  The
+    modelling file takes FLA's ``chunk_gated_delta_rule`` when flash-linear-attention is importable and its own
+    ``torch_chunk_gated_delta_rule`` otherwise; whichever it would pick is pointed at the operator."""
+    path = "transformers.models.qwen3_5.modeling_qwen3_5"
+    _bind(path, "torch_chunk_gated_delta_rule", "gdn", "qwen3_5")
+    if getattr(importlib.import_module(path), "chunk_gated_delta_rule", None) is not None:
+        from .runtime import original_operator
+        try:
+            original_operator("gdn")  # capture FLA's own function before its alias in the modelling file changes
+        except RuntimeError:
+            pass
+        _bind(path, "chunk_gated_delta_rule", "gdn", "qwen3_5")
 
 
 def bind_gdn2():
