@@ -1,4 +1,5 @@
-"""Packed sequences (FLA's cu_seqlens) whose lengths are multiples of 64: the chunk-local kernels do not see sequence
+"""Packed sequences (FLA's cu_seqlens) whose lengths are multiples of 64 (the form the library itself takes; other
+lengths are padded to it by the operators): the chunk-local kernels do not see sequence
 boundaries, the two state scans take per-sequence bounds.  A packed batch must give, sequence by sequence, exactly what
 the same sequences give when they are run one at a time (same kernels, same arithmetic order), for the forward outputs
 and every gradient, with initial states and final-state gradients per sequence.  The reference's kernels take cu_seqlens
@@ -61,16 +62,17 @@ def test_packed_batch_equals_its_sequences_run_one_at_a_time(op, saved):
         at += T
 
 
-def test_a_length_that_is_not_a_multiple_of_64_is_refused():
-    """The operators refuse it on the host; the scan kernels, given such offsets directly, record it in the status word
-    and leave their sequence untouched."""
+def test_offsets_that_do_not_match_the_token_count_are_refused_and_the_kernels_check_lengths():
+    """The operators refuse offsets that do not add up on the host (lengths that are not multiples of 64 are padded
+    there, tests/test_gpu_envelope.py); the scan kernels, given such offsets directly, record the length in the status
+    word and leave their sequence untouched."""
     import rewy_b200 as fdr
     from rewy_b200.forward import chunk_forward
     xs = make_inputs("kda", 1, 256, 2, seed=3, device=DEV)
     with fdr.use_backend("optimized"):
         with pytest.raises(RuntimeError, match="packed sequences need"):
             fdr.chunk_kda(xs["q"], xs["k"], xs["v"], xs["g"], xs["beta"],
-                          cu_seqlens=torch.tensor([0, 100, 256], device=DEV))
+                          cu_seqlens=torch.tensor([0, 100, 200], device=DEV))
     with pytest.raises(RuntimeError, match="device status"):
         chunk_forward("kda", xs["q"], xs["k"], xs["v"], g=xs["g"], beta=xs["beta"], check_status=True,
                       cu_seqlens=torch.tensor([0, 100, 256], device=DEV))
