@@ -354,6 +354,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
     }
   };
   fetch_rows(blockIdx.x, 0);
+  __syncthreads();  // the rows of the first chunk are in place (later ones are fetched a chunk ahead, before its barriers)
 
   for (int chunk = blockIdx.x; chunk < p.total_chunks && alive; chunk += gridDim.x) {
     // Work order: head fastest, then chunk, then batch.  CTAs that run at the same time then read the same token rows
@@ -389,7 +390,7 @@ chunk_adjoint_tc_kernel(const __grid_constant__ CUtensorMap tmAkk, const __grid_
                  : 0.f;
     }
     if (GATE == GATE_VECTOR && wg == NWG - 1) sGl[kch] = g[HALF - 1];
-    __syncthreads();  // everyone has its k / g out of the tiles before they are rebuilt as Ec / dAkk tiles
+    // (the tiles these values came from are first written again after the barriers below)
     float cen = 0.f;
     bool wide = false;
     if (GATE != GATE_NONE) {
